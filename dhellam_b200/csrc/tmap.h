@@ -1,0 +1,24 @@
+// Host-side cache of TMA tensor maps (cuTensorMapEncodeTiled obtained through the
+// runtime's driver entry point, so the library does not link libcuda).
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace dh {
+
+// 2-D bf16/fp32 tensor: `inner` contiguous elements per row, `outer` rows,
+// `row_stride_bytes` between rows; box = box_inner x box_outer; 128-byte swizzle when
+// box_inner * elem_bytes == 128, none otherwise.
+// Returns nullptr on failure (dh_last_error_string() has the reason).
+const CUtensorMap* get_tmap_2d(const void* base, int elem_bytes, uint64_t inner, uint64_t outer,
+                               uint64_t row_stride_bytes, uint32_t box_inner, uint32_t box_outer, bool swizzle128);
+
+// 3-D variant (inner, mid, outer) with strides for mid and outer in bytes.
+const CUtensorMap* get_tmap_3d(const void* base, int elem_bytes, uint64_t d0, uint64_t d1, uint64_t d2,
+                               uint64_t stride1_bytes, uint64_t stride2_bytes, uint32_t b0, uint32_t b1, uint32_t b2,
+                               bool swizzle128);
+
+void set_last_error(const char* fmt, ...);
+
+}  // namespace dh

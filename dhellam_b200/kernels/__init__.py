@@ -1,0 +1,97 @@
+"""ctypes loader for the sm_100a kernel library.
+
+``lib()`` returns the loaded ``libdhellam_b200.so``.  On a machine with a GPU a missing
+or unloadable library is an error (no silent fall-back to PyTorch); on a CPU-only
+machine ``available()`` is False and the ops layer uses its fp32 reference path.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from ctypes import c_char_p, c_float, c_int, c_int64, c_uint64, c_void_p
+from pathlib import Path
+
+import torch
+
+_LIB = None
+_LIB_PATH = Path(__file__).resolve().parent.parent / "lib" / "libdhellam_b200.so"
+
+
+class KernelError(RuntimeError):
+    """A launch was refused by the library (bad arguments, failed launch)."""
+
+
+class DeviceWaitTimeout(RuntimeError):
+    """A bounded device-side wait gave up; the status word says where."""
+
+
+class Status(ctypes.Structure):
+    _fields_ = [("code", c_int), ("where", c_int), ("block", c_int), ("extra", c_int)]
+
+
+def available() -> bool:
+    return torch.cuda.is_available()
+
+
+def lib_path() -> Path:
+    return _LIB_PATH
+
+
+def lib():
+    global _LIB
+    if _LIB is not None:
+        return _LIB
+    if not _LIB_PATH.exists():
+        if os.environ.get("DHELLAM_B200_BUILD_ON_IMPORT", "1") == "1":
+            from .build import build
+            build()
+        else:
+            raise KernelError(f"{_LIB_PATH} is missing; run python -m dhellam_b200.kernels.build")
+    _LIB = ctypes.CDLL(str(_LIB_PATH))
+    _declare(_LIB)
+    return _LIB
+
+
+def _declare(L):
+    L.dh_status_device_ptr.restype = c_void_p
+    L.dh_status_read.argtypes = [ctypes.POINTER(Status), c_int]
+    L.dh_last_error_string.restype = c_char_p
+    L.dh_sm_count.restype = c_int
+    # The remaining prototypes are attached by the modules that use them (see _proto).
+
+
+def proto(name: str, argtypes, restype=c_int):
+    fn = getattr(lib(), name)
+    if not getattr(fn, "_dh_declared", False):
+        fn.argtypes = argtypes
+        fn.restype = restype
+        fn._dh_declared = True
+    return fn
+
+
+def check(rc: int, what: str = "kernel"):
+    if rc != 0:
+        msg = lib().dh_last_error_string().decode()
+        raise KernelError(f"{what} failed (code {rc}): {msg}")
+
+
+def read_status(clear: bool = True) -> Status:
+    """Synchronises the device and returns the status word."""
+    st = Status()
+    check(lib().dh_status_read(ctypes.byref(st), 1 if clear else 0), "dh_status_read")
+    return st
+
+
+def raise_on_device_error():
+    st = read_status(clear=True)
+    if st.code != 0:
+        raise DeviceWaitTimeout(f"device status code={st.code} where={st.where} block={st.block} extra={st.extra}")
+
+
+def stream_ptr(stream=None) -> int:
+    s = stream if stream is not None else torch.cuda.current_stream()
+    return s.cuda_stream
+
+
+def ptr(t) -> int:
+    return 0 if t is None else t.data_ptr()
