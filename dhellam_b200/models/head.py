@@ -1,0 +1,109 @@
+"""Head block: embedding at the bottom of the model and final norm -> LM head -> loss at
+the top, both living on the first pipeline stage of the folded model.
+
+Capability parity with the reference's ``DSHB`` (dhellam/core/dshb.py:98-242): embedding
+forward of micro-batch k runs beside the loss-head backward of micro-batch k-1, and the
+loss-head forward of k beside the embedding backward of k-1; the LM-head weight is tied to
+the word embedding (dshb.py:256-262).  Unlike the reference, which differentiates the head
+through autograd (``template_bwd_new``), every piece has an explicit backward that
+accumulates into ``main_grad``, and the loss uses one fused statistics exchange instead of
+three all-reduces.
+"""
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+from ..ops import comm as C
+from ..ops import embedding as E
+from ..ops import gemm as G
+from ..ops import loss as L
+from ..ops import norm as N
+from .transformer import _norm_bwd, _norm_fwd
+
+
+class HeadParams:
+    """``word_embeddings [V/t, h]``, optional ``output_weight [V/t, h]`` (untied), final norm."""
+
+    def __init__(self, tensors: dict):
+        self.__dict__.update(tensors)
+        self._names = list(tensors.keys())
+
+    def named(self):
+        return [(n, getattr(self, n)) for n in self._names]
+
+    def get(self, name, default=None):
+        return self.__dict__.get(name, default)
+
+    @property
+    def lm_weight(self):
+        return self.get("output_weight") if self.get("output_weight") is not None else self.word_embeddings
+
+
+def _use(env, t):
+    s = getattr(env, "cur_stream", None)
+    if s is not None and t is not None and t.is_cuda:
+        t.record_stream(s)
+    return t
+
+
+def vocab_range(env):
+    vl = env.cfg.vocab_size // env.ps.tp
+    return env.ps.tp_rank * vl, vl
+
+
+def embed_fwd(env, hp: HeadParams, mb):
+    """tokens -> hidden ``[T/t, h]`` (sequence-parallel rows)."""
+    v0, _ = vocab_range(env)
+    partial = E.embedding_fwd(mb.tokens, hp.word_embeddings, v0)
+    if env.ps.tp > 1:
+        x, _ = C.reduce_scatter_along_first_dim(partial, env.ps.tp_group)
+    else:
+        x = partial
+    if env.cfg.position == "learned":
+        pos = hp.position_embeddings[mb.positions_local.long()]
+        x = x + pos
+    return x
+
+
+def embed_bwd(env, hp: HeadParams, mb, dx):
+    v0, _ = vocab_range(env)
+    dx = _use(env, dx)
+    if env.cfg.position == "learned":
+        hp.position_embeddings.main_grad.index_add_(0, mb.positions_local.long(), dx.float())
+    full, _ = C.gather_along_first_dim(dx, env.ps.tp_group)
+    E.embedding_bwd(full, mb.tokens, hp.word_embeddings.main_grad, v0)
+
+
+def loss_fwd(env, hp: HeadParams, mb, x):
+    """final norm -> gather -> logits -> vocab-parallel CE -> masked mean.
+    Returns ``(loss scalar tensor, saved)``."""
+    x = _use(env, x)
+    y, stat = _norm_fwd(env, x, hp.final_ln_weight, hp.get("final_ln_bias"), 0)
+    y_full, _ = C.gather_along_first_dim(y, env.ps.tp_group)
+    logits = G.gemm_nt(y_full, hp.lm_weight)
+    v0, _ = vocab_range(env)
+    loss_tok, lse = L.vocab_parallel_ce_fwd(logits, mb.labels, v0, env.ps.tp_group)
+    mask = mb.loss_mask.reshape(-1).float()
+    sums = torch.stack([(loss_tok * mask).sum(), mask.sum()])
+    if env.ps.cp > 1:
+        dist.all_reduce(sums, group=env.ps.cp_group)
+    loss = sums[0] / sums[1].clamp_min(1.0)
+    saved = dict(x=x, stat=stat, y_full=y_full, logits=logits, lse=lse, count=sums[1])
+    return loss, saved
+
+
+def loss_bwd(env, hp: HeadParams, mb, saved, grad_scale: float):
+    """Returns ``dx [T/t, h]``; accumulates the LM-head and final-norm gradients."""
+    v0, _ = vocab_range(env)
+    g_tok = L.mask_scale_loss_bwd(mb.loss_mask, saved["count"], grad_scale)
+    logits = _use(env, saved.pop("logits"))
+    dlogits = L.vocab_parallel_ce_bwd_(logits, mb.labels, _use(env, saved.pop("lse")), g_tok, v0)
+    if dlogits.dtype != hp.lm_weight.dtype:
+        dlogits = dlogits.to(hp.lm_weight.dtype)
+    y_full = _use(env, saved.pop("y_full"))
+    d_y_full = G.gemm_nn(dlogits, hp.lm_weight)
+    G.gemm_tn_acc(dlogits, y_full, hp.lm_weight.main_grad)
+    d_y, _ = C.reduce_scatter_along_first_dim(d_y_full, env.ps.tp_group)
+    dx = _norm_bwd(env, d_y, _use(env, saved.pop("x")), hp.final_ln_weight, hp.get("final_ln_bias"), saved.pop("stat"), None, 0)
+    return dx

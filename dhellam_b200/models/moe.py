@@ -1,0 +1,179 @@
+"""Routed expert MLP (Mixtral family) as forward/backward strand ops.
+
+The reference advertises expert parallelism (README.md:8) but has no router, dispatch or
+expert GEMM in its op set (dhellam/core/dstb.py:24-58); the only trace is an
+``all_to_all_single`` entry in its micro-benchmark (micro_benchmark/overlap.py:141-145).
+These ops are therefore new: softmax top-k router with the load-balancing auxiliary loss,
+dropless token dispatch (permute by expert, variable-size all-to-all over the expert
+parallel group), per-expert GEMMs on the tcgen05 kernel over contiguous row groups,
+SwiGLU, and the weighted combine; every op has an explicit backward.
+
+Tensor parallelism inside an expert is not combined with expert parallelism here
+(``tp`` must be 1 for MoE layers).
+"""
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+from ..ops import activation as A
+from ..ops import comm as C
+from ..ops import gemm as G
+from ..ops import moe as M
+
+
+def _use(run, t):
+    s = getattr(run.env, "cur_stream", None)
+    if s is not None and t is not None and t.is_cuda:
+        t.record_stream(s)
+    return t
+
+
+# --------------------------------------------------------------------------- forward
+def f_router(run):
+    env, p = run.env, run.params
+    assert env.ps.tp == 1, "expert layers need tp = 1"
+    x = _use(run, run.v.pop("ln2"))
+    probs, topi, gates = M.router_topk_fwd(x, p.router_weight, env.cfg.moe_top_k)
+    run.acts["moe_x"], run.acts["moe_probs"], run.acts["moe_topi"], run.acts["moe_gates"] = x, probs, topi, gates
+    if env.training and env.cfg.moe_aux_loss_coeff > 0:
+        env.moe_aux.append(M.aux_loss(probs, topi, env.cfg.num_experts))
+    run.v["moe_x"] = x
+
+
+def f_dispatch(run):
+    env = run.env
+    x = _use(run, run.v.pop("moe_x"))
+    plan = M.make_plan(run.acts["moe_topi"], env.cfg.num_experts, env.ps.ep, env.ps.ep_group)
+    run.acts["moe_plan"] = plan
+    xp = M.permute_rows(x, plan.src_row)                        # rows grouped by (destination rank, expert)
+    xr = C.all_to_all_rows(xp, plan.send_counts, plan.recv_counts, env.ps.ep_group)
+    xe = M.permute_rows(xr, plan.recv_sort) if plan.recv_sort is not None else xr   # expert-major on the owner
+    run.acts["moe_xe"] = xe
+    run.v["moe_xe"] = xe
+
+
+def _expert_loop(plan, fn):
+    o = 0
+    for e, n in enumerate(plan.expert_rows):
+        if n > 0:
+            fn(e, o, o + n)
+        o += n
+
+
+def f_expert_c(run):
+    p = run.params
+    xe = _use(run, run.v.pop("moe_xe"))
+    plan = run.acts["moe_plan"]
+    w = p.expert_column_weight
+    z = torch.empty((xe.shape[0], w.shape[1]), dtype=xe.dtype, device=xe.device)
+    _expert_loop(plan, lambda e, a, b: G.gemm_nt(xe[a:b], w[e], out=z[a:b], sm_budget=run.budget("gemm_expert_c")))
+    run.acts["moe_z"] = z
+    run.v["moe_z"] = z
+
+
+def f_expert_act(run):
+    z = _use(run, run.v.pop("moe_z"))
+    a = A.swiglu_fwd(z) if run.env.cfg.gated else A.gelu_fwd(z)
+    run.acts["moe_a"] = a
+    run.v["moe_a"] = a
+
+
+def f_expert_l(run):
+    p = run.params
+    a = _use(run, run.v.pop("moe_a"))
+    plan = run.acts["moe_plan"]
+    w = p.expert_linear_weight
+    y = torch.empty((a.shape[0], w.shape[1]), dtype=a.dtype, device=a.device)
+    _expert_loop(plan, lambda e, lo, hi: G.gemm_nt(a[lo:hi], w[e], out=y[lo:hi], sm_budget=run.budget("gemm_expert_l")))
+    run.v["moe_y"] = y
+
+
+def f_combine(run):
+    env = run.env
+    y = _use(run, run.v.pop("moe_y"))
+    plan = run.acts["moe_plan"]
+    yr = M.unpermute_rows(y, plan.recv_sort) if plan.recv_sort is not None else y
+    yb = C.all_to_all_rows(yr, plan.recv_counts, plan.send_counts, env.ps.ep_group)
+    run.acts["moe_yb"] = yb                                     # per (token, k) expert outputs, dispatch order
+    run.v["fc2"] = M.combine_rows(yb, plan, run.acts["moe_gates"])
+
+
+# --------------------------------------------------------------------------- backward
+def b_combine_bwd(run):
+    env = run.env
+    d_out = _use(run, run.v.pop("d_fc2"))                       # [T, h]
+    plan = run.acts["moe_plan"]
+    gates = run.acts["moe_gates"]
+    yb = _use(run, run.acts.pop("moe_yb"))
+    d_yb, d_gates = M.combine_rows_bwd(d_out, yb, plan, gates)
+    run.v["d_gates"] = d_gates
+    d_yr = C.all_to_all_rows(d_yb, plan.send_counts, plan.recv_counts, env.ps.ep_group)
+    run.v["d_y"] = M.permute_rows(d_yr, plan.recv_sort) if plan.recv_sort is not None else d_yr
+
+
+def b_dgrad_expert_l(run):
+    p = run.params
+    d_y = _use(run, run.v["d_y"])
+    plan = run.acts["moe_plan"]
+    w = p.expert_linear_weight
+    d_a = torch.empty((d_y.shape[0], w.shape[2]), dtype=d_y.dtype, device=d_y.device)
+    _expert_loop(plan, lambda e, lo, hi: G.gemm_nn(d_y[lo:hi], w[e], out=d_a[lo:hi], sm_budget=run.budget("gemm_dgrad_expert_l")))
+    run.v["d_a"] = d_a
+
+
+def b_wgrad_expert_l(run):
+    p = run.params
+    d_y = _use(run, run.v["d_y"])
+    a = _use(run, run.acts.pop("moe_a"))
+    plan = run.acts["moe_plan"]
+    mg = p.expert_linear_weight.main_grad
+    _expert_loop(plan, lambda e, lo, hi: G.gemm_tn_acc(d_y[lo:hi], a[lo:hi], mg[e], sm_budget=run.budget("gemm_wgrad_expert_l")))
+
+
+def b_expert_act_bwd(run):
+    d_a = _use(run, run.v.pop("d_a"))
+    z = _use(run, run.acts.pop("moe_z"))
+    run.v["d_z"] = A.swiglu_bwd(d_a, z) if run.env.cfg.gated else A.gelu_bwd(d_a, z)
+
+
+def b_dgrad_expert_c(run):
+    p = run.params
+    d_z = _use(run, run.v["d_z"])
+    plan = run.acts["moe_plan"]
+    w = p.expert_column_weight
+    d_xe = torch.empty((d_z.shape[0], w.shape[2]), dtype=d_z.dtype, device=d_z.device)
+    _expert_loop(plan, lambda e, lo, hi: G.gemm_nn(d_z[lo:hi], w[e], out=d_xe[lo:hi], sm_budget=run.budget("gemm_dgrad_expert_c")))
+    run.v["d_xe"] = d_xe
+
+
+def b_wgrad_expert_c(run):
+    p = run.params
+    d_z = _use(run, run.v["d_z"])
+    xe = _use(run, run.acts.pop("moe_xe"))
+    plan = run.acts["moe_plan"]
+    mg = p.expert_column_weight.main_grad
+    _expert_loop(plan, lambda e, lo, hi: G.gemm_tn_acc(d_z[lo:hi], xe[lo:hi], mg[e], sm_budget=run.budget("gemm_wgrad_expert_c")))
+
+
+def b_dispatch_bwd(run):
+    env = run.env
+    d_xe = _use(run, run.v.pop("d_xe"))
+    plan = run.acts["moe_plan"]
+    d_xr = M.unpermute_rows(d_xe, plan.recv_sort) if plan.recv_sort is not None else d_xe
+    d_xp = C.all_to_all_rows(d_xr, plan.recv_counts, plan.send_counts, env.ps.ep_group)
+    run.v["d_moe_x"] = M.scatter_add_rows(d_xp, plan.src_row, plan.num_tokens)      # sum over the k copies of a token
+
+
+def b_router_bwd(run):
+    env, p = run.env, run.params
+    x = _use(run, run.acts.pop("moe_x"))
+    probs, topi, gates = run.acts.pop("moe_probs"), run.acts.pop("moe_topi"), run.acts.pop("moe_gates")
+    run.acts.pop("moe_plan")
+    aux_scale = env.cfg.moe_aux_loss_coeff * getattr(env, "grad_scale", 1.0) if env.training else 0.0
+    d_logits = M.router_topk_bwd(run.v.pop("d_gates"), probs, topi, gates, env.cfg.num_experts, aux_scale)
+    dl = d_logits.to(x.dtype)
+    d_x = run.v.pop("d_moe_x")
+    d_x = d_x + G.gemm_nn(dl, p.router_weight).to(d_x.dtype)
+    G.gemm_tn_acc(dl, x, p.router_weight.main_grad)
+    run.v["d_ln2"] = d_x.to(x.dtype)

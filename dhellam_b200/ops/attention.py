@@ -1,0 +1,113 @@
+"""Causal / full multi-head attention with grouped KV heads, explicit forward and backward.
+
+Role of the reference's ``pymha_varlen_fwd`` / ``pymha_varlen_bwd`` (flash-attention 2
+wrappers, csrc/operators/flash_atten.cu:220-434, 479-757) and of the per-ring-step calls in
+dhellam/operators/ring_attn.py:97-144, 315-381.  Operands are strided 4-D views
+``[S, B, heads, d]`` (sequence-first, so a packed QKV buffer is used without copies); the
+softmax statistics are returned as ``lse [B, heads, S]`` in fp32 (natural log).
+
+CUDA tensors run the tcgen05 flash-attention kernels (csrc/attention_sm100.cu); CPU tensors
+run the fp32 reference below.
+"""
+from __future__ import annotations
+
+import math
+from ctypes import c_float, c_int, c_int64, c_void_p
+
+import torch
+
+from .. import kernels as K
+
+
+def _ref_fwd(q, k, v, causal, scale):
+    Sq, B, Hq, d = q.shape
+    Sk, Hk = k.shape[0], k.shape[2]
+    g = Hq // Hk
+    qf = q.float().permute(1, 2, 0, 3)                      # B Hq Sq d
+    kf = k.float().permute(1, 2, 0, 3).repeat_interleave(g, dim=1)
+    vf = v.float().permute(1, 2, 0, 3).repeat_interleave(g, dim=1)
+    s = torch.matmul(qf, kf.transpose(-1, -2)) * scale       # B Hq Sq Sk
+    if causal:
+        # bottom-right aligned: query i sees keys j <= i + (Sk - Sq)
+        i = torch.arange(Sq, device=q.device)[:, None]
+        j = torch.arange(Sk, device=q.device)[None, :]
+        s = s.masked_fill(j > i + (Sk - Sq), float("-inf"))
+    lse = torch.logsumexp(s, dim=-1)                         # B Hq Sq
+    p = torch.exp(s - lse.unsqueeze(-1))
+    o = torch.matmul(p, vf)                                  # B Hq Sq d
+    return o.permute(2, 0, 1, 3).contiguous(), lse, p
+
+
+def attn_fwd(q, k, v, causal: bool = True, scale: float | None = None, sm_budget: int = 0, stream=None):
+    """Returns ``(out [Sq,B,Hq,d], lse [B,Hq,Sq] fp32)``."""
+    d = q.shape[-1]
+    scale = scale if scale is not None else 1.0 / math.sqrt(d)
+    if not q.is_cuda:
+        o, lse, _ = _ref_fwd(q, k, v, causal, scale)
+        return o.to(q.dtype), lse
+    Sq, B, Hq, _ = q.shape
+    Sk, Hk = k.shape[0], k.shape[2]
+    assert q.stride(3) == 1 and k.stride(3) == 1 and v.stride(3) == 1
+    out = torch.empty((Sq, B, Hq, d), dtype=q.dtype, device=q.device)
+    lse = torch.empty((B, Hq, Sq), dtype=torch.float32, device=q.device)
+    fn = K.proto("dh_attn_fwd", [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                 c_int64, c_int64, c_int64, c_int64, c_int64, c_int64, c_int64, c_int64, c_int64,
+                                 c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p])
+    K.check(fn(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr(),
+               q.stride(0), q.stride(1), q.stride(2), k.stride(0), k.stride(1), k.stride(2),
+               v.stride(0), v.stride(1), v.stride(2),
+               B, Hq, Hk, Sq, Sk, d, 1 if causal else 0, scale, sm_budget, K.stream_ptr(stream)), "dh_attn_fwd")
+    return out, lse
+
+
+def attn_bwd(dout, q, k, v, out, lse, causal: bool = True, scale: float | None = None, dq=None, dk=None, dv=None,
+             sm_budget: int = 0, stream=None):
+    """Returns ``(dq, dk, dv)`` shaped like ``q, k, v``.  ``dq/dk/dv`` may be given as strided
+    views (for example into a packed dQKV buffer) and are then written in place, which
+    removes the reference's ``cat(dq, dk, dv)`` (dhellam/core/dstb.py:379-384)."""
+    d = q.shape[-1]
+    scale = scale if scale is not None else 1.0 / math.sqrt(d)
+    if not q.is_cuda:
+        Sq, B, Hq, _ = q.shape
+        Sk, Hk = k.shape[0], k.shape[2]
+        g = Hq // Hk
+        _, _, p = _ref_fwd(q, k, v, causal, scale)
+        do = dout.float().permute(1, 2, 0, 3)                # B Hq Sq d
+        of = out.float().permute(1, 2, 0, 3)
+        qf = q.float().permute(1, 2, 0, 3)
+        kf = k.float().permute(1, 2, 0, 3).repeat_interleave(g, dim=1)
+        vf = v.float().permute(1, 2, 0, 3).repeat_interleave(g, dim=1)
+        dvf = torch.matmul(p.transpose(-1, -2), do)          # B Hq Sk d
+        dp = torch.matmul(do, vf.transpose(-1, -2))
+        delta = (do * of).sum(-1, keepdim=True)
+        ds = p * (dp - delta) * scale
+        dqf = torch.matmul(ds, kf)
+        dkf = torch.matmul(ds.transpose(-1, -2), qf)
+        dkf = dkf.view(B, Hk, g, Sk, d).sum(2)
+        dvf = dvf.view(B, Hk, g, Sk, d).sum(2)
+        rq = dqf.permute(2, 0, 1, 3).to(q.dtype)
+        rk = dkf.permute(2, 0, 1, 3).to(k.dtype)
+        rv = dvf.permute(2, 0, 1, 3).to(v.dtype)
+        if dq is not None:
+            dq.copy_(rq), dk.copy_(rk), dv.copy_(rv)
+            return dq, dk, dv
+        return rq.contiguous(), rk.contiguous(), rv.contiguous()
+    Sq, B, Hq, _ = q.shape
+    Sk, Hk = k.shape[0], k.shape[2]
+    if dq is None:
+        dq = torch.empty((Sq, B, Hq, d), dtype=q.dtype, device=q.device)
+        dk = torch.empty((Sk, B, Hk, d), dtype=q.dtype, device=q.device)
+        dv = torch.empty((Sk, B, Hk, d), dtype=q.dtype, device=q.device)
+    from .attention_native import attn_bwd_native
+    attn_bwd_native(dout, q, k, v, out, lse, dq, dk, dv, causal, scale, sm_budget, stream)
+    return dq, dk, dv
+
+
+def merge_attention_partials(o_a, lse_a, o_b, lse_b):
+    """Combines two attention partial results over disjoint key sets (fp32 math; the
+    reference does this step in fp64, dhellam/operators/ring_attn.py:26-40)."""
+    lse = torch.logaddexp(lse_a, lse_b)                      # B H S
+    wa = torch.exp(lse_a - lse).permute(2, 0, 1).unsqueeze(-1)
+    wb = torch.exp(lse_b - lse).permute(2, 0, 1).unsqueeze(-1)
+    o = o_a.float() * wa + o_b.float() * wb
+    return o.to(o_a.dtype), lse

@@ -1,0 +1,160 @@
+"""Dual-strand executor: runs the forward strand of one micro-batch and the backward
+strand of another through one transformer layer each, following a strategy.
+
+What it keeps from the reference's interpreter (dhellam/core/dstb.py:1133-1281): blocks
+run in order; a block first launches its collectives (``S3``), then the compute ops of the
+strand that does *not* wait for those collectives, then the other strand; deferred weight
+gradients run at their ``*_n`` marker or at the end.  What is different: there is no
+device-wide synchronisation per block (the reference calls ``torch.cuda.synchronize()``
+after every block, dstb.py:1266).  Ordering is carried by CUDA events between three
+streams (forward compute, backward compute, communication), so the host runs ahead of the
+device; on CPU tensors the same code runs synchronously without streams.
+"""
+from __future__ import annotations
+
+import contextlib
+from typing import Dict, List, Optional
+
+import torch
+
+from .ir import BWD, COMM, FWD, LayerProgram, LayerRun
+from .strategy import Block, Strategy, split_budget
+
+
+class StreamSet:
+    """Three CUDA streams (forward compute, backward compute, communication)."""
+
+    def __init__(self, device=None, single_stream: bool = False):
+        self.cuda = device is not None and torch.device(device).type == "cuda"
+        if self.cuda:
+            with torch.cuda.device(device):
+                if single_stream:
+                    s = torch.cuda.current_stream()
+                    self.s1 = self.s2 = self.s3 = s
+                else:
+                    self.s1 = torch.cuda.Stream()
+                    self.s2 = torch.cuda.Stream()
+                    self.s3 = torch.cuda.Stream()
+        else:
+            self.s1 = self.s2 = self.s3 = None
+
+    def lane(self, lane: str):
+        return {"S1": self.s1, "S2": self.s2, "S3": self.s3}[lane]
+
+    def ctx(self, stream):
+        return torch.cuda.stream(stream) if (self.cuda and stream is not None) else contextlib.nullcontext()
+
+    def join_all_into(self, target):
+        """Makes ``target`` wait for everything enqueued so far on the three streams."""
+        if not self.cuda:
+            return
+        for s in {self.s1, self.s2, self.s3}:
+            if s is not target:
+                target.wait_stream(s)
+
+    def fork_from(self, source):
+        if not self.cuda:
+            return
+        for s in {self.s1, self.s2, self.s3}:
+            if s is not source:
+                s.wait_stream(source)
+
+
+class Executor:
+    def __init__(self, program: LayerProgram, strategy: Strategy, streams: StreamSet, profile: bool = False,
+                 trace=None):
+        self.program = program
+        self.strategy = strategy.completed(program)
+        self.strategy.validate(program)
+        self.streams = streams
+        self.profile = profile
+        self.trace = trace                       # optional list collecting (name, lane) launch records
+        self.timings: Dict[str, List] = {}
+        self._events: Dict[str, object] = {}
+        self._lane_of: Dict[str, Dict[str, str]] = {}
+        self._markers = program.marker_targets()
+        for key, blocks in (("pair", self.strategy.dcblocks), ("fwd", self.strategy.fwd_only), ("bwd", self.strategy.bwd_only)):
+            lanes = {}
+            for blk in blocks:
+                for lane, lst in (("S3", blk.s3), ("S1", blk.s1), ("S2", blk.s2)):
+                    for e in lst:
+                        lanes[split_budget(e)[0]] = lane
+            self._lane_of[key] = lanes
+
+    # ------------------------------------------------------------------ public
+    def run(self, fwd_run: Optional[LayerRun], bwd_run: Optional[LayerRun]):
+        if fwd_run is not None and bwd_run is not None:
+            key, blocks = "pair", self.strategy.dcblocks
+        elif fwd_run is not None:
+            key, blocks = "fwd", self.strategy.fwd_only
+        elif bwd_run is not None:
+            key, blocks = "bwd", self.strategy.bwd_only
+        else:
+            return
+        lanes = self._lane_of[key]
+        deferred_names = {self._markers[m] for m in lanes if m in self._markers}
+        pending: Dict[str, tuple] = {}
+        runs = {FWD: fwd_run, BWD: bwd_run}
+
+        def launch(entry: str, lane: str):
+            name, budget = split_budget(entry)
+            if name in self._markers:                       # placement marker of a deferred wgrad
+                target = self._markers[name]
+                if target in pending:
+                    op, run, b = pending.pop(target)
+                    self._exec(op, run, lane, lanes, b or budget)
+                return
+            op = self.program.op(name)
+            run = runs[op.strand]
+            if name in deferred_names:
+                pending[name] = (op, run, budget)
+                return
+            self._exec(op, run, lane, lanes, budget)
+
+        for blk in blocks:
+            for e in blk.s3:
+                launch(e, "S3")
+            fwd_comm = any(self.program.has(split_budget(e)[0]) and self.program.op(split_budget(e)[0]).strand == FWD
+                           for e in blk.s3)
+            order = (("S2", blk.s2), ("S1", blk.s1)) if fwd_comm else (("S1", blk.s1), ("S2", blk.s2))
+            for lane, lst in order:
+                for e in lst:
+                    launch(e, lane)
+        for target, (op, run, b) in list(pending.items()):   # flush what no marker claimed
+            self._exec(op, run, "S2", lanes, b)
+
+    # ------------------------------------------------------------------ internals
+    def _exec(self, op, run: LayerRun, lane: str, lanes: Dict[str, str], budget: int):
+        st = self.streams
+        stream = st.lane(lane)
+        if self.trace is not None:
+            self.trace.append((op.name, lane, run.layer_index, getattr(run.mb, "index", -1)))
+        if st.cuda:
+            for d in op.deps:
+                rec = self._events.get(d)
+                if rec is not None and rec[1] is not stream:   # produced on another stream
+                    stream.wait_event(rec[0])
+        if budget:
+            run.sm_budget[op.name] = budget
+        run.env.cur_stream = stream
+        with st.ctx(stream):
+            if self.profile and st.cuda:
+                e0 = torch.cuda.Event(enable_timing=True)
+                e1 = torch.cuda.Event(enable_timing=True)
+                e0.record(stream)
+                op.fn(run)
+                e1.record(stream)
+                self.timings.setdefault(op.name, []).append((e0, e1))
+            else:
+                op.fn(run)
+        if st.cuda:
+            rec = self._events.get(op.name)
+            ev = rec[0] if rec is not None else torch.cuda.Event()
+            ev.record(stream)
+            self._events[op.name] = (ev, stream)
+
+    def timing_ms(self) -> Dict[str, float]:
+        """Mean device time per op (profile mode); synchronises."""
+        if self.streams.cuda:
+            torch.cuda.synchronize()
+        return {k: sum(a.elapsed_time(b) for a, b in v) / len(v) for k, v in self.timings.items() if v}

@@ -1,0 +1,64 @@
+"""Trainer: builds the folded model, the double-strand engine and the optimizer for one
+rank and runs optimizer steps.  This is the public entry point a user calls
+(``Trainer(...).train_step(batches)``); ``train.py`` wraps it with a command line.
+
+Stands in for the parts of Megatron's ``pretrain`` / ``train_step`` that the reference
+drives through its patch (megatron.patch:764-812): gradient zeroing, the forward-backward
+schedule, gradient finalisation, the optimizer step, and loss / throughput reporting.
+"""
+from __future__ import annotations
+
+import time
+from typing import List, Optional
+
+import torch
+import torch.distributed as dist
+
+from .config import ModelConfig, ParallelConfig, TrainConfig
+from .core.engine import DoubleStrandEngine, Env, MicroBatch
+from .core.modules import DSLLM
+from .optim.adam import MixedPrecisionAdam
+from .parallel import state as PS
+from .sched.strategy import Strategy
+
+
+class Trainer:
+    def __init__(self, cfg: ModelConfig, pcfg: ParallelConfig, train: TrainConfig, device=None, ps=None,
+                 strategy: Optional[Strategy] = None, distributed_optimizer: bool = False, model_init: str = "random",
+                 single_stream: bool = False, profile: bool = False, trace=None):
+        self.cfg, self.pcfg, self.train = cfg, pcfg, train
+        if device is None:
+            device = torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available() else torch.device("cpu")
+        self.device = torch.device(device)
+        self.ps = ps if ps is not None else PS.initialize_model_parallel(pcfg)
+        self.model = DSLLM(cfg, self.ps, train, device=self.device, init=model_init)
+        fused = None
+        if train.fused_comm and self.device.type == "cuda" and self.ps.tp > 1:
+            from .ops.fused_comm import FusedTP
+            fused = FusedTP(self.ps, cfg, train, self.device)
+        self.env = Env(cfg, self.ps, train, self.device, self.model.dtype, fused=fused)
+        if strategy is None and train.schedule_config:
+            strategy = Strategy.load(train.schedule_config)
+        self.engine = DoubleStrandEngine(self.model, self.env, strategy, single_stream=single_stream or not train.dhellam,
+                                         profile=profile, trace=trace)
+        self.optimizer = MixedPrecisionAdam(self.model, train, self.ps, distributed=distributed_optimizer)
+        self.iteration = 0
+        self.last_grad_norm = None
+
+    def train_step(self, mbs: List[MicroBatch], lr: Optional[float] = None):
+        """One optimizer step over ``mbs``.  Returns the mean loss as a tensor on the first
+        pipeline stage (``None`` elsewhere); nothing here synchronises the host."""
+        self.optimizer.zero_grad()
+        losses = self.engine.run_step(mbs)
+        self.last_grad_norm = self.optimizer.step(lr)
+        self.iteration += 1
+        if losses:
+            loss = torch.stack([l.float() for l in losses]).mean()
+            if self.ps.dp > 1:
+                dist.all_reduce(loss, group=self.ps.dp_group)
+                loss = loss / self.ps.dp
+            return loss
+        return None
+
+    def tokens_per_step(self) -> int:
+        return self.train.global_batch_size * self.cfg.seq_length
