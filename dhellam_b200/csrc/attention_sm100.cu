@@ -1,0 +1,653 @@
+// Flash attention forward and backward for sm_100a (head size 128, bf16, grouped KV heads,
+// causal or full, strided [S, B, heads, d] operands so a packed QKV buffer needs no copies).
+//
+// Forward, one CTA per (128 query rows, batch, query head):
+//   warp 0     TMA producer: Q once, then K_j / V_j tiles through 2-stage rings
+//   warp 1     MMA issuer:   S_j = Q K_j^T and O_j = P_j V_j with tcgen05.mma, S and O tiles
+//                            double-buffered in TMEM (4 x 128 columns = all 512)
+//   warps 2-5  softmax:      thread = query row; two passes over S_j in TMEM (row max, then
+//                            exp2 / row sum / bf16 P_j into swizzled shared memory), running
+//                            output kept in registers and rescaled once per block
+//   S_{j+1} and P_{j-1} V_{j-1} run on the tensor cores while the softmax warps work on S_j.
+//
+// Backward, one CTA per (128 keys, batch, KV head); it loops over the query heads of the
+// group and the query blocks that see these keys:
+//   S = Q K^T and dP = dO V^T into TMEM; threads form P = exp2(S - lse) and
+//   dS = P (dP - delta) into ONE swizzled shared-memory image each, which serves both as a
+//   K-major operand (dQ = dS K) and as an MN-major operand (dV += P^T dO, dK += dS^T Q), so
+//   no transposed copies exist anywhere; dK / dV accumulate in TMEM over the whole loop
+//   (this also sums the query heads of a KV group), dQ is added to an fp32 scratch with
+//   vector atomics and converted at the end.
+//
+// Role in the reference: the bundled flash-attention 2 sm80 kernels behind
+// pymha_varlen_fwd / pymha_varlen_bwd (csrc/operators/flash_atten.cu:220-434, 479-757),
+// including its fp32 dq_accum and the separate GQA reduction (:637-652, 742-745).
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <float.h>
+#include <stdint.h>
+
+#include "api.h"
+#include "ptx.cuh"
+#include "tmap.h"
+
+namespace dh {
+namespace attn {
+
+constexpr int BQ = 128, BKV = 128, D = 128;
+constexpr int HALF_BYTES = 128 * 128;        // one [128 rows][64 elems] swizzled box
+constexpr int TILE_BYTES = 2 * HALF_BYTES;   // [128][128] bf16
+constexpr int THREADS = 192;
+constexpr float LOG2E = 1.4426950408889634f;
+
+struct Geometry {
+  int B, Hq, Hk, Sq, Sk, causal;
+  float scale;
+  long long o_s, o_b, o_h;        // output strides (elements)
+  DeviceStatus* status;
+};
+
+// K-major operand descriptor for step kk (16 elements of the contraction) of a tile stored
+// as two [128][64] swizzled boxes.
+__device__ __forceinline__ uint64_t desc_kmajor(uint32_t base, int kk) {
+  return umma_smem_desc(base + (kk >> 2) * HALF_BYTES + (kk & 3) * 32, 16, 1024);
+}
+// MN-major operand descriptor: the contraction runs over the 128 rows of the tile.
+__device__ __forceinline__ uint64_t desc_mnmajor(uint32_t base, int kk) {
+  return umma_smem_desc(base + kk * 2048, HALF_BYTES, 1024);
+}
+// Byte offset of 16-byte chunk c (0..15) of row r in the two-box swizzled image.
+__device__ __forceinline__ uint32_t swz_off(int r, int c) {
+  return (uint32_t)((c >> 3) * HALF_BYTES + r * 128 + (((c & 7) ^ (r & 7)) << 4));
+}
+
+// ======================================================================= forward
+struct FwdCtl {
+  uint64_t q_full;
+  uint64_t k_full[2], k_empty[2], v_full[2], v_empty[2];
+  uint64_t s_full[2], p_ready[2], o_full[2];
+  uint32_t tmem_base;
+  int abort_flag;
+};
+constexpr int FWD_SMEM = TILE_BYTES * 7 + 1024 + 256;   // Q, K x2, V x2, P x2
+
+__global__ void __launch_bounds__(THREADS, 1)
+attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ CUtensorMap tk, const __grid_constant__ CUtensorMap tv,
+                __nv_bfloat16* __restrict__ out, float* __restrict__ lse, const Geometry g) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sQ = smem;
+  uint8_t* sK = smem + TILE_BYTES;
+  uint8_t* sV = smem + 3 * TILE_BYTES;
+  uint8_t* sP = smem + 5 * TILE_BYTES;
+  FwdCtl* ctl = reinterpret_cast<FwdCtl*>(smem + 7 * TILE_BYTES);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nqb = (g.Sq + BQ - 1) / BQ;
+  const int qb = nqb - 1 - (int)blockIdx.x;       // heaviest (latest) query blocks first
+  const int hq = blockIdx.y, b = blockIdx.z;
+  const int hk = hq / (g.Hq / g.Hk);
+  const int off = g.Sk - g.Sq;                    // key j visible to query i iff j <= i + off
+  int nblk = (g.Sk + BKV - 1) / BKV;
+  if (g.causal) {
+    const int last_key = qb * BQ + BQ - 1 + off;
+    nblk = last_key < 0 ? 0 : min(nblk, last_key / BKV + 1);
+  }
+
+  if (threadIdx.x == 0) {
+    mbar_init(&ctl->q_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&ctl->k_full[i], 1); mbar_init(&ctl->k_empty[i], 1);
+      mbar_init(&ctl->v_full[i], 1); mbar_init(&ctl->v_empty[i], 1);
+      mbar_init(&ctl->s_full[i], 1); mbar_init(&ctl->p_ready[i], 4); mbar_init(&ctl->o_full[i], 1);
+    }
+    ctl->abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) { tmem_alloc(&ctl->tmem_base, 512); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = ctl->tmem_base;
+  volatile int* abort_flag = &ctl->abort_flag;
+
+  if (warp == 0) {
+    if (lane == 0 && nblk > 0) {
+      tma_prefetch_desc(&tq); tma_prefetch_desc(&tk); tma_prefetch_desc(&tv);
+      mbar_expect_tx(&ctl->q_full, TILE_BYTES);
+      tma_load_4d(sQ, &tq, &ctl->q_full, 0, hq, b, qb * BQ);
+      tma_load_4d(sQ + HALF_BYTES, &tq, &ctl->q_full, 64, hq, b, qb * BQ);
+      for (int j = 0; j < nblk; ++j) {
+        const int s = j & 1;
+        const uint32_t ph = (j >> 1) & 1;
+        if (!mbar_wait(&ctl->k_empty[s], ph ^ 1, abort_flag, g.status, 400)) break;
+        mbar_expect_tx(&ctl->k_full[s], TILE_BYTES);
+        tma_load_4d(sK + s * TILE_BYTES, &tk, &ctl->k_full[s], 0, hk, b, j * BKV);
+        tma_load_4d(sK + s * TILE_BYTES + HALF_BYTES, &tk, &ctl->k_full[s], 64, hk, b, j * BKV);
+        if (!mbar_wait(&ctl->v_empty[s], ph ^ 1, abort_flag, g.status, 401)) break;
+        mbar_expect_tx(&ctl->v_full[s], TILE_BYTES);
+        tma_load_4d(sV + s * TILE_BYTES, &tv, &ctl->v_full[s], 0, hk, b, j * BKV);
+        tma_load_4d(sV + s * TILE_BYTES + HALF_BYTES, &tv, &ctl->v_full[s], 64, hk, b, j * BKV);
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    if (lane == 0 && nblk > 0) {
+      constexpr uint32_t idesc_s = umma_idesc_bf16(128, 128, 0, 0);
+      constexpr uint32_t idesc_pv = umma_idesc_bf16(128, 128, 0, 1);
+      const uint32_t q_base = smem_u32(sQ);
+      bool ok = mbar_wait(&ctl->q_full, 0, abort_flag, g.status, 410);
+      auto issue_s = [&](int j) -> bool {
+        const int s = j & 1;
+        if (!mbar_wait(&ctl->k_full[s], (j >> 1) & 1, abort_flag, g.status, 411)) return false;
+        tc_fence_after();
+        const uint32_t k_base = smem_u32(sK + s * TILE_BYTES);
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) umma_bf16(tmem + s * 128, desc_kmajor(q_base, kk), desc_kmajor(k_base, kk), idesc_s, kk > 0);
+        umma_commit(&ctl->k_empty[s]);
+        umma_commit(&ctl->s_full[s]);
+        return true;
+      };
+      if (ok) ok = issue_s(0);
+      if (ok && nblk > 1) ok = issue_s(1);
+      for (int j = 0; j < nblk && ok; ++j) {
+        const int s = j & 1;
+        const uint32_t ph = (j >> 1) & 1;
+        if (!mbar_wait(&ctl->p_ready[s], ph, abort_flag, g.status, 412)) break;
+        if (!mbar_wait(&ctl->v_full[s], ph, abort_flag, g.status, 413)) break;
+        tc_fence_after();
+        const uint32_t p_base = smem_u32(sP + s * TILE_BYTES);
+        const uint32_t v_base = smem_u32(sV + s * TILE_BYTES);
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) umma_bf16(tmem + 256 + s * 128, desc_kmajor(p_base, kk), desc_mnmajor(v_base, kk), idesc_pv, kk > 0);
+        umma_commit(&ctl->v_empty[s]);
+        umma_commit(&ctl->o_full[s]);
+        if (j + 2 < nblk) ok = issue_s(j + 2);
+      }
+    }
+    __syncwarp();
+  } else {
+    const int quarter = warp & 3;
+    const int r = quarter * 32 + lane;               // row inside the tile
+    const int qi = qb * BQ + r;                      // global query index
+    const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
+    const float sl2 = g.scale * LOG2E;
+    float m = -FLT_MAX, l = 0.f;
+    float o[D];
+#pragma unroll
+    for (int i = 0; i < D; ++i) o[i] = 0.f;
+    bool ok = nblk > 0;
+    for (int j = 0; j < nblk && ok; ++j) {
+      const int s = j & 1;
+      const uint32_t ph = (j >> 1) & 1;
+      if (!mbar_wait(&ctl->s_full[s], ph, abort_flag, g.status, 420)) { ok = false; break; }
+      tc_fence_after();
+      const uint32_t ts = tmem + s * 128 + lane_base;
+      const int key0 = j * BKV;
+      // which keys of this block may this row see
+      int limit = g.Sk - key0;                                        // keys beyond Sk are padding
+      if (g.causal) limit = min(limit, qi + off - key0 + 1);
+      const bool full_block = limit >= BKV;
+      // pass 1: row maximum
+      float bm = -FLT_MAX;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t v[32];
+        tmem_ld32(ts + c * 32, v);
+        tmem_ld_wait();
+        if (full_block) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) bm = fmaxf(bm, __uint_as_float(v[i]));
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) if (c * 32 + i < limit) bm = fmaxf(bm, __uint_as_float(v[i]));
+        }
+      }
+      const float m_new = fmaxf(m, bm);
+      const float alpha = (m == -FLT_MAX) ? 0.f : exp2f((m - m_new) * sl2);
+      const float mb = (m_new == -FLT_MAX) ? 0.f : m_new * sl2;
+      // pass 2: probabilities -> shared memory (bf16, swizzled), row sum
+      float rs = 0.f;
+      uint8_t* pdst = sP + s * TILE_BYTES;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t v[32];
+        tmem_ld32(ts + c * 32, v);
+        tmem_ld_wait();
+        float p[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          float e = exp2f(__uint_as_float(v[i]) * sl2 - mb);
+          if (!full_block && c * 32 + i >= limit) e = 0.f;
+          p[i] = e;
+          rs += e;
+        }
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) {
+          uint4 u;
+          u.x = pack_bf16x2(p[q4 * 8 + 0], p[q4 * 8 + 1]);
+          u.y = pack_bf16x2(p[q4 * 8 + 2], p[q4 * 8 + 3]);
+          u.z = pack_bf16x2(p[q4 * 8 + 4], p[q4 * 8 + 5]);
+          u.w = pack_bf16x2(p[q4 * 8 + 6], p[q4 * 8 + 7]);
+          *reinterpret_cast<uint4*>(pdst + swz_off(r, c * 4 + q4)) = u;
+        }
+      }
+      l = l * alpha + rs;
+      m = m_new;
+      tc_fence_before();
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&ctl->p_ready[s]);
+      // fold in the previous block's P V (relative to the previous maximum), then rescale
+      if (j > 0) {
+        const int sp = (j - 1) & 1;
+        if (!mbar_wait(&ctl->o_full[sp], ((j - 1) >> 1) & 1, abort_flag, g.status, 421)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t to = tmem + 256 + sp * 128 + lane_base;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          uint32_t v[32];
+          tmem_ld32(to + c * 32, v);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[c * 32 + i] = (o[c * 32 + i] + __uint_as_float(v[i])) * alpha;
+        }
+        tc_fence_before();
+      }
+    }
+    if (ok && nblk > 0) {
+      const int sp = (nblk - 1) & 1;
+      if (mbar_wait(&ctl->o_full[sp], ((nblk - 1) >> 1) & 1, abort_flag, g.status, 422)) {
+        tc_fence_after();
+        const uint32_t to = tmem + 256 + sp * 128 + lane_base;
+        const float inv = l > 0.f ? 1.f / l : 0.f;
+        __nv_bfloat16* orow = out + (long long)qi * g.o_s + (long long)b * g.o_b + (long long)hq * g.o_h;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          uint32_t v[32];
+          tmem_ld32(to + c * 32, v);
+          tmem_ld_wait();
+          if (qi < g.Sq) {
+#pragma unroll
+            for (int q4 = 0; q4 < 4; ++q4) {
+              uint4 u;
+              const int i0 = q4 * 8;
+              u.x = pack_bf16x2((o[c * 32 + i0 + 0] + __uint_as_float(v[i0 + 0])) * inv, (o[c * 32 + i0 + 1] + __uint_as_float(v[i0 + 1])) * inv);
+              u.y = pack_bf16x2((o[c * 32 + i0 + 2] + __uint_as_float(v[i0 + 2])) * inv, (o[c * 32 + i0 + 3] + __uint_as_float(v[i0 + 3])) * inv);
+              u.z = pack_bf16x2((o[c * 32 + i0 + 4] + __uint_as_float(v[i0 + 4])) * inv, (o[c * 32 + i0 + 5] + __uint_as_float(v[i0 + 5])) * inv);
+              u.w = pack_bf16x2((o[c * 32 + i0 + 6] + __uint_as_float(v[i0 + 6])) * inv, (o[c * 32 + i0 + 7] + __uint_as_float(v[i0 + 7])) * inv);
+              reinterpret_cast<uint4*>(orow + c * 32)[q4] = u;
+            }
+          }
+        }
+        if (qi < g.Sq) lse[((long long)b * g.Hq + hq) * g.Sq + qi] = (l > 0.f) ? m * g.scale + logf(l) : -INFINITY;
+      }
+    } else if (nblk == 0 && qi < g.Sq) {
+      __nv_bfloat16* orow = out + (long long)qi * g.o_s + (long long)b * g.o_b + (long long)hq * g.o_h;
+      for (int i = 0; i < D / 8; ++i) reinterpret_cast<uint4*>(orow)[i] = make_uint4(0, 0, 0, 0);
+      lse[((long long)b * g.Hq + hq) * g.Sq + qi] = -INFINITY;
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem, 512); }
+}
+
+// ======================================================================= backward
+// delta[b, h, s] = sum_d dO * O
+__global__ void __launch_bounds__(256) attn_delta_kernel(const __nv_bfloat16* __restrict__ dout, const __nv_bfloat16* __restrict__ out,
+                                                         float* __restrict__ delta, int B, int Hq, int Sq, long long do_s, long long do_b,
+                                                         long long do_h, long long o_s, long long o_b, long long o_h) {
+  const int wid = (blockIdx.x * 256 + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  const int total = B * Hq * Sq;
+  if (wid >= total) return;
+  const int s = wid % Sq, h = (wid / Sq) % Hq, b = wid / (Sq * Hq);
+  const uint2* a = reinterpret_cast<const uint2*>(dout + s * do_s + b * do_b + h * do_h) + lane;
+  const uint2* c = reinterpret_cast<const uint2*>(out + s * o_s + b * o_b + h * o_h) + lane;
+  const uint2 av = *a, cv = *c;
+  float2 a0 = unpack_bf16x2(av.x), a1 = unpack_bf16x2(av.y), c0 = unpack_bf16x2(cv.x), c1 = unpack_bf16x2(cv.y);
+  float v = a0.x * c0.x + a0.y * c0.y + a1.x * c1.x + a1.y * c1.y;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  if (lane == 0) delta[((long long)b * Hq + h) * Sq + s] = v;
+}
+
+// fp32 scratch -> bf16 strided output, times `scale`
+__global__ void __launch_bounds__(256) attn_dq_convert_kernel(const float* __restrict__ acc, __nv_bfloat16* __restrict__ dq, int B, int Hq,
+                                                              int Sq, long long s_s, long long s_b, long long s_h, float scale) {
+  const long long total = (long long)B * Hq * Sq * (D / 8);
+  for (long long i = (long long)blockIdx.x * 256 + threadIdx.x; i < total; i += (long long)gridDim.x * 256) {
+    const int c = (int)(i % (D / 8));
+    const long long row = i / (D / 8);                 // (s, b, h) flattened as [Sq][B][Hq]
+    const int h = (int)(row % Hq);
+    const int b = (int)((row / Hq) % B);
+    const long long s = row / ((long long)Hq * B);
+    const float4 x = reinterpret_cast<const float4*>(acc + row * D)[c * 2];
+    const float4 y = reinterpret_cast<const float4*>(acc + row * D)[c * 2 + 1];
+    uint4 u;
+    u.x = pack_bf16x2(x.x * scale, x.y * scale); u.y = pack_bf16x2(x.z * scale, x.w * scale);
+    u.z = pack_bf16x2(y.x * scale, y.y * scale); u.w = pack_bf16x2(y.z * scale, y.w * scale);
+    reinterpret_cast<uint4*>(dq + s * s_s + b * s_b + h * s_h)[c] = u;
+  }
+}
+
+struct BwdCtl {
+  uint64_t kv_full, qdo_full, qdo_empty, sdp_full, pds_ready, dq_full, dq_read, acc_full;
+  uint32_t tmem_base;
+  int abort_flag;
+};
+constexpr int BWD_SMEM = TILE_BYTES * 6 + 1024 + 256;     // K, V, Q, dO, P, dS
+
+struct BwdGeometry {
+  int B, Hq, Hk, Sq, Sk, causal;
+  float scale;
+  long long dk_s, dk_b, dk_h, dv_s, dv_b, dv_h;
+  DeviceStatus* status;
+};
+
+__global__ void __launch_bounds__(THREADS, 1)
+attn_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ CUtensorMap tk, const __grid_constant__ CUtensorMap tv,
+                const __grid_constant__ CUtensorMap tdo, const float* __restrict__ lse, const float* __restrict__ delta,
+                float* __restrict__ dq_acc, __nv_bfloat16* __restrict__ dk, __nv_bfloat16* __restrict__ dv, const BwdGeometry g) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sK = smem;
+  uint8_t* sV = smem + TILE_BYTES;
+  uint8_t* sQ = smem + 2 * TILE_BYTES;
+  uint8_t* sDO = smem + 3 * TILE_BYTES;
+  uint8_t* sP = smem + 4 * TILE_BYTES;
+  uint8_t* sDS = smem + 5 * TILE_BYTES;
+  BwdCtl* ctl = reinterpret_cast<BwdCtl*>(smem + 6 * TILE_BYTES);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int kb = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
+  const int group = g.Hq / g.Hk;
+  const int off = g.Sk - g.Sq;
+  const int nqb = (g.Sq + BQ - 1) / BQ;
+  // first query block that sees any key of this block: i + off >= kb*BKV
+  int qb0 = 0;
+  if (g.causal) {
+    const int first_q = kb * BKV - off;
+    qb0 = first_q <= 0 ? 0 : first_q / BQ;
+  }
+  const int n_iter = qb0 < nqb ? (nqb - qb0) * group : 0;
+
+  if (threadIdx.x == 0) {
+    mbar_init(&ctl->kv_full, 1); mbar_init(&ctl->qdo_full, 1); mbar_init(&ctl->qdo_empty, 1);
+    mbar_init(&ctl->sdp_full, 1); mbar_init(&ctl->pds_ready, 4); mbar_init(&ctl->dq_full, 1);
+    mbar_init(&ctl->dq_read, 4); mbar_init(&ctl->acc_full, 1);
+    ctl->abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) { tmem_alloc(&ctl->tmem_base, 512); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = ctl->tmem_base;
+  volatile int* abort_flag = &ctl->abort_flag;
+  // TMEM columns: [0,128) S then dQ, [128,256) dP, [256,384) dV, [384,512) dK
+
+  if (warp == 0) {
+    if (lane == 0 && n_iter > 0) {
+      tma_prefetch_desc(&tq); tma_prefetch_desc(&tk); tma_prefetch_desc(&tv); tma_prefetch_desc(&tdo);
+      mbar_expect_tx(&ctl->kv_full, 2 * TILE_BYTES);
+      tma_load_4d(sK, &tk, &ctl->kv_full, 0, hk, b, kb * BKV);
+      tma_load_4d(sK + HALF_BYTES, &tk, &ctl->kv_full, 64, hk, b, kb * BKV);
+      tma_load_4d(sV, &tv, &ctl->kv_full, 0, hk, b, kb * BKV);
+      tma_load_4d(sV + HALF_BYTES, &tv, &ctl->kv_full, 64, hk, b, kb * BKV);
+      for (int it = 0; it < n_iter; ++it) {
+        const int hq = hk * group + it % group;
+        const int qb = qb0 + it / group;
+        if (!mbar_wait(&ctl->qdo_empty, (it & 1) ^ 1, abort_flag, g.status, 500)) break;
+        mbar_expect_tx(&ctl->qdo_full, 2 * TILE_BYTES);
+        tma_load_4d(sQ, &tq, &ctl->qdo_full, 0, hq, b, qb * BQ);
+        tma_load_4d(sQ + HALF_BYTES, &tq, &ctl->qdo_full, 64, hq, b, qb * BQ);
+        tma_load_4d(sDO, &tdo, &ctl->qdo_full, 0, hq, b, qb * BQ);
+        tma_load_4d(sDO + HALF_BYTES, &tdo, &ctl->qdo_full, 64, hq, b, qb * BQ);
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    if (lane == 0 && n_iter > 0) {
+      constexpr uint32_t id_kk = umma_idesc_bf16(128, 128, 0, 0);   // S, dP: both operands K-major
+      constexpr uint32_t id_mm = umma_idesc_bf16(128, 128, 1, 1);   // dV, dK: both operands MN-major
+      constexpr uint32_t id_km = umma_idesc_bf16(128, 128, 0, 1);   // dQ: dS K-major, K MN-major
+      const uint32_t k_base = smem_u32(sK), v_base = smem_u32(sV), q_base = smem_u32(sQ), do_base = smem_u32(sDO);
+      const uint32_t p_base = smem_u32(sP), ds_base = smem_u32(sDS);
+      bool ok = mbar_wait(&ctl->kv_full, 0, abort_flag, g.status, 510);
+      for (int it = 0; it < n_iter && ok; ++it) {
+        const uint32_t ph = it & 1;
+        if (!mbar_wait(&ctl->qdo_full, ph, abort_flag, g.status, 511)) break;
+        // the S columns are reused for dQ: wait until the threads have drained the previous dQ
+        if (!mbar_wait(&ctl->dq_read, ph ^ 1, abort_flag, g.status, 512)) break;
+        tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) umma_bf16(tmem + 0, desc_kmajor(q_base, kk), desc_kmajor(k_base, kk), id_kk, kk > 0);
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) umma_bf16(tmem + 128, desc_kmajor(do_base, kk), desc_kmajor(v_base, kk), id_kk, kk > 0);
+        umma_commit(&ctl->sdp_full);
+        if (!mbar_wait(&ctl->pds_ready, ph, abort_flag, g.status, 513)) break;
+        tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) umma_bf16(tmem + 256, desc_mnmajor(p_base, kk), desc_mnmajor(do_base, kk), id_mm, (it | kk) != 0);
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) umma_bf16(tmem + 384, desc_mnmajor(ds_base, kk), desc_mnmajor(q_base, kk), id_mm, (it | kk) != 0);
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) umma_bf16(tmem + 0, desc_kmajor(ds_base, kk), desc_mnmajor(k_base, kk), id_km, kk > 0);
+        umma_commit(&ctl->qdo_empty);
+        umma_commit(&ctl->dq_full);
+      }
+      if (ok) umma_commit(&ctl->acc_full);
+    }
+    __syncwarp();
+  } else {
+    const int quarter = warp & 3;
+    const int r = quarter * 32 + lane;
+    const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
+    const float sl2 = g.scale * LOG2E;
+    bool ok = n_iter > 0;
+    for (int it = 0; it < n_iter && ok; ++it) {
+      const uint32_t ph = it & 1;
+      const int hq = hk * group + it % group;
+      const int qb = qb0 + it / group;
+      const int qi = qb * BQ + r;
+      const bool row_ok = qi < g.Sq;
+      const long long stat = ((long long)b * g.Hq + hq) * g.Sq + qi;
+      const float L = row_ok ? lse[stat] * LOG2E : 0.f;
+      const float dl = row_ok ? delta[stat] : 0.f;
+      if (!mbar_wait(&ctl->sdp_full, ph, abort_flag, g.status, 520)) { ok = false; break; }
+      tc_fence_after();
+      const int key0 = kb * BKV;
+      int limit = g.Sk - key0;
+      if (g.causal) limit = min(limit, qi + off - key0 + 1);
+      if (!row_ok) limit = 0;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t sv[32], dpv[32];
+        tmem_ld32(tmem + 0 + lane_base + c * 32, sv);
+        tmem_ld32(tmem + 128 + lane_base + c * 32, dpv);
+        tmem_ld_wait();
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) {
+          float p[8], ds[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int col = c * 32 + q4 * 8 + i;
+            float pe = exp2f(__uint_as_float(sv[q4 * 8 + i]) * sl2 - L);
+            if (col >= limit) pe = 0.f;
+            p[i] = pe;
+            ds[i] = pe * (__uint_as_float(dpv[q4 * 8 + i]) - dl);
+          }
+          uint4 up, ud;
+          up.x = pack_bf16x2(p[0], p[1]); up.y = pack_bf16x2(p[2], p[3]); up.z = pack_bf16x2(p[4], p[5]); up.w = pack_bf16x2(p[6], p[7]);
+          ud.x = pack_bf16x2(ds[0], ds[1]); ud.y = pack_bf16x2(ds[2], ds[3]); ud.z = pack_bf16x2(ds[4], ds[5]); ud.w = pack_bf16x2(ds[6], ds[7]);
+          const uint32_t o = swz_off(r, c * 4 + q4);
+          *reinterpret_cast<uint4*>(sP + o) = up;
+          *reinterpret_cast<uint4*>(sDS + o) = ud;
+        }
+      }
+      tc_fence_before();
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&ctl->pds_ready);
+      // dQ tile of this (query block, head): add into the fp32 scratch
+      if (!mbar_wait(&ctl->dq_full, ph, abort_flag, g.status, 521)) { ok = false; break; }
+      tc_fence_after();
+      float* dst = dq_acc + (((long long)qi * g.B + b) * g.Hq + hq) * D;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t v[32];
+        tmem_ld32(tmem + 0 + lane_base + c * 32, v);
+        tmem_ld_wait();
+        if (row_ok) {
+#pragma unroll
+          for (int q4 = 0; q4 < 8; ++q4)
+            atomicAdd(reinterpret_cast<float4*>(dst + c * 32) + q4,
+                      make_float4(__uint_as_float(v[q4 * 4]), __uint_as_float(v[q4 * 4 + 1]), __uint_as_float(v[q4 * 4 + 2]),
+                                  __uint_as_float(v[q4 * 4 + 3])));
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&ctl->dq_read);
+    }
+    // dK (times scale) and dV of this key block
+    const int kj = kb * BKV + r;
+    if (ok && n_iter > 0) {
+      if (mbar_wait(&ctl->acc_full, 0, abort_flag, g.status, 522)) {
+        tc_fence_after();
+        __nv_bfloat16* dvr = dv + (long long)kj * g.dv_s + (long long)b * g.dv_b + (long long)hk * g.dv_h;
+        __nv_bfloat16* dkr = dk + (long long)kj * g.dk_s + (long long)b * g.dk_b + (long long)hk * g.dk_h;
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          uint32_t a[32], bb[32];
+          tmem_ld32(tmem + 256 + lane_base + c * 32, a);
+          tmem_ld32(tmem + 384 + lane_base + c * 32, bb);
+          tmem_ld_wait();
+          if (kj < g.Sk) {
+#pragma unroll
+            for (int q4 = 0; q4 < 4; ++q4) {
+              uint4 u, w;
+              const int i0 = q4 * 8;
+              u.x = pack_bf16x2(__uint_as_float(a[i0]), __uint_as_float(a[i0 + 1]));
+              u.y = pack_bf16x2(__uint_as_float(a[i0 + 2]), __uint_as_float(a[i0 + 3]));
+              u.z = pack_bf16x2(__uint_as_float(a[i0 + 4]), __uint_as_float(a[i0 + 5]));
+              u.w = pack_bf16x2(__uint_as_float(a[i0 + 6]), __uint_as_float(a[i0 + 7]));
+              w.x = pack_bf16x2(__uint_as_float(bb[i0]) * g.scale, __uint_as_float(bb[i0 + 1]) * g.scale);
+              w.y = pack_bf16x2(__uint_as_float(bb[i0 + 2]) * g.scale, __uint_as_float(bb[i0 + 3]) * g.scale);
+              w.z = pack_bf16x2(__uint_as_float(bb[i0 + 4]) * g.scale, __uint_as_float(bb[i0 + 5]) * g.scale);
+              w.w = pack_bf16x2(__uint_as_float(bb[i0 + 6]) * g.scale, __uint_as_float(bb[i0 + 7]) * g.scale);
+              reinterpret_cast<uint4*>(dvr + c * 32)[q4] = u;
+              reinterpret_cast<uint4*>(dkr + c * 32)[q4] = w;
+            }
+          }
+        }
+      }
+    } else if (n_iter == 0 && kj < g.Sk) {
+      __nv_bfloat16* dvr = dv + (long long)kj * g.dv_s + (long long)b * g.dv_b + (long long)hk * g.dv_h;
+      __nv_bfloat16* dkr = dk + (long long)kj * g.dk_s + (long long)b * g.dk_b + (long long)hk * g.dk_h;
+      for (int i = 0; i < D / 8; ++i) {
+        reinterpret_cast<uint4*>(dvr)[i] = make_uint4(0, 0, 0, 0);
+        reinterpret_cast<uint4*>(dkr)[i] = make_uint4(0, 0, 0, 0);
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem, 512); }
+}
+
+static const CUtensorMap* tensor_map_sbhd(const void* p, int S, int B, int H, long long s_s, long long s_b, long long s_h) {
+  const uint64_t dims[4] = {(uint64_t)D, (uint64_t)H, (uint64_t)B, (uint64_t)S};
+  const uint64_t st[3] = {(uint64_t)s_h * 2, (uint64_t)s_b * 2, (uint64_t)s_s * 2};
+  const uint32_t box[4] = {64, 1, 1, 128};
+  return get_tmap_4d(p, 2, dims, st, box, true);
+}
+
+}  // namespace attn
+}  // namespace dh
+
+using namespace dh;
+using namespace dh::attn;
+
+extern "C" {
+
+int dh_attn_fwd(const void* q, const void* k, const void* v, void* out, void* lse, int64_t q_s, int64_t q_b, int64_t q_h, int64_t k_s,
+                int64_t k_b, int64_t k_h, int64_t v_s, int64_t v_b, int64_t v_h, int B, int Hq, int Hk, int Sq, int Sk, int d, int causal,
+                float scale, int sm_budget, cudaStream_t stream) {
+  (void)sm_budget;
+  if (d != D) { set_last_error("dh_attn_fwd: head size %d is not supported (128 only)", d); return (int)cudaErrorInvalidValue; }
+  if (Hq % Hk != 0) { set_last_error("dh_attn_fwd: query heads must be a multiple of KV heads"); return (int)cudaErrorInvalidValue; }
+  if (B <= 0 || Sq <= 0 || Sk <= 0) return 0;
+  const CUtensorMap* tq = tensor_map_sbhd(q, Sq, B, Hq, q_s, q_b, q_h);
+  const CUtensorMap* tk = tensor_map_sbhd(k, Sk, B, Hk, k_s, k_b, k_h);
+  const CUtensorMap* tv = tensor_map_sbhd(v, Sk, B, Hk, v_s, v_b, v_h);
+  if (!tq || !tk || !tv) return (int)cudaErrorInvalidValue;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, FWD_SMEM);
+    if (e != cudaSuccess) { set_last_error("dh_attn_fwd: shared memory opt-in failed: %s", cudaGetErrorString(e)); return (int)e; }
+    configured = true;
+  }
+  Geometry g;
+  g.B = B; g.Hq = Hq; g.Hk = Hk; g.Sq = Sq; g.Sk = Sk; g.causal = causal; g.scale = scale;
+  g.o_h = D; g.o_b = (long long)Hq * D; g.o_s = (long long)B * Hq * D;
+  g.status = reinterpret_cast<DeviceStatus*>(dh_status_device_ptr());
+  dim3 grid((Sq + BQ - 1) / BQ, Hq, B);
+  attn_fwd_kernel<<<grid, THREADS, FWD_SMEM, stream>>>(*tq, *tk, *tv, (__nv_bfloat16*)out, (float*)lse, g);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) set_last_error("dh_attn_fwd launch failed: %s", cudaGetErrorString(e));
+  return (int)e;
+}
+
+// Scratch layout: delta [B*Hq*Sq] fp32 followed (256-byte aligned) by dq_acc [Sq*B*Hq*128] fp32.
+int64_t dh_attn_bwd_scratch_bytes(int B, int Hq, int Sq) {
+  const int64_t delta = ((int64_t)B * Hq * Sq * 4 + 255) / 256 * 256;
+  return delta + (int64_t)Sq * B * Hq * D * 4;
+}
+
+int dh_attn_bwd(const void* dout, const void* q, const void* k, const void* v, const void* out, const void* lse, void* dq, void* dk,
+                void* dv, void* scratch, const int64_t* strides /* 8 tensors x (s,b,h): do,q,k,v,o,dq,dk,dv */, int B, int Hq, int Hk,
+                int Sq, int Sk, int d, int causal, float scale, int sm_budget, cudaStream_t stream) {
+  (void)sm_budget;
+  if (d != D) { set_last_error("dh_attn_bwd: head size %d is not supported (128 only)", d); return (int)cudaErrorInvalidValue; }
+  if (Hq % Hk != 0) { set_last_error("dh_attn_bwd: query heads must be a multiple of KV heads"); return (int)cudaErrorInvalidValue; }
+  if (B <= 0 || Sq <= 0 || Sk <= 0) return 0;
+  const int64_t* sdo = strides; const int64_t* sq = strides + 3; const int64_t* sk = strides + 6; const int64_t* sv = strides + 9;
+  const int64_t* so = strides + 12; const int64_t* sdq = strides + 15; const int64_t* sdk = strides + 18; const int64_t* sdv = strides + 21;
+  const CUtensorMap* tq = tensor_map_sbhd(q, Sq, B, Hq, sq[0], sq[1], sq[2]);
+  const CUtensorMap* tk = tensor_map_sbhd(k, Sk, B, Hk, sk[0], sk[1], sk[2]);
+  const CUtensorMap* tv = tensor_map_sbhd(v, Sk, B, Hk, sv[0], sv[1], sv[2]);
+  const CUtensorMap* tdo = tensor_map_sbhd(dout, Sq, B, Hq, sdo[0], sdo[1], sdo[2]);
+  if (!tq || !tk || !tv || !tdo) return (int)cudaErrorInvalidValue;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(attn_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, BWD_SMEM);
+    if (e != cudaSuccess) { set_last_error("dh_attn_bwd: shared memory opt-in failed: %s", cudaGetErrorString(e)); return (int)e; }
+    configured = true;
+  }
+  float* delta = reinterpret_cast<float*>(scratch);
+  const int64_t delta_bytes = ((int64_t)B * Hq * Sq * 4 + 255) / 256 * 256;
+  float* dq_acc = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(scratch) + delta_bytes);
+  cudaError_t e = cudaMemsetAsync(dq_acc, 0, (size_t)Sq * B * Hq * D * 4, stream);
+  if (e != cudaSuccess) { set_last_error("dh_attn_bwd: memset failed: %s", cudaGetErrorString(e)); return (int)e; }
+  const int rows = B * Hq * Sq;
+  attn_delta_kernel<<<(rows * 32 + 255) / 256, 256, 0, stream>>>((const __nv_bfloat16*)dout, (const __nv_bfloat16*)out, delta, B, Hq, Sq,
+                                                                 sdo[0], sdo[1], sdo[2], so[0], so[1], so[2]);
+  BwdGeometry g;
+  g.B = B; g.Hq = Hq; g.Hk = Hk; g.Sq = Sq; g.Sk = Sk; g.causal = causal; g.scale = scale;
+  g.dk_s = sdk[0]; g.dk_b = sdk[1]; g.dk_h = sdk[2]; g.dv_s = sdv[0]; g.dv_b = sdv[1]; g.dv_h = sdv[2];
+  g.status = reinterpret_cast<DeviceStatus*>(dh_status_device_ptr());
+  dim3 grid((Sk + BKV - 1) / BKV, Hk, B);
+  attn_bwd_kernel<<<grid, THREADS, BWD_SMEM, stream>>>(*tq, *tk, *tv, *tdo, (const float*)lse, delta, dq_acc, (__nv_bfloat16*)dk,
+                                                       (__nv_bfloat16*)dv, g);
+  const long long total = (long long)rows * (D / 8);
+  int cgrid = (int)((total + 255) / 256);
+  if (cgrid > dh_sm_count() * 16) cgrid = dh_sm_count() * 16;
+  attn_dq_convert_kernel<<<cgrid, 256, 0, stream>>>(dq_acc, (__nv_bfloat16*)dq, B, Hq, Sq, sdq[0], sdq[1], sdq[2], scale);
+  e = cudaGetLastError();
+  if (e != cudaSuccess) set_last_error("dh_attn_bwd launch failed: %s", cudaGetErrorString(e));
+  return (int)e;
+}
+
+}  // extern "C"

@@ -125,6 +125,23 @@ const CUtensorMap* get_tmap_3d(const void* base, int elem_bytes, uint64_t d0, ui
   return encode_cached(key, dtype_of(elem_bytes), 3, const_cast<void*>(base), dims, strides, box, swizzle128);
 }
 
+const CUtensorMap* get_tmap_4d(const void* base, int elem_bytes, const uint64_t dims[4], const uint64_t strides_bytes[3],
+                               const uint32_t box[4], bool swizzle128) {
+  if ((reinterpret_cast<uintptr_t>(base) & 15) != 0 || (strides_bytes[0] & 15) != 0 || (strides_bytes[1] & 15) != 0 ||
+      (strides_bytes[2] & 15) != 0) {
+    set_last_error("TMA operand must be 16-byte aligned with 16-byte multiple strides (base %p)", base);
+    return nullptr;
+  }
+  TmapKey key = {{(uint64_t)(uintptr_t)base, dims[0] | (dims[1] << 32), dims[2] | (dims[3] << 32), strides_bytes[0],
+                  strides_bytes[1], strides_bytes[2],
+                  ((uint64_t)box[0] << 48) | ((uint64_t)box[1] << 32) | ((uint64_t)box[2] << 16) | box[3],
+                  (uint64_t)elem_bytes | ((uint64_t)swizzle128 << 8) | (4ull << 16)}};
+  cuuint64_t d[4] = {dims[0], dims[1], dims[2], dims[3]};
+  cuuint64_t st[3] = {strides_bytes[0], strides_bytes[1], strides_bytes[2]};
+  cuuint32_t bx[4] = {box[0], box[1], box[2], box[3]};
+  return encode_cached(key, dtype_of(elem_bytes), 4, const_cast<void*>(base), d, st, bx, swizzle128);
+}
+
 }  // namespace dh
 
 extern "C" {
@@ -165,3 +182,20 @@ int dh_sm_count() {
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------------------
+// Bounded-wait self test: one thread waits (for at most `budget_cycles`) on a flag that the
+// caller controls; used to check that a wait which cannot succeed returns an error status
+// instead of hanging.
+// ---------------------------------------------------------------------------
+namespace dh {
+__global__ void probe_flag_wait_kernel(const uint32_t* flag, uint32_t expect, long long budget, DeviceStatus* st) {
+  if (threadIdx.x == 0 && blockIdx.x == 0) flag_wait_geq_gpu(flag, expect, budget, st, 900);
+}
+}  // namespace dh
+
+extern "C" int dh_probe_flag_wait(const void* flag, uint32_t expect, long long budget_cycles, cudaStream_t s) {
+  dh::probe_flag_wait_kernel<<<1, 32, 0, s>>>(reinterpret_cast<const uint32_t*>(flag), expect, budget_cycles,
+                                              reinterpret_cast<dh::DeviceStatus*>(dh_status_device_ptr()));
+  return (int)cudaGetLastError();
+}

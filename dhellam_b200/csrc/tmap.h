@@ -19,6 +19,12 @@ const CUtensorMap* get_tmap_3d(const void* base, int elem_bytes, uint64_t d0, ui
                                uint64_t stride1_bytes, uint64_t stride2_bytes, uint32_t b0, uint32_t b1, uint32_t b2,
                                bool swizzle128);
 
+// 4-D variant: dims/box innermost first, strides (bytes) for dimensions 1..3.
+const CUtensorMap* get_tmap_4d(const void* base, int elem_bytes, const uint64_t dims[4], const uint64_t strides_bytes[3],
+                               const uint32_t box[4], bool swizzle128);
+
 void set_last_error(const char* fmt, ...);
 
 }  // namespace dh
+
+inline void set_last_error_c(const char* what, const char* msg) { dh::set_last_error("%s: %s", what, msg); }

@@ -71,12 +71,19 @@ def attn_bwd(dout, q, k, v, out, lse, causal: bool = True, scale: float | None =
         Sq, B, Hq, _ = q.shape
         Sk, Hk = k.shape[0], k.shape[2]
         g = Hq // Hk
-        _, _, p = _ref_fwd(q, k, v, causal, scale)
         do = dout.float().permute(1, 2, 0, 3)                # B Hq Sq d
         of = out.float().permute(1, 2, 0, 3)
         qf = q.float().permute(1, 2, 0, 3)
         kf = k.float().permute(1, 2, 0, 3).repeat_interleave(g, dim=1)
         vf = v.float().permute(1, 2, 0, 3).repeat_interleave(g, dim=1)
+        # probabilities are rebuilt from the GIVEN statistics, which for a ring step are
+        # those of the whole key set, not of this block alone
+        s = torch.matmul(qf, kf.transpose(-1, -2)) * scale
+        if causal:
+            i = torch.arange(Sq, device=q.device)[:, None]
+            j = torch.arange(Sk, device=q.device)[None, :]
+            s = s.masked_fill(j > i + (Sk - Sq), float("-inf"))
+        p = torch.exp(s - lse.unsqueeze(-1))
         dvf = torch.matmul(p.transpose(-1, -2), do)          # B Hq Sk d
         dp = torch.matmul(do, vf.transpose(-1, -2))
         delta = (do * of).sum(-1, keepdim=True)

@@ -13,13 +13,15 @@ import torch.distributed as dist
 
 
 def group_size(group) -> int:
-    if group is None and not dist.is_initialized():
+    """Size of ``group``.  In this framework ``None`` means "no group" (a parallel axis of
+    size one), never the world group; pass ``dist.group.WORLD`` for that."""
+    if group is None:
         return 1
     return dist.get_world_size(group)
 
 
 def group_rank(group) -> int:
-    if group is None and not dist.is_initialized():
+    if group is None:
         return 0
     return dist.get_rank(group)
 

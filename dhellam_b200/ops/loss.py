@@ -52,8 +52,10 @@ def vocab_parallel_ce_fwd(logits, labels, vocab_start: int = 0, group=None, stre
     stats = ce_local_stats(logits, labels, vocab_start, stream=stream)
     ws = group_size(group)
     if ws > 1:
-        gathered = torch.empty((ws,) + tuple(stats.shape), dtype=stats.dtype, device=stats.device)
-        dist.all_gather_into_tensor(gathered, stats, group=group)
+        T = stats.shape[0]
+        flat = torch.empty((ws * T, 3), dtype=stats.dtype, device=stats.device)
+        dist.all_gather_into_tensor(flat, stats, group=group)
+        gathered = flat.view(ws, T, 3)
     else:
         gathered = stats.unsqueeze(0)
     return ce_combine_stats(gathered)
