@@ -69,7 +69,17 @@ def proto(name: str, argtypes, restype=c_int):
     return fn
 
 
+_LAUNCHES = 0
+
+
+def launch_count() -> int:
+    """Number of calls into the kernel library so far (each launches at least one kernel)."""
+    return _LAUNCHES
+
+
 def check(rc: int, what: str = "kernel"):
+    global _LAUNCHES
+    _LAUNCHES += 1
     if rc != 0:
         msg = lib().dh_last_error_string().decode()
         raise KernelError(f"{what} failed (code {rc}): {msg}")

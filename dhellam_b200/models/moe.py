@@ -174,6 +174,17 @@ def b_router_bwd(run):
     d_logits = M.router_topk_bwd(run.v.pop("d_gates"), probs, topi, gates, env.cfg.num_experts, aux_scale)
     dl = d_logits.to(x.dtype)
     d_x = run.v.pop("d_moe_x")
-    d_x = d_x + G.gemm_nn(dl, p.router_weight).to(d_x.dtype)
-    G.gemm_tn_acc(dl, x, p.router_weight.main_grad)
+    E = dl.shape[1]
+    if dl.is_cuda and E % 8 != 0:
+        # the tensor-core GEMM needs 16-byte rows: pad the expert dimension with zeros
+        pad = (-E) % 8
+        dl = torch.nn.functional.pad(dl, (0, pad))
+        w_pad = torch.nn.functional.pad(p.router_weight, (0, 0, 0, pad))
+        g_pad = torch.zeros((E + pad, x.shape[1]), dtype=torch.float32, device=x.device)
+        d_x = d_x + G.gemm_nn(dl, w_pad).to(d_x.dtype)
+        G.gemm_tn_acc(dl, x, g_pad, accumulate=False)
+        p.router_weight.main_grad.add_(g_pad[:E])
+    else:
+        d_x = d_x + G.gemm_nn(dl, p.router_weight).to(d_x.dtype)
+        G.gemm_tn_acc(dl, x, p.router_weight.main_grad)
     run.v["d_ln2"] = d_x.to(x.dtype)
