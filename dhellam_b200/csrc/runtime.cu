@@ -199,3 +199,29 @@ extern "C" int dh_probe_flag_wait(const void* flag, uint32_t expect, long long b
                                               reinterpret_cast<dh::DeviceStatus*>(dh_status_device_ptr()));
   return (int)cudaGetLastError();
 }
+
+// Encodes a 4-D tensor map straight into caller-provided storage (no cache entry, no heap).
+namespace dh {
+bool encode_tmap_4d_into(CUtensorMap* out, const void* base, int elem_bytes, const uint64_t dims[4], const uint64_t strides_bytes[3],
+                         const uint32_t box[4], bool swizzle128) {
+  if ((reinterpret_cast<uintptr_t>(base) & 15) != 0 || (strides_bytes[0] & 15) != 0 || (strides_bytes[1] & 15) != 0 ||
+      (strides_bytes[2] & 15) != 0) {
+    set_last_error("TMA operand must be 16-byte aligned with 16-byte multiple strides (base %p)", base);
+    return false;
+  }
+  EncodeTiledFn enc = get_encode();
+  if (!enc) return false;
+  cuuint64_t d[4] = {dims[0], dims[1], dims[2], dims[3]};
+  cuuint64_t st[3] = {strides_bytes[0], strides_bytes[1], strides_bytes[2]};
+  cuuint32_t bx[4] = {box[0], box[1], box[2], box[3]};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = enc(out, dtype_of(elem_bytes), 4, const_cast<void*>(base), d, st, bx, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    set_last_error("cuTensorMapEncodeTiled failed: code %d", (int)r);
+    return false;
+  }
+  return true;
+}
+}  // namespace dh
