@@ -651,3 +651,85 @@ int dh_attn_bwd(const void* dout, const void* q, const void* k, const void* v, c
 }
 
 }  // extern "C"
+
+// =========================================================================== no-allocation entry
+#include "attn_noalloc.h"
+
+namespace dh {
+bool encode_tmap_4d_into(CUtensorMap* out, const void* base, int elem_bytes, const uint64_t dims[4], const uint64_t strides_bytes[3],
+                         const uint32_t box[4], bool swizzle128);
+namespace attn {
+
+// Scratch of the no-allocation entry point.  In host code this name is only a handle for
+// cudaGetSymbolAddress; kernels receive the resolved device address.
+static __device__ __align__(256) unsigned char g_noalloc_scratch[DH_ATTN_NOALLOC_SCRATCH_BYTES];
+
+constexpr int kNoallocMaxDev = 32;
+static void* g_noalloc_addr[kNoallocMaxDev] = {nullptr};
+static bool g_noalloc_ready[kNoallocMaxDev] = {false};
+
+static bool map_sbhd_into(CUtensorMap* m, const void* p, int S, int B, int H, const int64_t* st) {
+  const uint64_t dims[4] = {(uint64_t)D, (uint64_t)H, (uint64_t)B, (uint64_t)S};
+  const uint64_t sb[3] = {(uint64_t)st[2] * 2, (uint64_t)st[1] * 2, (uint64_t)st[0] * 2};
+  const uint32_t box[4] = {64, 1, 1, 128};
+  return encode_tmap_4d_into(m, p, 2, dims, sb, box, true);
+}
+
+}  // namespace attn
+}  // namespace dh
+
+extern "C" int dh_attn_bwd_noalloc(const void* dout, const void* q, const void* k, const void* v, const void* out, const void* lse,
+                                   void* dq, void* dk, void* dv, const int64_t* strides, int B, int Hq, int Hk, int Sq, int Sk, int d,
+                                   int causal, float scale, cudaStream_t stream) {
+  if (d != D) { set_last_error("dh_attn_bwd_noalloc: head size %d is not supported (128 only)", d); return (int)cudaErrorInvalidValue; }
+  if (Hk <= 0 || Hq % Hk != 0) { set_last_error("dh_attn_bwd_noalloc: query heads must be a multiple of KV heads"); return (int)cudaErrorInvalidValue; }
+  if (B <= 0 || Sq <= 0 || Sk <= 0) return 0;
+  const int64_t rows = (int64_t)B * Hq * Sq;
+  const int64_t delta_bytes = (rows * 4 + 255) / 256 * 256;
+  const int64_t need = delta_bytes + rows * D * 4;
+  if (need > (int64_t)DH_ATTN_NOALLOC_SCRATCH_BYTES) {
+    set_last_error("dh_attn_bwd_noalloc: B*Hq*Sq = %lld rows need %lld bytes of scratch, the built-in array holds %u; "
+                   "use dh_attn_bwd with a caller-provided buffer", (long long)rows, (long long)need, DH_ATTN_NOALLOC_SCRATCH_BYTES);
+    return (int)cudaErrorInvalidValue;
+  }
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= kNoallocMaxDev) { set_last_error("dh_attn_bwd_noalloc: no usable current device"); return (int)cudaErrorInvalidDevice; }
+  if (!g_noalloc_ready[dev]) {
+    // once per device, with that device current: resolve the array's device address
+    void* ptr = nullptr;
+    e = cudaGetSymbolAddress(&ptr, g_noalloc_scratch);
+    if (e != cudaSuccess || ptr == nullptr) { set_last_error("dh_attn_bwd_noalloc: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e)); return (int)e; }
+    e = cudaFuncSetAttribute(attn_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, BWD_SMEM);
+    if (e != cudaSuccess) { set_last_error("dh_attn_bwd_noalloc: shared memory opt-in failed: %s", cudaGetErrorString(e)); return (int)e; }
+    g_noalloc_addr[dev] = ptr;
+    g_noalloc_ready[dev] = true;
+  }
+  const int64_t* sdo = strides; const int64_t* sq = strides + 3; const int64_t* sk = strides + 6; const int64_t* sv = strides + 9;
+  const int64_t* so = strides + 12; const int64_t* sdq = strides + 15; const int64_t* sdk = strides + 18; const int64_t* sdv = strides + 21;
+  CUtensorMap tq, tk, tv, tdo;
+  if (!map_sbhd_into(&tq, q, Sq, B, Hq, sq) || !map_sbhd_into(&tk, k, Sk, B, Hk, sk) || !map_sbhd_into(&tv, v, Sk, B, Hk, sv) ||
+      !map_sbhd_into(&tdo, dout, Sq, B, Hq, sdo))
+    return (int)cudaErrorInvalidValue;
+  unsigned char* base = reinterpret_cast<unsigned char*>(g_noalloc_addr[dev]);
+  float* delta = reinterpret_cast<float*>(base);
+  float* dq_acc = reinterpret_cast<float*>(base + delta_bytes);
+  e = cudaMemsetAsync(dq_acc, 0, (size_t)rows * D * 4, stream);           // the accumulator must start at zero
+  if (e != cudaSuccess) { set_last_error("dh_attn_bwd_noalloc: memset failed: %s", cudaGetErrorString(e)); return (int)e; }
+  attn_delta_kernel<<<(unsigned)((rows * 32 + 255) / 256), 256, 0, stream>>>((const __nv_bfloat16*)dout, (const __nv_bfloat16*)out, delta, B,
+                                                                             Hq, Sq, sdo[0], sdo[1], sdo[2], so[0], so[1], so[2]);
+  BwdGeometry g;
+  g.B = B; g.Hq = Hq; g.Hk = Hk; g.Sq = Sq; g.Sk = Sk; g.causal = causal; g.scale = scale;
+  g.dk_s = sdk[0]; g.dk_b = sdk[1]; g.dk_h = sdk[2]; g.dv_s = sdv[0]; g.dv_b = sdv[1]; g.dv_h = sdv[2];
+  g.status = nullptr;
+  dim3 grid((Sk + BKV - 1) / BKV, Hk, B);
+  attn_bwd_kernel<<<grid, THREADS, BWD_SMEM, stream>>>(tq, tk, tv, tdo, (const float*)lse, delta, dq_acc, (__nv_bfloat16*)dk,
+                                                       (__nv_bfloat16*)dv, g);
+  const long long total = (long long)rows * (D / 8);
+  int cgrid = (int)((total + 255) / 256);
+  if (cgrid > 148 * 16) cgrid = 148 * 16;
+  attn_dq_convert_kernel<<<cgrid, 256, 0, stream>>>(dq_acc, (__nv_bfloat16*)dq, B, Hq, Sq, sdq[0], sdq[1], sdq[2], scale);
+  e = cudaGetLastError();
+  if (e != cudaSuccess) set_last_error("dh_attn_bwd_noalloc launch failed: %s", cudaGetErrorString(e));
+  return (int)e;
+}
