@@ -1,0 +1,588 @@
+// Tensor-parallel collectives fused into the tcgen05 GEMM, over NVLink peer memory.
+//
+//  ag_gemm : sequence all-gather -> GEMM            (QKV / FC1 forward, proj / FC2 dgrad)
+//    A few "copy" CTAs of the same grid push this rank's row shard into every peer's
+//    symmetric staging buffer with plain 16-byte peer stores (data is read once from HBM and
+//    stored to all peers from registers) and bump a per-row-block counter on the receiver
+//    with a system-scope release.  The GEMM CTAs walk the row blocks starting with the local
+//    shard; the TMA producer of a tile waits (bounded) on the counter of its row block and
+//    then loads A from LOCAL memory only.  The copy CTAs also copy every arrived block to a
+//    regular tensor that the caller keeps for the weight-gradient GEMM.
+//
+//  gemm_rs : GEMM -> sequence reduce-scatter        (proj / FC2 forward, QKV / FC1 dgrad)
+//    The epilogue stores each partial tile straight into the row OWNER's symmetric buffer
+//    (slot = source rank) and bumps a per-source arrival counter there; row blocks of remote
+//    owners are computed first, the local ones last.  After its last tile every CTA waits
+//    (bounded) for all sources and the whole grid reduces the owner's slots in fp32 to the
+//    bf16 shard.
+//
+// Both kernels use double-buffered symmetric buffers with monotonically increasing counter
+// targets (no resets, no host barriers).  The host runs fused kernels one at a time and in
+// the same order on every rank, which makes the double buffering sufficient: a rank can
+// only finish call c after every peer has started call c, i.e. finished call c-1.
+//
+// No load in this file is a multi-CTA broadcast; peer memory is only ever the target of
+// plain stores / reductions or the source of plain loads.
+//
+// Role in the reference: all_gather_into_tensor / reduce_scatter_tensor around torch.matmul
+// (dhellam/operators/comm.py:13-58, dhellam/core/dstb.py:407-425) and the host-level
+// chunk_allgather_gemm / chunk_gemm_reduce_scatter prototypes (comm.py:89-143).
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "api.h"
+#include "ptx.cuh"
+#include "tmap.h"
+
+namespace dh {
+namespace fused {
+
+constexpr int BM = 128, BN = 256, BK = 64, STAGES = 4, UMMA_K = 16;
+constexpr int A_STAGE_BYTES = BM * BK * 2, B_STAGE_BYTES = BN * BK * 2, STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
+constexpr int NUM_ACC = 2, ACC_COLS = BN, TMEM_COLS = 512;
+constexpr int THREADS = 192;
+constexpr int GROUP_M = 8;
+constexpr int MAX_RANKS = 8;
+constexpr long long PEER_WAIT_CYCLES = 40000000000ll;     // ~20 s: covers start-up skew between ranks
+
+struct __align__(8) Control {
+  uint64_t full[STAGES], empty[STAGES], acc_full[NUM_ACC], acc_empty[NUM_ACC];
+  uint32_t tmem_base;
+  int abort_flag;
+};
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
+
+__device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int& tm, int& tn) {
+  const int band = GROUP_M * tiles_n;
+  const int g = t / band;
+  const int first_m = g * GROUP_M;
+  const int rows = min(GROUP_M, tiles_m - first_m);
+  const int r = t - g * band;
+  tm = first_m + (r % rows);
+  tn = r / rows;
+}
+
+__device__ __forceinline__ bool wait_counter_sys(const uint32_t* p, uint32_t want, volatile int* abort_flag, DeviceStatus* st, int where) {
+  if (ld_acquire_sys(p) >= want) return true;
+  const long long t0 = clock64();
+  while (true) {
+    if (ld_acquire_sys(p) >= want) return true;
+    __nanosleep(100);
+    if (abort_flag != nullptr && *abort_flag) return false;
+    if (clock64() - t0 > PEER_WAIT_CYCLES) {
+      if (abort_flag != nullptr) *abort_flag = 1;
+      report_error(st, ERR_FLAG_TIMEOUT, where, (int)want);
+      return false;
+    }
+  }
+}
+
+// ------------------------------------------------------------------ shared main-loop pieces
+template <bool B_MN>
+__device__ __forceinline__ void load_stage(uint8_t* a_dst, uint8_t* b_dst, const CUtensorMap* ta, const CUtensorMap* tb, uint64_t* bar,
+                                           int m0, int n0, int k0) {
+  mbar_expect_tx(bar, STAGE_BYTES);
+  tma_load_2d(a_dst, ta, bar, k0, m0);
+  if (B_MN) {
+#pragma unroll
+    for (int j = 0; j < BN / 64; ++j) tma_load_2d(b_dst + j * (BK * 128), tb, bar, n0 + 64 * j, k0);
+  } else {
+    tma_load_2d(b_dst, tb, bar, k0, n0);
+  }
+}
+
+template <bool B_MN>
+__device__ __forceinline__ void mma_stage(uint32_t tmem_acc, uint32_t a_base, uint32_t b_base, bool first) {
+  constexpr uint32_t idesc = umma_idesc_bf16(BM, BN, 0, B_MN ? 1 : 0);
+#pragma unroll
+  for (int kk = 0; kk < BK / UMMA_K; ++kk) {
+    const uint64_t adesc = umma_smem_desc(a_base + kk * 32, 16, 1024);
+    const uint64_t bdesc = B_MN ? umma_smem_desc(b_base + kk * 2048, BK * 128, 1024) : umma_smem_desc(b_base + kk * 32, 16, 1024);
+    umma_bf16(tmem_acc, adesc, bdesc, idesc, (!first || kk != 0) ? 1u : 0u);
+  }
+}
+
+// ============================================================================ all-gather -> GEMM
+struct AgParams {
+  const __nv_bfloat16* shard;            // [rows_per_rank, K] this rank's rows (any memory)
+  __nv_bfloat16* stage[MAX_RANKS];       // staging [M, K] on every rank (stage[rank] is local)
+  uint32_t* count[MAX_RANKS];            // per row-block arrival counters on every rank
+  __nv_bfloat16* saved;                  // [M, K] regular tensor kept for the weight gradient (may be null)
+  __nv_bfloat16* d;                      // output [M, N]
+  long long ldd;
+  int M, N, K;
+  int tiles_m, tiles_n;
+  int rank, world, rows_per_rank, blocks_per_rank;
+  int copy_ctas, slices;                 // slices per row block (column split of the push work)
+  uint32_t target;                       // counter value that means "this call's block is complete"
+  DeviceStatus* status;
+};
+
+__device__ __forceinline__ void copy_rows_16B(const __nv_bfloat16* src, __nv_bfloat16* dst, int rows, int cols, long long ld, int c0, int cw) {
+  // copies rows x [c0, c0+cw) (cw multiple of 8) with the whole CTA
+  const int vec_per_row = cw >> 3;
+  const int total = rows * vec_per_row;
+  for (int i = threadIdx.x; i < total; i += blockDim.x) {
+    const int r = i / vec_per_row, c = i - r * vec_per_row;
+    const long long off = (long long)r * ld + c0 + c * 8;
+    st_v4(dst + off, ld_v4(src + off));
+  }
+}
+
+template <bool B_MN>
+__global__ void __launch_bounds__(THREADS, 1)
+ag_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, const AgParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sA = smem;
+  uint8_t* sB = smem + STAGES * A_STAGE_BYTES;
+  Control* ctl = reinterpret_cast<Control*>(smem + STAGES * STAGE_BYTES);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  // ------------------------------------------------------------------ copy CTAs
+  if ((int)blockIdx.x < p.copy_ctas) {
+    __shared__ int s_ok;
+    const int items = p.blocks_per_rank * p.slices;
+    const int cw = p.K / p.slices;                          // columns per slice (multiple of 8)
+    // phase 1: push my shard to every rank's staging (local first), one (row block, slice) at a time
+    for (int it = blockIdx.x; it < items; it += p.copy_ctas) {
+      const int lb = it / p.slices, sl = it - lb * p.slices;
+      const int gb = p.rank * p.blocks_per_rank + lb;       // global row block
+      const long long row0 = (long long)lb * BM;
+      const int vec_per_row = cw >> 3;
+      const int total = BM * vec_per_row;
+      for (int i = threadIdx.x; i < total; i += blockDim.x) {
+        const int r = i / vec_per_row, c = i - r * vec_per_row;
+        const long long src_off = (row0 + r) * p.K + (long long)sl * cw + c * 8;
+        const long long dst_off = ((long long)gb * BM + r) * p.K + (long long)sl * cw + c * 8;
+        const uint4 v = ld_nc_v4(p.shard + src_off);
+        // the destination that consumes this shard earliest is rank-1, then rank-2, ...
+#pragma unroll 1
+        for (int j = 0; j < p.world; ++j) {
+          const int dst = (p.rank - j + p.world) % p.world;
+          st_v4(p.stage[dst] + dst_off, v);
+        }
+        if (p.saved != nullptr) st_v4(p.saved + dst_off, v);
+      }
+      __syncthreads();
+      if (threadIdx.x == 0) {
+        fence_proxy_async_all();
+        for (int j = 0; j < p.world; ++j) {
+          const int dst = (p.rank - j + p.world) % p.world;
+          red_add_release_sys(p.count[dst] + gb, 1u);
+        }
+      }
+    }
+    // phase 2: keep a copy of every remote block as it arrives
+    if (p.saved != nullptr) {
+      const int remote_items = (p.world - 1) * p.blocks_per_rank;
+      for (int it = blockIdx.x; it < remote_items; it += p.copy_ctas) {
+        const int src = (p.rank + 1 + it / p.blocks_per_rank) % p.world;
+        const int gb = src * p.blocks_per_rank + it % p.blocks_per_rank;
+        if (threadIdx.x == 0) s_ok = wait_counter_sys(p.count[p.rank] + gb, p.target, nullptr, p.status, 600) ? 1 : 0;
+        __syncthreads();
+        const int ok = s_ok;
+        __syncthreads();
+        if (!ok) break;
+        const long long base = (long long)gb * BM * p.K;
+        copy_rows_16B(p.stage[p.rank] + base, p.saved + base, BM, p.K, p.K, 0, p.K);
+      }
+    }
+    return;
+  }
+
+  // ------------------------------------------------------------------ GEMM CTAs
+  const int gemm_ctas = gridDim.x - p.copy_ctas;
+  const int cta = blockIdx.x - p.copy_ctas;
+  const int num_tiles = p.tiles_m * p.tiles_n;
+  const int num_kb = (p.K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) { mbar_init(&ctl->full[s], 1); mbar_init(&ctl->empty[s], 1); }
+    for (int a = 0; a < NUM_ACC; ++a) { mbar_init(&ctl->acc_full[a], 1); mbar_init(&ctl->acc_empty[a], 4); }
+    ctl->abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) { tmem_alloc(&ctl->tmem_base, TMEM_COLS); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = ctl->tmem_base;
+  volatile int* abort_flag = &ctl->abort_flag;
+  const int rot = p.rank * p.blocks_per_rank;               // local row blocks first
+
+  if (warp == 0) {
+    if (lane == 0) {
+      tma_prefetch_desc(&tmap_a);
+      tma_prefetch_desc(&tmap_b);
+      int s = 0;
+      uint32_t ph = 0;
+      bool ok = true;
+      int ready_block = -1;
+      for (int t = cta; t < num_tiles && ok; t += gemm_ctas) {
+        int tm, tn;
+        tile_coords(t, p.tiles_m, p.tiles_n, tm, tn);
+        tm = (tm + rot) % p.tiles_m;
+        if (tm != ready_block) {
+          if (!wait_counter_sys(p.count[p.rank] + tm, p.target, abort_flag, p.status, 610)) { ok = false; break; }
+          fence_proxy_async_all();                          // peer / other-CTA stores -> visible to the TMA reads below
+          ready_block = tm;
+        }
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&ctl->empty[s], ph ^ 1, abort_flag, p.status, 611)) { ok = false; break; }
+          load_stage<B_MN>(sA + s * A_STAGE_BYTES, sB + s * B_STAGE_BYTES, &tmap_a, &tmap_b, &ctl->full[s], tm * BM, tn * BN, kb * BK);
+          if (++s == STAGES) { s = 0; ph ^= 1; }
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    if (lane == 0) {
+      int s = 0, acc = 0;
+      uint32_t ph = 0, acc_ph = 0;
+      bool ok = true;
+      for (int t = cta; t < num_tiles && ok; t += gemm_ctas) {
+        if (!mbar_wait(&ctl->acc_empty[acc], acc_ph ^ 1, abort_flag, p.status, 620)) { ok = false; break; }
+        tc_fence_after();
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&ctl->full[s], ph, abort_flag, p.status, 621)) { ok = false; break; }
+          tc_fence_after();
+          mma_stage<B_MN>(tmem_base + acc * ACC_COLS, smem_u32(sA + s * A_STAGE_BYTES), smem_u32(sB + s * B_STAGE_BYTES), kb == 0);
+          umma_commit(&ctl->empty[s]);
+          if (++s == STAGES) { s = 0; ph ^= 1; }
+        }
+        if (!ok) break;
+        umma_commit(&ctl->acc_full[acc]);
+        if (++acc == NUM_ACC) { acc = 0; acc_ph ^= 1; }
+      }
+    }
+    __syncwarp();
+  } else {
+    const int quarter = warp & 3;
+    int acc = 0;
+    uint32_t acc_ph = 0;
+    bool ok = true;
+    for (int t = cta; t < num_tiles && ok; t += gemm_ctas) {
+      int tm, tn;
+      tile_coords(t, p.tiles_m, p.tiles_n, tm, tn);
+      tm = (tm + rot) % p.tiles_m;
+      if (!mbar_wait(&ctl->acc_full[acc], acc_ph, abort_flag, p.status, 630)) { ok = false; break; }
+      tc_fence_after();
+      const int row = tm * BM + quarter * 32 + lane;
+      const uint32_t taddr = tmem_base + acc * ACC_COLS + ((uint32_t)(quarter * 32) << 16);
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        const int col0 = tn * BN + c * 32;
+        if (col0 >= p.N) break;
+        uint32_t r[32];
+        tmem_ld32(taddr + c * 32, r);
+        tmem_ld_wait();
+        if (row >= p.M) continue;
+        __nv_bfloat16* dst = p.d + (long long)row * p.ldd + col0;
+        if (col0 + 32 <= p.N) {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            uint4 v;
+            v.x = pack_bf16x2(__uint_as_float(r[8 * j + 0]), __uint_as_float(r[8 * j + 1]));
+            v.y = pack_bf16x2(__uint_as_float(r[8 * j + 2]), __uint_as_float(r[8 * j + 3]));
+            v.z = pack_bf16x2(__uint_as_float(r[8 * j + 4]), __uint_as_float(r[8 * j + 5]));
+            v.w = pack_bf16x2(__uint_as_float(r[8 * j + 6]), __uint_as_float(r[8 * j + 7]));
+            reinterpret_cast<uint4*>(dst)[j] = v;
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            if (col0 + j < p.N) dst[j] = __float2bfloat16(__uint_as_float(r[j]));
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&ctl->acc_empty[acc]);
+      if (++acc == NUM_ACC) { acc = 0; acc_ph ^= 1; }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, TMEM_COLS); }
+}
+
+// ============================================================================ GEMM -> reduce-scatter
+struct RsParams {
+  __nv_bfloat16* part[MAX_RANKS];        // partial buffers [world][rows_per_rank, N] on every rank (slot = source rank)
+  uint32_t* arrived[MAX_RANKS];          // per-source tile arrival counters on every rank
+  __nv_bfloat16* out;                    // [rows_per_rank, N] reduced shard
+  int M, N, K;
+  int tiles_m, tiles_n;
+  int rank, world, rows_per_rank, blocks_per_rank;
+  uint32_t target;                       // arrival count (per source) that completes this call
+  DeviceStatus* status;
+};
+
+template <bool B_MN>
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_rs_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, const RsParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sA = smem;
+  uint8_t* sB = smem + STAGES * A_STAGE_BYTES;
+  Control* ctl = reinterpret_cast<Control*>(smem + STAGES * STAGE_BYTES);
+  __shared__ int s_ok;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int num_tiles = p.tiles_m * p.tiles_n;
+  const int num_kb = (p.K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) { mbar_init(&ctl->full[s], 1); mbar_init(&ctl->empty[s], 1); }
+    for (int a = 0; a < NUM_ACC; ++a) { mbar_init(&ctl->acc_full[a], 1); mbar_init(&ctl->acc_empty[a], 4); }
+    ctl->abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) { tmem_alloc(&ctl->tmem_base, TMEM_COLS); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = ctl->tmem_base;
+  volatile int* abort_flag = &ctl->abort_flag;
+  // remote owners first (rank+1, rank+2, ...), the local rows last
+  const int rot = ((p.rank + 1) % p.world) * p.blocks_per_rank;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      tma_prefetch_desc(&tmap_a);
+      tma_prefetch_desc(&tmap_b);
+      int s = 0;
+      uint32_t ph = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+        int tm, tn;
+        tile_coords(t, p.tiles_m, p.tiles_n, tm, tn);
+        tm = (tm + rot) % p.tiles_m;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&ctl->empty[s], ph ^ 1, abort_flag, p.status, 700)) { ok = false; break; }
+          load_stage<B_MN>(sA + s * A_STAGE_BYTES, sB + s * B_STAGE_BYTES, &tmap_a, &tmap_b, &ctl->full[s], tm * BM, tn * BN, kb * BK);
+          if (++s == STAGES) { s = 0; ph ^= 1; }
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    if (lane == 0) {
+      int s = 0, acc = 0;
+      uint32_t ph = 0, acc_ph = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+        if (!mbar_wait(&ctl->acc_empty[acc], acc_ph ^ 1, abort_flag, p.status, 710)) { ok = false; break; }
+        tc_fence_after();
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&ctl->full[s], ph, abort_flag, p.status, 711)) { ok = false; break; }
+          tc_fence_after();
+          mma_stage<B_MN>(tmem_base + acc * ACC_COLS, smem_u32(sA + s * A_STAGE_BYTES), smem_u32(sB + s * B_STAGE_BYTES), kb == 0);
+          umma_commit(&ctl->empty[s]);
+          if (++s == STAGES) { s = 0; ph ^= 1; }
+        }
+        if (!ok) break;
+        umma_commit(&ctl->acc_full[acc]);
+        if (++acc == NUM_ACC) { acc = 0; acc_ph ^= 1; }
+      }
+    }
+    __syncwarp();
+  } else {
+    const int quarter = warp & 3;
+    int acc = 0;
+    uint32_t acc_ph = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+      int tm, tn;
+      tile_coords(t, p.tiles_m, p.tiles_n, tm, tn);
+      tm = (tm + rot) % p.tiles_m;
+      if (!mbar_wait(&ctl->acc_full[acc], acc_ph, abort_flag, p.status, 720)) { ok = false; break; }
+      tc_fence_after();
+      const int owner = tm / p.blocks_per_rank;
+      const int lrow = (tm - owner * p.blocks_per_rank) * BM + quarter * 32 + lane;      // row inside the owner's shard
+      const uint32_t taddr = tmem_base + acc * ACC_COLS + ((uint32_t)(quarter * 32) << 16);
+      __nv_bfloat16* slot = p.part[owner] + ((long long)p.rank * p.rows_per_rank + lrow) * p.N;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        const int col0 = tn * BN + c * 32;
+        if (col0 >= p.N) break;
+        uint32_t r[32];
+        tmem_ld32(taddr + c * 32, r);
+        tmem_ld_wait();
+        __nv_bfloat16* dst = slot + col0;
+        if (col0 + 32 <= p.N) {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            uint4 v;
+            v.x = pack_bf16x2(__uint_as_float(r[8 * j + 0]), __uint_as_float(r[8 * j + 1]));
+            v.y = pack_bf16x2(__uint_as_float(r[8 * j + 2]), __uint_as_float(r[8 * j + 3]));
+            v.z = pack_bf16x2(__uint_as_float(r[8 * j + 4]), __uint_as_float(r[8 * j + 5]));
+            v.w = pack_bf16x2(__uint_as_float(r[8 * j + 6]), __uint_as_float(r[8 * j + 7]));
+            st_v4(dst + 8 * j, v);
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            if (col0 + j < p.N) dst[j] = __float2bfloat16(__uint_as_float(r[j]));
+        }
+      }
+      tc_fence_before();
+      // this warp's 32 rows of the tile are stored -> tell the owner (four arrivals per tile)
+      __syncwarp();
+      if (lane == 0) {
+        red_add_release_sys(p.arrived[owner] + p.rank, 1u);
+        mbar_arrive(&ctl->acc_empty[acc]);
+      }
+      if (++acc == NUM_ACC) { acc = 0; acc_ph ^= 1; }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, TMEM_COLS); }
+
+  // ------------------------------------------------------------------ owner-side reduction
+  if (threadIdx.x == 0) {
+    int ok = ctl->abort_flag ? 0 : 1;
+    for (int s = 0; s < p.world && ok; ++s)
+      ok = wait_counter_sys(p.arrived[p.rank] + s, p.target, nullptr, p.status, 730) ? 1 : 0;
+    s_ok = ok;
+  }
+  __syncthreads();
+  if (!s_ok) return;
+  const long long vecs = (long long)p.rows_per_rank * p.N / 8;
+  const long long slot_elems = (long long)p.rows_per_rank * p.N;
+  const __nv_bfloat16* base = p.part[p.rank];
+  for (long long i = (long long)blockIdx.x * THREADS + threadIdx.x; i < vecs; i += (long long)gridDim.x * THREADS) {
+    float accv[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) accv[j] = 0.f;
+    for (int s = 0; s < p.world; ++s) {
+      const uint4 u = ld_v4(base + s * slot_elems + i * 8);
+      float2 a = unpack_bf16x2(u.x), b = unpack_bf16x2(u.y), c = unpack_bf16x2(u.z), d = unpack_bf16x2(u.w);
+      accv[0] += a.x; accv[1] += a.y; accv[2] += b.x; accv[3] += b.y; accv[4] += c.x; accv[5] += c.y; accv[6] += d.x; accv[7] += d.y;
+    }
+    uint4 o;
+    o.x = pack_bf16x2(accv[0], accv[1]); o.y = pack_bf16x2(accv[2], accv[3]); o.z = pack_bf16x2(accv[4], accv[5]); o.w = pack_bf16x2(accv[6], accv[7]);
+    reinterpret_cast<uint4*>(p.out)[i] = o;
+  }
+}
+
+template <typename Kern>
+static int configure(Kern kern, bool& done) {
+  if (done) return 0;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+  if (e != cudaSuccess) { set_last_error("fused GEMM: shared memory opt-in failed: %s", cudaGetErrorString(e)); return (int)e; }
+  done = true;
+  return 0;
+}
+
+}  // namespace fused
+}  // namespace dh
+
+using namespace dh;
+using namespace dh::fused;
+
+extern "C" {
+
+// stage_ptrs / count_ptrs: `world` device pointers (index = rank).  The local shard has
+// rows_per_rank = M / world rows; rows_per_rank must be a multiple of 128.
+int dh_ag_gemm_bf16(const void* shard, void* const* stage_ptrs, void* const* count_ptrs, void* saved, const void* b, int64_t ldb,
+                    int b_mn_major, void* d, int64_t ldd, int M, int N, int K, int rank, int world, int copy_ctas, unsigned target_base,
+                    int sm_budget, cudaStream_t stream) {
+  if (world < 2 || world > MAX_RANKS) { set_last_error("dh_ag_gemm_bf16: world size %d not in [2, %d]", world, MAX_RANKS); return (int)cudaErrorInvalidValue; }
+  if (M % (world * BM) != 0 || K % 64 != 0) { set_last_error("dh_ag_gemm_bf16: M must divide by world*128 and K by 64 (M=%d K=%d)", M, K); return (int)cudaErrorInvalidValue; }
+  if ((ldd % 8) != 0) { set_last_error("dh_ag_gemm_bf16: ldd must be a multiple of 8"); return (int)cudaErrorInvalidValue; }
+  const CUtensorMap* ta = get_tmap_2d(stage_ptrs[rank], 2, (uint64_t)K, (uint64_t)M, (uint64_t)K * 2, BK, BM, true);
+  const CUtensorMap* tb = b_mn_major ? get_tmap_2d(b, 2, (uint64_t)N, (uint64_t)K, (uint64_t)ldb * 2, 64, BK, true)
+                                     : get_tmap_2d(b, 2, (uint64_t)K, (uint64_t)N, (uint64_t)ldb * 2, BK, BN, true);
+  if (!ta || !tb) return (int)cudaErrorInvalidValue;
+  AgParams p;
+  p.shard = (const __nv_bfloat16*)shard;
+  for (int i = 0; i < MAX_RANKS; ++i) {
+    p.stage[i] = i < world ? (__nv_bfloat16*)stage_ptrs[i] : nullptr;
+    p.count[i] = i < world ? (uint32_t*)count_ptrs[i] : nullptr;
+  }
+  p.saved = (__nv_bfloat16*)saved;
+  p.d = (__nv_bfloat16*)d;
+  p.ldd = ldd;
+  p.M = M; p.N = N; p.K = K;
+  p.tiles_m = M / BM;
+  p.tiles_n = (N + BN - 1) / BN;
+  p.rank = rank; p.world = world;
+  p.rows_per_rank = M / world;
+  p.blocks_per_rank = p.rows_per_rank / BM;
+  const int sms = dh_sm_count();
+  int budget = (sm_budget <= 0 || sm_budget > sms) ? sms : sm_budget;
+  if (copy_ctas <= 0) copy_ctas = 16;
+  if (copy_ctas > budget / 2) copy_ctas = budget / 2;
+  p.copy_ctas = copy_ctas;
+  // enough (row block, column slice) items to keep every copy CTA busy; slices divide K/8 evenly
+  int slices = 1;
+  while (p.blocks_per_rank * slices < 2 * copy_ctas && (K / (slices * 2)) % 8 == 0 && slices < 64) slices *= 2;
+  p.slices = slices;
+  p.target = target_base + (unsigned)slices;             // counters grow by `slices` per call; target_base = value before it
+  p.status = reinterpret_cast<DeviceStatus*>(dh_status_device_ptr());
+  const int grid = budget;
+  static bool c0 = false, c1 = false;
+  int rc = b_mn_major ? configure(ag_gemm_kernel<true>, c1) : configure(ag_gemm_kernel<false>, c0);
+  if (rc) return rc;
+  if (b_mn_major) ag_gemm_kernel<true><<<grid, THREADS, SMEM_BYTES, stream>>>(*ta, *tb, p);
+  else ag_gemm_kernel<false><<<grid, THREADS, SMEM_BYTES, stream>>>(*ta, *tb, p);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) set_last_error("dh_ag_gemm_bf16 launch failed: %s", cudaGetErrorString(e));
+  return (int)e;
+}
+
+// Number of counter increments one ag_gemm call adds to every row-block counter, so the
+// caller can keep `target_base` (= number of calls so far on this buffer) as the only state.
+int dh_ag_gemm_slices(int M, int K, int world, int copy_ctas, int sm_budget) {
+  const int sms = dh_sm_count();
+  int budget = (sm_budget <= 0 || sm_budget > sms) ? sms : sm_budget;
+  if (copy_ctas <= 0) copy_ctas = 16;
+  if (copy_ctas > budget / 2) copy_ctas = budget / 2;
+  const int bpr = M / world / BM;
+  int slices = 1;
+  while (bpr * slices < 2 * copy_ctas && (K / (slices * 2)) % 8 == 0 && slices < 64) slices *= 2;
+  return slices;
+}
+
+// part_ptrs / arrived_ptrs: `world` device pointers.  A is [M, K] local, the result is this
+// rank's [M/world, N] shard of the sum over ranks.  target = tiles per owner block x call count.
+int dh_gemm_rs_bf16(const void* a, int64_t lda, const void* b, int64_t ldb, int b_mn_major, void* const* part_ptrs,
+                    void* const* arrived_ptrs, void* out, int M, int N, int K, int rank, int world, unsigned call_count, int sm_budget,
+                    cudaStream_t stream) {
+  if (world < 2 || world > MAX_RANKS) { set_last_error("dh_gemm_rs_bf16: world size %d not in [2, %d]", world, MAX_RANKS); return (int)cudaErrorInvalidValue; }
+  if (M % (world * BM) != 0 || N % 8 != 0) { set_last_error("dh_gemm_rs_bf16: M must divide by world*128 and N by 8 (M=%d N=%d)", M, N); return (int)cudaErrorInvalidValue; }
+  const CUtensorMap* ta = get_tmap_2d(a, 2, (uint64_t)K, (uint64_t)M, (uint64_t)lda * 2, BK, BM, true);
+  const CUtensorMap* tb = b_mn_major ? get_tmap_2d(b, 2, (uint64_t)N, (uint64_t)K, (uint64_t)ldb * 2, 64, BK, true)
+                                     : get_tmap_2d(b, 2, (uint64_t)K, (uint64_t)N, (uint64_t)ldb * 2, BK, BN, true);
+  if (!ta || !tb) return (int)cudaErrorInvalidValue;
+  RsParams p;
+  for (int i = 0; i < MAX_RANKS; ++i) {
+    p.part[i] = i < world ? (__nv_bfloat16*)part_ptrs[i] : nullptr;
+    p.arrived[i] = i < world ? (uint32_t*)arrived_ptrs[i] : nullptr;
+  }
+  p.out = (__nv_bfloat16*)out;
+  p.M = M; p.N = N; p.K = K;
+  p.tiles_m = M / BM;
+  p.tiles_n = (N + BN - 1) / BN;
+  p.rank = rank; p.world = world;
+  p.rows_per_rank = M / world;
+  p.blocks_per_rank = p.rows_per_rank / BM;
+  p.target = call_count + (unsigned)(p.blocks_per_rank * p.tiles_n * 4);   // call_count = counter value before this call; four warps arrive per tile
+  p.status = reinterpret_cast<DeviceStatus*>(dh_status_device_ptr());
+  const int sms = dh_sm_count();
+  int budget = (sm_budget <= 0 || sm_budget > sms) ? sms : sm_budget;
+  const int num_tiles = p.tiles_m * p.tiles_n;
+  const int grid = num_tiles < budget ? num_tiles : budget;
+  static bool c0 = false, c1 = false;
+  int rc = b_mn_major ? configure(gemm_rs_kernel<true>, c1) : configure(gemm_rs_kernel<false>, c0);
+  if (rc) return rc;
+  if (b_mn_major) gemm_rs_kernel<true><<<grid, THREADS, SMEM_BYTES, stream>>>(*ta, *tb, p);
+  else gemm_rs_kernel<false><<<grid, THREADS, SMEM_BYTES, stream>>>(*ta, *tb, p);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) set_last_error("dh_gemm_rs_bf16 launch failed: %s", cudaGetErrorString(e));
+  return (int)e;
+}
+
+}  // extern "C"

@@ -1,0 +1,154 @@
+"""Multi-GPU tests (need >= 2 CUDA devices; skipped otherwise): the fused
+all-gather->GEMM and GEMM->reduce-scatter kernels against the NCCL + GEMM composition, and
+the engine with tensor parallelism on GPUs against the single-GPU engine."""
+import os
+import socket
+import traceback
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _entry(rank, world, port, fn, args, errq):
+    import torch.distributed as dist
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank))
+    os.environ.setdefault("TORCH_NCCL_AVOID_RECORD_STREAMS", "1")
+    try:
+        torch.cuda.set_device(rank)
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+        fn(rank, world, *args)
+        torch.cuda.synchronize()
+        dist.barrier()
+    except Exception:
+        errq.put((rank, traceback.format_exc()))
+    finally:
+        if dist.is_initialized():
+            dist.destroy_process_group()
+
+
+def run_gpu_ranks(fn, world, *args, timeout=300):
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    errq = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_entry, args=(r, world, port, fn, args, errq)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout)
+    errs = []
+    while not errq.empty():
+        errs.append(errq.get())
+    for p in procs:
+        if p.is_alive():
+            p.terminate()
+            errs.append((-1, "rank timed out"))
+    if errs:
+        raise AssertionError("\n".join(f"[rank {r}]\n{tb}" for r, tb in errs))
+
+
+def _need(n):
+    if torch.cuda.device_count() < n:
+        pytest.skip(f"needs {n} GPUs")
+
+
+def _rel(a, b):
+    return ((a.float() - b.float()).norm() / b.float().norm().clamp_min(1e-12)).item()
+
+
+def _fused_worker(rank, world, rows, h, n_out, iters):
+    import torch.distributed as dist
+    from dhellam_b200 import kernels as K
+    from dhellam_b200.config import ModelConfig, ParallelConfig, TrainConfig
+    from dhellam_b200.ops import comm as C
+    from dhellam_b200.ops.fused_comm import FusedTP
+    from dhellam_b200.ops.gemm import gemm_nn, gemm_nt
+    from dhellam_b200.parallel import state as PS
+    dev = torch.device("cuda", rank)
+    ps = PS.initialize_model_parallel(ParallelConfig(tp=world))
+    cfg = ModelConfig(hidden_size=h, seq_length=rows, num_attention_heads=h // 128, num_query_groups=h // 128)
+    fused = FusedTP(ps, cfg, TrainConfig(micro_batch_size=1), dev, max_rows=rows, width=h)
+    torch.manual_seed(100 + rank)
+    for it in range(iters):
+        shard = (torch.randn(rows // world, h, device=dev)).to(torch.bfloat16)
+        w = (torch.randn(n_out, h, device=dev) * 0.05).to(torch.bfloat16)
+        # all-gather -> GEMM, forward form (B K-major) and dgrad form (B MN-major)
+        full_ref, _ = C.gather_along_first_dim(shard, ps.tp_group)
+        out, full = fused.ag_gemm(shard, w)
+        torch.cuda.synchronize()
+        assert torch.equal(full, full_ref), f"gathered operand differs (iter {it})"
+        assert _rel(out, gemm_nt(full_ref, w)) < 1e-3
+        wt = (torch.randn(h, n_out, device=dev) * 0.05).to(torch.bfloat16)
+        out2, _ = fused.ag_gemm(shard, wt, transpose_w=True)
+        assert _rel(out2, gemm_nn(full_ref, wt)) < 1e-3
+        # GEMM -> reduce-scatter, both forms
+        a = torch.randn(rows, n_out, device=dev).to(torch.bfloat16)
+        w2 = (torch.randn(h, n_out, device=dev) * 0.05).to(torch.bfloat16)
+        ref, _ = C.reduce_scatter_along_first_dim(gemm_nt(a, w2), ps.tp_group)
+        got = fused.gemm_rs(a, w2)
+        assert _rel(got, ref) < 1e-2, _rel(got, ref)
+        w3 = (torch.randn(n_out, h, device=dev) * 0.05).to(torch.bfloat16)
+        ref3, _ = C.reduce_scatter_along_first_dim(gemm_nn(a, w3), ps.tp_group)
+        got3 = fused.gemm_rs(a, w3, transpose_w=True)
+        assert _rel(got3, ref3) < 1e-2, _rel(got3, ref3)
+    torch.cuda.synchronize()
+    st = K.read_status()
+    assert st.code == 0, (st.code, st.where, st.extra)
+
+
+def test_fused_ag_gemm_and_gemm_rs_match_nccl_composition():
+    _need(2)
+    world = 2 if torch.cuda.device_count() < 4 else 4
+    run_gpu_ranks(_fused_worker, world, 2048, 1024, 768, 3)
+
+
+def _engine_worker(rank, world, fused, out_path):
+    from dhellam_b200 import kernels as K
+    from dhellam_b200.config import ModelConfig, ParallelConfig, TrainConfig
+    from dhellam_b200.data import make_microbatch, synthetic_tokens
+    from dhellam_b200.models.sharding import random_full_head, random_full_layer
+    from dhellam_b200.parallel import state as PS
+    from dhellam_b200.trainer import Trainer
+    cfg = ModelConfig(name="t-llama", num_layers=4, hidden_size=1024, ffn_hidden_size=2048, num_attention_heads=8,
+                      num_query_groups=4, head_dim=128, vocab_size=4096, seq_length=512, rope_theta=500000.0)
+    train = TrainConfig(micro_batch_size=2, global_batch_size=6, dtype="bf16", clip_grad=0.0, fused_comm=fused)
+    tr = Trainer(cfg, ParallelConfig(tp=world), train, device=torch.device("cuda", rank))
+    layers = [random_full_layer(cfg, i, 3) for i in range(cfg.num_layers)]
+    head = random_full_head(cfg, 3)
+    for i, w in enumerate(layers):
+        tr.model.load_full_layer_weights(i, w)
+    tr.model.load_full_head_weights(head)
+    samples = [synthetic_tokens(cfg, 2, 40 + i) for i in range(3)]
+    mbs = [make_microbatch(cfg, tr.ps, s, i, 40 + i, tr.device) for i, s in enumerate(samples)]
+    tr.optimizer.zero_grad()
+    losses = tr.engine.run_step(mbs)
+    tr.optimizer.reduce_gradients()
+    torch.cuda.synchronize()
+    assert K.read_status().code == 0
+    if rank == 0:
+        torch.save({"losses": [float(l) for l in losses], "fused": bool(tr.env.fused_tp),
+                    "g_ln": tr.model.dctb[0].ln_attn_weight_first.main_grad.cpu(),
+                    "g_qkv": tr.model.dctb[0].column_attn_weight_first.main_grad.cpu()}, out_path)
+
+
+def test_tp_engine_fused_matches_unfused(tmp_path):
+    _need(2)
+    a, b = str(tmp_path / "fused.pt"), str(tmp_path / "nccl.pt")
+    run_gpu_ranks(_engine_worker, 2, True, a)
+    run_gpu_ranks(_engine_worker, 2, False, b)
+    ra, rb = torch.load(a), torch.load(b)
+    assert ra["fused"] and not rb["fused"]
+    for x, y in zip(ra["losses"], rb["losses"]):
+        assert abs(x - y) / abs(y) < 1e-2, (ra["losses"], rb["losses"])
+    assert _rel(ra["g_ln"], rb["g_ln"]) < 5e-2
+    assert _rel(ra["g_qkv"], rb["g_qkv"]) < 5e-2
