@@ -63,6 +63,24 @@ class Env:
         self.moe_aux = []             # auxiliary (load-balance) losses of the current step
 
 
+def hand_over(obj, stream):
+    """Marks every CUDA tensor inside ``obj`` (tensor, tuple, list or dict) as used on
+    ``stream``.  Activations are allocated by the forward strand's stream and read, one round
+    later, by the backward strand's stream; without this the caching allocator could recycle
+    a block for the forward stream while the backward stream's kernels are still queued."""
+    if stream is None or obj is None:
+        return
+    if isinstance(obj, torch.Tensor):
+        if obj.is_cuda:
+            obj.record_stream(stream)
+    elif isinstance(obj, dict):
+        for v in obj.values():
+            hand_over(v, stream)
+    elif isinstance(obj, (tuple, list)):
+        for v in obj:
+            hand_over(v, stream)
+
+
 class DoubleStrandEngine:
     def __init__(self, model, env: Env, strategy: Optional[Strategy] = None, single_stream: bool = False,
                  profile: bool = False, trace=None):
@@ -116,8 +134,10 @@ class DoubleStrandEngine:
                     self._set_stream("S2")
                     if st.cuda and b in self.fwd_done:
                         st.s2.wait_event(self.fwd_done[b])
+                    saved = self.head_saved.pop(b)
+                    hand_over(saved, st.s2)
                     with self._on("S2"):
-                        g = H.loss_bwd(self.env, self.model.head, mbs[b], self.head_saved.pop(b), self.grad_scale)
+                        g = H.loss_bwd(self.env, self.model.head, mbs[b], saved, self.grad_scale)
             else:
                 x, g = self._inbox["prev"]
         else:
@@ -142,7 +162,9 @@ class DoubleStrandEngine:
             if fa:
                 frun = LayerRun(f_params, self.acts.setdefault((a, f_idx), {}), mbs[a], self.env, {"x": x}, f_idx)
             if fb:
-                brun = LayerRun(b_params, self.acts.pop((b, b_idx)), mbs[b], self.env, {"dout": g}, b_idx)
+                saved_acts = self.acts.pop((b, b_idx))
+                hand_over(saved_acts, st.s2)
+                brun = LayerRun(b_params, saved_acts, mbs[b], self.env, {"dout": g}, b_idx)
             self.executor.run(frun, brun)
             if fa:
                 x = frun.v["out"]
