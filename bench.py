@@ -45,6 +45,7 @@ def parse():
     ap.add_argument("--no-fused-comm", action="store_true", help="library collectives instead of in-kernel ones")
     ap.add_argument("--no-dual-strand", action="store_true", help="one stream, no forward/backward pairing")
     ap.add_argument("--schedule-config", default=None)
+    ap.add_argument("--compute-streams", type=int, default=1, help="2 = let compute kernels of the two strands co-run")
     ap.add_argument("--skip-e2e", action="store_true")
     return ap.parse_args()
 
@@ -136,7 +137,8 @@ def main():
     cfg = preset(args.model, **over)
     mbs = args.micro_batch or (4 if N >= 2 else 2)
     train = TrainConfig(micro_batch_size=mbs, global_batch_size=args.global_batch, dtype="bf16", fused_comm=not args.no_fused_comm,
-                        dhellam=not args.no_dual_strand, schedule_config=args.schedule_config)
+                        dhellam=not args.no_dual_strand, schedule_config=args.schedule_config,
+                        compute_streams=args.compute_streams)
     pcfg = ParallelConfig(tp=N, sequence_parallel=True)
     device = torch.device("cuda", local)
     PS.set_state(None)
@@ -231,7 +233,7 @@ def main():
                        "heads": cfg.num_attention_heads, "kv_heads": cfg.num_query_groups, "vocab": cfg.vocab_size,
                        "global_batch": args.global_batch, "micro_batch": mbs, "seq_len": cfg.seq_length,
                        "parallelism": f"tp{N}+sp" if N > 1 else "single", "optimizer": "adam, fp32 master + fp32 main_grad",
-                       "fused_comm": bool(tr.env.fused_tp), "dual_strand": train.dhellam,
+                       "fused_comm": bool(tr.env.fused_tp), "dual_strand": train.dhellam, "compute_streams": train.compute_streams,
                        "l2": "working set per step (weights + activations, tens of GB) is far larger than the 126 MB L2"},
             "clocks": clocks, "e2e": e2e, "gpu_launches": launches,
         }

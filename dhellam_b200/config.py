@@ -113,6 +113,7 @@ class TrainConfig:
     fused_comm: bool = True              # in-kernel collectives (peer memory) instead of NCCL
     schedule_config: Optional[str] = None
     dhellam: bool = True                 # dual-strand scheduling on/off (the reference's --dhellam)
+    compute_streams: int = 1             # 1: both strands' compute in schedule order on one stream; 2: co-run
     train_iters: int = 2
     log_interval: int = 1
     save: Optional[str] = None

@@ -83,11 +83,12 @@ def hand_over(obj, stream):
 
 class DoubleStrandEngine:
     def __init__(self, model, env: Env, strategy: Optional[Strategy] = None, single_stream: bool = False,
-                 profile: bool = False, trace=None):
+                 profile: bool = False, trace=None, compute_streams: int = 2):
         self.model, self.env = model, env
         self.cfg, self.ps = env.cfg, env.ps
         self.program = build_layer_program(env.cfg, cp=env.ps.cp)
-        self.streams = StreamSet(env.device if env.device.type == "cuda" else None, single_stream=single_stream)
+        self.streams = StreamSet(env.device if env.device.type == "cuda" else None, single_stream=single_stream,
+                                 compute_streams=compute_streams)
         self.executor = Executor(self.program, strategy or Strategy(), self.streams, profile=profile, trace=trace)
         self.acts: Dict[tuple, dict] = {}
         self.head_saved: Dict[int, dict] = {}

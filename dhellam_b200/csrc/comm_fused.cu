@@ -45,6 +45,9 @@ constexpr int THREADS = 192;
 constexpr int GROUP_M = 8;
 constexpr int MAX_RANKS = 8;
 constexpr long long PEER_WAIT_CYCLES = 40000000000ll;     // ~20 s: covers start-up skew between ranks
+// Barriers inside the CTA sit downstream of a peer wait (the MMA warp waits for a stage that the
+// producer fills only after a peer's data arrived), so they must outlast it.
+constexpr long long LOCAL_WAIT_CYCLES = 2 * PEER_WAIT_CYCLES;
 
 struct __align__(8) Control {
   uint64_t full[STAGES], empty[STAGES], acc_full[NUM_ACC], acc_empty[NUM_ACC];
@@ -230,7 +233,7 @@ ag_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           ready_block = tm;
         }
         for (int kb = 0; kb < num_kb; ++kb) {
-          if (!mbar_wait(&ctl->empty[s], ph ^ 1, abort_flag, p.status, 611)) { ok = false; break; }
+          if (!mbar_wait(&ctl->empty[s], ph ^ 1, abort_flag, p.status, 611, LOCAL_WAIT_CYCLES)) { ok = false; break; }
           load_stage<B_MN>(sA + s * A_STAGE_BYTES, sB + s * B_STAGE_BYTES, &tmap_a, &tmap_b, &ctl->full[s], tm * BM, tn * BN, kb * BK);
           if (++s == STAGES) { s = 0; ph ^= 1; }
         }
@@ -243,10 +246,10 @@ ag_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       uint32_t ph = 0, acc_ph = 0;
       bool ok = true;
       for (int t = cta; t < num_tiles && ok; t += gemm_ctas) {
-        if (!mbar_wait(&ctl->acc_empty[acc], acc_ph ^ 1, abort_flag, p.status, 620)) { ok = false; break; }
+        if (!mbar_wait(&ctl->acc_empty[acc], acc_ph ^ 1, abort_flag, p.status, 620, LOCAL_WAIT_CYCLES)) { ok = false; break; }
         tc_fence_after();
         for (int kb = 0; kb < num_kb; ++kb) {
-          if (!mbar_wait(&ctl->full[s], ph, abort_flag, p.status, 621)) { ok = false; break; }
+          if (!mbar_wait(&ctl->full[s], ph, abort_flag, p.status, 621, LOCAL_WAIT_CYCLES)) { ok = false; break; }
           tc_fence_after();
           mma_stage<B_MN>(tmem_base + acc * ACC_COLS, smem_u32(sA + s * A_STAGE_BYTES), smem_u32(sB + s * B_STAGE_BYTES), kb == 0);
           umma_commit(&ctl->empty[s]);
@@ -267,7 +270,7 @@ ag_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       int tm, tn;
       tile_coords(t, p.tiles_m, p.tiles_n, tm, tn);
       tm = (tm + rot) % p.tiles_m;
-      if (!mbar_wait(&ctl->acc_full[acc], acc_ph, abort_flag, p.status, 630)) { ok = false; break; }
+      if (!mbar_wait(&ctl->acc_full[acc], acc_ph, abort_flag, p.status, 630, LOCAL_WAIT_CYCLES)) { ok = false; break; }
       tc_fence_after();
       const int row = tm * BM + quarter * 32 + lane;
       const uint32_t taddr = tmem_base + acc * ACC_COLS + ((uint32_t)(quarter * 32) << 16);
@@ -359,7 +362,7 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         tile_coords(t, p.tiles_m, p.tiles_n, tm, tn);
         tm = (tm + rot) % p.tiles_m;
         for (int kb = 0; kb < num_kb; ++kb) {
-          if (!mbar_wait(&ctl->empty[s], ph ^ 1, abort_flag, p.status, 700)) { ok = false; break; }
+          if (!mbar_wait(&ctl->empty[s], ph ^ 1, abort_flag, p.status, 700, LOCAL_WAIT_CYCLES)) { ok = false; break; }
           load_stage<B_MN>(sA + s * A_STAGE_BYTES, sB + s * B_STAGE_BYTES, &tmap_a, &tmap_b, &ctl->full[s], tm * BM, tn * BN, kb * BK);
           if (++s == STAGES) { s = 0; ph ^= 1; }
         }
@@ -372,10 +375,10 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       uint32_t ph = 0, acc_ph = 0;
       bool ok = true;
       for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
-        if (!mbar_wait(&ctl->acc_empty[acc], acc_ph ^ 1, abort_flag, p.status, 710)) { ok = false; break; }
+        if (!mbar_wait(&ctl->acc_empty[acc], acc_ph ^ 1, abort_flag, p.status, 710, LOCAL_WAIT_CYCLES)) { ok = false; break; }
         tc_fence_after();
         for (int kb = 0; kb < num_kb; ++kb) {
-          if (!mbar_wait(&ctl->full[s], ph, abort_flag, p.status, 711)) { ok = false; break; }
+          if (!mbar_wait(&ctl->full[s], ph, abort_flag, p.status, 711, LOCAL_WAIT_CYCLES)) { ok = false; break; }
           tc_fence_after();
           mma_stage<B_MN>(tmem_base + acc * ACC_COLS, smem_u32(sA + s * A_STAGE_BYTES), smem_u32(sB + s * B_STAGE_BYTES), kb == 0);
           umma_commit(&ctl->empty[s]);
@@ -396,7 +399,7 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       int tm, tn;
       tile_coords(t, p.tiles_m, p.tiles_n, tm, tn);
       tm = (tm + rot) % p.tiles_m;
-      if (!mbar_wait(&ctl->acc_full[acc], acc_ph, abort_flag, p.status, 720)) { ok = false; break; }
+      if (!mbar_wait(&ctl->acc_full[acc], acc_ph, abort_flag, p.status, 720, LOCAL_WAIT_CYCLES)) { ok = false; break; }
       tc_fence_after();
       const int owner = tm / p.blocks_per_rank;
       const int lrow = (tm - owner * p.blocks_per_rank) * BM + quarter * 32 + lane;      // row inside the owner's shard

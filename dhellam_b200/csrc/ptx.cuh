@@ -110,7 +110,8 @@ __device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t* bar, uint32_t pa
 // Bounded wait.  `abort_flag` is a CTA-shared int that any role sets when it gives
 // up, so that the remaining roles leave their own waits quickly.
 template <bool kCluster = false>
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, DeviceStatus* st, int where) {
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, DeviceStatus* st, int where,
+                                          long long budget = DH_WAIT_BUDGET_CYCLES) {
   if (kCluster ? mbar_try_wait_cluster(bar, parity) : mbar_try_wait(bar, parity)) return true;
   long long t0 = clock64();
   uint32_t spins = 0;
@@ -118,7 +119,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
     if (kCluster ? mbar_try_wait_cluster(bar, parity) : mbar_try_wait(bar, parity)) return true;
     if ((++spins & 0xff) == 0) {
       if (*abort_flag) return false;
-      if (clock64() - t0 > DH_WAIT_BUDGET_CYCLES) {
+      if (clock64() - t0 > budget) {
         *abort_flag = 1;
         report_error(st, ERR_MBAR_TIMEOUT, where, (int)parity);
         return false;

@@ -24,7 +24,11 @@ from .strategy import Block, Strategy, split_budget
 class StreamSet:
     """Three CUDA streams (forward compute, backward compute, communication)."""
 
-    def __init__(self, device=None, single_stream: bool = False):
+    def __init__(self, device=None, single_stream: bool = False, compute_streams: int = 2):
+        """``compute_streams = 1`` issues both strands' compute ops to one stream in schedule
+        order (collectives still overlap from the communication stream), which is how the
+        reference actually trains (it aliases its second stream to the first,
+        dhellam/core/dsllm.py:59-61); ``2`` lets compute kernels of the two strands co-run."""
         self.cuda = device is not None and torch.device(device).type == "cuda"
         if self.cuda:
             with torch.cuda.device(device):
@@ -33,7 +37,7 @@ class StreamSet:
                     self.s1 = self.s2 = self.s3 = s
                 else:
                     self.s1 = torch.cuda.Stream()
-                    self.s2 = torch.cuda.Stream()
+                    self.s2 = torch.cuda.Stream() if compute_streams >= 2 else self.s1
                     self.s3 = torch.cuda.Stream()
         else:
             self.s1 = self.s2 = self.s3 = None

@@ -40,7 +40,7 @@ class Trainer:
         if strategy is None and train.schedule_config:
             strategy = Strategy.load(train.schedule_config)
         self.engine = DoubleStrandEngine(self.model, self.env, strategy, single_stream=single_stream or not train.dhellam,
-                                         profile=profile, trace=trace)
+                                         profile=profile, trace=trace, compute_streams=train.compute_streams)
         self.optimizer = MixedPrecisionAdam(self.model, train, self.ps, distributed=distributed_optimizer)
         self.iteration = 0
         self.last_grad_norm = None
