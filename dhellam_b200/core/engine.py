@@ -90,6 +90,7 @@ class DoubleStrandEngine:
         self.streams = StreamSet(env.device if env.device.type == "cuda" else None, single_stream=single_stream,
                                  compute_streams=compute_streams)
         self.executor = Executor(self.program, strategy or Strategy(), self.streams, profile=profile, trace=trace)
+        env.streams = self.streams
         self.acts: Dict[tuple, dict] = {}
         self.head_saved: Dict[int, dict] = {}
         self.fwd_done: Dict[int, object] = {}

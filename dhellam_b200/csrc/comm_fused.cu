@@ -55,6 +55,8 @@ struct __align__(8) Control {
   int abort_flag;
 };
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
+constexpr int RS_STAGE_BYTES = 4 * 32 * 256;
+constexpr int RS_SMEM_BYTES = SMEM_BYTES + RS_STAGE_BYTES;
 
 __device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int& tm, int& tn) {
   const int band = GROUP_M * tiles_n;
@@ -110,8 +112,8 @@ __device__ __forceinline__ void mma_stage(uint32_t tmem_acc, uint32_t a_base, ui
 struct AgParams {
   const __nv_bfloat16* shard;            // [rows_per_rank, K] this rank's rows (any memory)
   __nv_bfloat16* stage[MAX_RANKS];       // staging [M, K] on every rank (stage[rank] is local)
+  __nv_bfloat16* stage_mc;               // the same staging through the NVSwitch multicast address (null: unicast stores)
   uint32_t* count[MAX_RANKS];            // per row-block arrival counters on every rank
-  __nv_bfloat16* saved;                  // [M, K] regular tensor kept for the weight gradient (may be null)
   __nv_bfloat16* d;                      // output [M, N]
   long long ldd;
   int M, N, K;
@@ -122,15 +124,68 @@ struct AgParams {
   DeviceStatus* status;
 };
 
-__device__ __forceinline__ void copy_rows_16B(const __nv_bfloat16* src, __nv_bfloat16* dst, int rows, int cols, long long ld, int c0, int cw) {
-  // copies rows x [c0, c0+cw) (cw multiple of 8) with the whole CTA
+// One 16-byte store that the NVSwitch replicates into the buffer of every rank of the group.
+__device__ __forceinline__ void multimem_st_v4(void* mc_addr, const uint4& v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mc_addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
+               : "memory");
+}
+
+// Pushes this rank's shard into every rank's staging buffer and raises the row-block counters.
+// Work items are (row block, column slice); `cta`/`ncta` spread them over the calling CTAs.
+// Four independent 16-byte loads are in flight per thread; with the multicast address one
+// store reaches all ranks, otherwise the registers are stored to each rank in turn (the rank
+// that consumes this shard earliest first).
+__device__ __forceinline__ void push_shard(const AgParams& p, int cta, int ncta) {
+  constexpr int U = 4;
+  const int items = p.blocks_per_rank * p.slices;
+  const int cw = p.K / p.slices;                            // columns per slice (multiple of 8)
   const int vec_per_row = cw >> 3;
-  const int total = rows * vec_per_row;
-  for (int i = threadIdx.x; i < total; i += blockDim.x) {
-    const int r = i / vec_per_row, c = i - r * vec_per_row;
-    const long long off = (long long)r * ld + c0 + c * 8;
-    st_v4(dst + off, ld_v4(src + off));
+  const int total = BM * vec_per_row;
+  for (int it = cta; it < items; it += ncta) {
+    const int lb = it / p.slices, sl = it - lb * p.slices;
+    const int gb = p.rank * p.blocks_per_rank + lb;         // global row block
+    const long long src_base = (long long)lb * BM * p.K + (long long)sl * cw;
+    const long long dst_base = (long long)gb * BM * p.K + (long long)sl * cw;
+    for (int i0 = threadIdx.x; i0 < total; i0 += blockDim.x * U) {
+      uint4 v[U];
+      long long off[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int i = i0 + u * blockDim.x;
+        if (i < total) {
+          const int r = i / vec_per_row, c = i - r * vec_per_row;
+          off[u] = (long long)r * p.K + c * 8;
+          v[u] = ld_nc_v4(p.shard + src_base + off[u]);
+        }
+      }
+      if (p.stage_mc != nullptr) {
+#pragma unroll
+        for (int u = 0; u < U; ++u)
+          if (i0 + u * blockDim.x < total) multimem_st_v4(p.stage_mc + dst_base + off[u], v[u]);
+      } else {
+        for (int j = 0; j < p.world; ++j) {
+          __nv_bfloat16* dst = p.stage[(p.rank - j + p.world) % p.world] + dst_base;
+#pragma unroll
+          for (int u = 0; u < U; ++u)
+            if (i0 + u * blockDim.x < total) *reinterpret_cast<uint4*>(dst + off[u]) = v[u];
+        }
+      }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      asm volatile("fence.acq_rel.sys;" ::: "memory");
+      for (int j = 0; j < p.world; ++j) red_add_release_sys(p.count[(p.rank - j + p.world) % p.world] + gb, 1u);
+    }
   }
+}
+
+// Stand-alone all-gather: only the push (used to re-gather a saved shard for a weight gradient).
+__global__ void __launch_bounds__(256) ag_push_kernel(const AgParams p) { push_shard(p, blockIdx.x, gridDim.x); }
+
+// Waits (bounded) until `n` counters have reached `target`; a later kernel on the same stream
+// then reads the staged rows.
+__global__ void __launch_bounds__(256) wait_counters_kernel(const uint32_t* count, int n, uint32_t target, DeviceStatus* st) {
+  for (int i = threadIdx.x; i < n; i += blockDim.x) wait_counter_sys(count + i, target, nullptr, st, 640);
 }
 
 template <bool B_MN>
@@ -145,53 +200,7 @@ ag_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 
   // ------------------------------------------------------------------ copy CTAs
   if ((int)blockIdx.x < p.copy_ctas) {
-    __shared__ int s_ok;
-    const int items = p.blocks_per_rank * p.slices;
-    const int cw = p.K / p.slices;                          // columns per slice (multiple of 8)
-    // phase 1: push my shard to every rank's staging (local first), one (row block, slice) at a time
-    for (int it = blockIdx.x; it < items; it += p.copy_ctas) {
-      const int lb = it / p.slices, sl = it - lb * p.slices;
-      const int gb = p.rank * p.blocks_per_rank + lb;       // global row block
-      const long long row0 = (long long)lb * BM;
-      const int vec_per_row = cw >> 3;
-      const int total = BM * vec_per_row;
-      for (int i = threadIdx.x; i < total; i += blockDim.x) {
-        const int r = i / vec_per_row, c = i - r * vec_per_row;
-        const long long src_off = (row0 + r) * p.K + (long long)sl * cw + c * 8;
-        const long long dst_off = ((long long)gb * BM + r) * p.K + (long long)sl * cw + c * 8;
-        const uint4 v = ld_nc_v4(p.shard + src_off);
-        // the destination that consumes this shard earliest is rank-1, then rank-2, ...
-#pragma unroll 1
-        for (int j = 0; j < p.world; ++j) {
-          const int dst = (p.rank - j + p.world) % p.world;
-          st_v4(p.stage[dst] + dst_off, v);
-        }
-        if (p.saved != nullptr) st_v4(p.saved + dst_off, v);
-      }
-      __syncthreads();
-      if (threadIdx.x == 0) {
-        fence_proxy_async_all();
-        for (int j = 0; j < p.world; ++j) {
-          const int dst = (p.rank - j + p.world) % p.world;
-          red_add_release_sys(p.count[dst] + gb, 1u);
-        }
-      }
-    }
-    // phase 2: keep a copy of every remote block as it arrives
-    if (p.saved != nullptr) {
-      const int remote_items = (p.world - 1) * p.blocks_per_rank;
-      for (int it = blockIdx.x; it < remote_items; it += p.copy_ctas) {
-        const int src = (p.rank + 1 + it / p.blocks_per_rank) % p.world;
-        const int gb = src * p.blocks_per_rank + it % p.blocks_per_rank;
-        if (threadIdx.x == 0) s_ok = wait_counter_sys(p.count[p.rank] + gb, p.target, nullptr, p.status, 600) ? 1 : 0;
-        __syncthreads();
-        const int ok = s_ok;
-        __syncthreads();
-        if (!ok) break;
-        const long long base = (long long)gb * BM * p.K;
-        copy_rows_16B(p.stage[p.rank] + base, p.saved + base, BM, p.K, p.K, 0, p.K);
-      }
-    }
+    push_shard(p, blockIdx.x, p.copy_ctas);
     return;
   }
 
@@ -329,7 +338,8 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sA = smem;
   uint8_t* sB = smem + STAGES * A_STAGE_BYTES;
-  Control* ctl = reinterpret_cast<Control*>(smem + STAGES * STAGE_BYTES);
+  uint8_t* sStage = smem + STAGES * STAGE_BYTES;                       // 4 epilogue warps x 32 rows x 256 B
+  Control* ctl = reinterpret_cast<Control*>(smem + STAGES * STAGE_BYTES + RS_STAGE_BYTES);
   __shared__ int s_ok;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int num_tiles = p.tiles_m * p.tiles_n;
@@ -402,18 +412,22 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       if (!mbar_wait(&ctl->acc_full[acc], acc_ph, abort_flag, p.status, 720, LOCAL_WAIT_CYCLES)) { ok = false; break; }
       tc_fence_after();
       const int owner = tm / p.blocks_per_rank;
-      const int lrow = (tm - owner * p.blocks_per_rank) * BM + quarter * 32 + lane;      // row inside the owner's shard
+      const int lrow0 = (tm - owner * p.blocks_per_rank) * BM + quarter * 32;            // first of this warp's 32 rows in the owner's shard
       const uint32_t taddr = tmem_base + acc * ACC_COLS + ((uint32_t)(quarter * 32) << 16);
-      __nv_bfloat16* slot = p.part[owner] + ((long long)p.rank * p.rows_per_rank + lrow) * p.N;
+      __nv_bfloat16* slot = p.part[owner] + ((long long)p.rank * p.rows_per_rank + lrow0) * p.N;
+      // The accumulator rows are staged through shared memory so that one warp store covers
+      // two whole 256-byte row segments: NVLink moves 128..256-byte payloads efficiently,
+      // while 32 scattered 16-byte segments per store would not.
+      uint8_t* stg = sStage + (warp - 2) * (32 * 256);
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        const int col0 = tn * BN + c * 32;
-        if (col0 >= p.N) break;
-        uint32_t r[32];
-        tmem_ld32(taddr + c * 32, r);
-        tmem_ld_wait();
-        __nv_bfloat16* dst = slot + col0;
-        if (col0 + 32 <= p.N) {
+      for (int g = 0; g < BN / 128; ++g) {
+        const int colg = tn * BN + g * 128;
+        if (colg >= p.N) break;
+#pragma unroll
+        for (int c4 = 0; c4 < 4; ++c4) {
+          uint32_t r[32];
+          tmem_ld32(taddr + g * 128 + c4 * 32, r);
+          tmem_ld_wait();
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
             uint4 v;
@@ -421,13 +435,19 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
             v.y = pack_bf16x2(__uint_as_float(r[8 * j + 2]), __uint_as_float(r[8 * j + 3]));
             v.z = pack_bf16x2(__uint_as_float(r[8 * j + 4]), __uint_as_float(r[8 * j + 5]));
             v.w = pack_bf16x2(__uint_as_float(r[8 * j + 6]), __uint_as_float(r[8 * j + 7]));
-            st_v4(dst + 8 * j, v);
+            const int chunk = c4 * 4 + j;
+            *reinterpret_cast<uint4*>(stg + lane * 256 + ((chunk ^ (lane & 15)) << 4)) = v;
           }
-        } else {
-#pragma unroll
-          for (int j = 0; j < 32; ++j)
-            if (col0 + j < p.N) dst[j] = __float2bfloat16(__uint_as_float(r[j]));
         }
+        __syncwarp();
+#pragma unroll 4
+        for (int i = 0; i < 16; ++i) {
+          const int rr = 2 * i + (lane >> 4), ch = lane & 15;
+          const uint4 v = *reinterpret_cast<const uint4*>(stg + rr * 256 + ((ch ^ (rr & 15)) << 4));
+          const int col = colg + ch * 8;
+          if (col < p.N) *reinterpret_cast<uint4*>(slot + (long long)rr * p.N + col) = v;
+        }
+        __syncwarp();
       }
       tc_fence_before();
       // this warp's 32 rows of the tile are stored -> tell the owner (four arrivals per tile)
@@ -471,9 +491,9 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 }
 
 template <typename Kern>
-static int configure(Kern kern, bool& done) {
+static int configure(Kern kern, bool& done, int smem_bytes = SMEM_BYTES) {
   if (done) return 0;
-  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
   if (e != cudaSuccess) { set_last_error("fused GEMM: shared memory opt-in failed: %s", cudaGetErrorString(e)); return (int)e; }
   done = true;
   return 0;
@@ -487,66 +507,93 @@ using namespace dh::fused;
 
 extern "C" {
 
-// stage_ptrs / count_ptrs: `world` device pointers (index = rank).  The local shard has
-// rows_per_rank = M / world rows; rows_per_rank must be a multiple of 128.
-int dh_ag_gemm_bf16(const void* shard, void* const* stage_ptrs, void* const* count_ptrs, void* saved, const void* b, int64_t ldb,
-                    int b_mn_major, void* d, int64_t ldd, int M, int N, int K, int rank, int world, int copy_ctas, unsigned target_base,
-                    int sm_budget, cudaStream_t stream) {
-  if (world < 2 || world > MAX_RANKS) { set_last_error("dh_ag_gemm_bf16: world size %d not in [2, %d]", world, MAX_RANKS); return (int)cudaErrorInvalidValue; }
-  if (M % (world * BM) != 0 || K % 64 != 0) { set_last_error("dh_ag_gemm_bf16: M must divide by world*128 and K by 64 (M=%d K=%d)", M, K); return (int)cudaErrorInvalidValue; }
-  if ((ldd % 8) != 0) { set_last_error("dh_ag_gemm_bf16: ldd must be a multiple of 8"); return (int)cudaErrorInvalidValue; }
-  const CUtensorMap* ta = get_tmap_2d(stage_ptrs[rank], 2, (uint64_t)K, (uint64_t)M, (uint64_t)K * 2, BK, BM, true);
-  const CUtensorMap* tb = b_mn_major ? get_tmap_2d(b, 2, (uint64_t)N, (uint64_t)K, (uint64_t)ldb * 2, 64, BK, true)
-                                     : get_tmap_2d(b, 2, (uint64_t)K, (uint64_t)N, (uint64_t)ldb * 2, BK, BN, true);
-  if (!ta || !tb) return (int)cudaErrorInvalidValue;
-  AgParams p;
+// Counter increments that one all-gather adds to every row-block counter: the number of
+// column slices a row block is pushed in.  A pure function of the shape, so that the fused
+// kernel, the stand-alone push and the host agree without exchanging state.
+int dh_ag_slices(int M, int K, int world) {
+  const int bpr = M / world / BM;
+  int slices = 1;
+  while (bpr * slices < 32 && (K / (slices * 2)) % 8 == 0 && slices < 64) slices *= 2;
+  return slices;
+}
+
+static int fill_ag_params(AgParams& p, const char* who, const void* shard, void* const* stage_ptrs, void* const* count_ptrs, void* stage_mc,
+                          int M, int K, int rank, int world, unsigned target_base) {
+  if (world < 2 || world > MAX_RANKS) { set_last_error("%s: world size %d not in [2, %d]", who, world, MAX_RANKS); return (int)cudaErrorInvalidValue; }
+  if (M % (world * BM) != 0 || K % 64 != 0) { set_last_error("%s: M must divide by world*128 and K by 64 (M=%d K=%d)", who, M, K); return (int)cudaErrorInvalidValue; }
   p.shard = (const __nv_bfloat16*)shard;
   for (int i = 0; i < MAX_RANKS; ++i) {
     p.stage[i] = i < world ? (__nv_bfloat16*)stage_ptrs[i] : nullptr;
     p.count[i] = i < world ? (uint32_t*)count_ptrs[i] : nullptr;
   }
-  p.saved = (__nv_bfloat16*)saved;
-  p.d = (__nv_bfloat16*)d;
-  p.ldd = ldd;
-  p.M = M; p.N = N; p.K = K;
+  p.stage_mc = (__nv_bfloat16*)stage_mc;
+  p.d = nullptr;
+  p.ldd = 0;
+  p.M = M; p.N = 0; p.K = K;
   p.tiles_m = M / BM;
-  p.tiles_n = (N + BN - 1) / BN;
+  p.tiles_n = 0;
   p.rank = rank; p.world = world;
   p.rows_per_rank = M / world;
   p.blocks_per_rank = p.rows_per_rank / BM;
+  p.copy_ctas = 0;
+  p.slices = dh_ag_slices(M, K, world);
+  p.target = target_base + (unsigned)p.slices;            // target_base = counter value before this call
+  p.status = reinterpret_cast<DeviceStatus*>(dh_status_device_ptr());
+  return 0;
+}
+
+// stage_ptrs / count_ptrs: `world` device pointers (index = rank); stage_mc: multicast address
+// of the same staging buffer or null.  The local shard has M / world rows (a multiple of 128).
+// After the call the local staging buffer holds the gathered [M, K] operand.
+int dh_ag_gemm_bf16(const void* shard, void* const* stage_ptrs, void* const* count_ptrs, void* stage_mc, const void* b, int64_t ldb,
+                    int b_mn_major, void* d, int64_t ldd, int M, int N, int K, int rank, int world, int copy_ctas, unsigned target_base,
+                    int sm_budget, cudaStream_t stream) {
+  AgParams p;
+  int rc = fill_ag_params(p, "dh_ag_gemm_bf16", shard, stage_ptrs, count_ptrs, stage_mc, M, K, rank, world, target_base);
+  if (rc) return rc;
+  if ((ldd % 8) != 0) { set_last_error("dh_ag_gemm_bf16: ldd must be a multiple of 8"); return (int)cudaErrorInvalidValue; }
+  const CUtensorMap* ta = get_tmap_2d(stage_ptrs[rank], 2, (uint64_t)K, (uint64_t)M, (uint64_t)K * 2, BK, BM, true);
+  const CUtensorMap* tb = b_mn_major ? get_tmap_2d(b, 2, (uint64_t)N, (uint64_t)K, (uint64_t)ldb * 2, 64, BK, true)
+                                     : get_tmap_2d(b, 2, (uint64_t)K, (uint64_t)N, (uint64_t)ldb * 2, BK, BN, true);
+  if (!ta || !tb) return (int)cudaErrorInvalidValue;
+  p.d = (__nv_bfloat16*)d;
+  p.ldd = ldd;
+  p.N = N;
+  p.tiles_n = (N + BN - 1) / BN;
   const int sms = dh_sm_count();
   int budget = (sm_budget <= 0 || sm_budget > sms) ? sms : sm_budget;
-  if (copy_ctas <= 0) copy_ctas = 16;
+  if (copy_ctas <= 0) copy_ctas = 8;
   if (copy_ctas > budget / 2) copy_ctas = budget / 2;
   p.copy_ctas = copy_ctas;
-  // enough (row block, column slice) items to keep every copy CTA busy; slices divide K/8 evenly
-  int slices = 1;
-  while (p.blocks_per_rank * slices < 2 * copy_ctas && (K / (slices * 2)) % 8 == 0 && slices < 64) slices *= 2;
-  p.slices = slices;
-  p.target = target_base + (unsigned)slices;             // counters grow by `slices` per call; target_base = value before it
-  p.status = reinterpret_cast<DeviceStatus*>(dh_status_device_ptr());
-  const int grid = budget;
   static bool c0 = false, c1 = false;
-  int rc = b_mn_major ? configure(ag_gemm_kernel<true>, c1) : configure(ag_gemm_kernel<false>, c0);
+  rc = b_mn_major ? configure(ag_gemm_kernel<true>, c1) : configure(ag_gemm_kernel<false>, c0);
   if (rc) return rc;
-  if (b_mn_major) ag_gemm_kernel<true><<<grid, THREADS, SMEM_BYTES, stream>>>(*ta, *tb, p);
-  else ag_gemm_kernel<false><<<grid, THREADS, SMEM_BYTES, stream>>>(*ta, *tb, p);
+  if (b_mn_major) ag_gemm_kernel<true><<<budget, THREADS, SMEM_BYTES, stream>>>(*ta, *tb, p);
+  else ag_gemm_kernel<false><<<budget, THREADS, SMEM_BYTES, stream>>>(*ta, *tb, p);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) set_last_error("dh_ag_gemm_bf16 launch failed: %s", cudaGetErrorString(e));
   return (int)e;
 }
 
-// Number of counter increments one ag_gemm call adds to every row-block counter, so the
-// caller can keep `target_base` (= number of calls so far on this buffer) as the only state.
-int dh_ag_gemm_slices(int M, int K, int world, int copy_ctas, int sm_budget) {
-  const int sms = dh_sm_count();
-  int budget = (sm_budget <= 0 || sm_budget > sms) ? sms : sm_budget;
-  if (copy_ctas <= 0) copy_ctas = 16;
-  if (copy_ctas > budget / 2) copy_ctas = budget / 2;
-  const int bpr = M / world / BM;
-  int slices = 1;
-  while (bpr * slices < 2 * copy_ctas && (K / (slices * 2)) % 8 == 0 && slices < 64) slices *= 2;
-  return slices;
+// Stand-alone all-gather of a row shard into every rank's staging buffer (push only; pair it
+// with dh_wait_counters on the consumer's stream).
+int dh_ag_push(const void* shard, void* const* stage_ptrs, void* const* count_ptrs, void* stage_mc, int M, int K, int rank, int world,
+               int ctas, unsigned target_base, cudaStream_t stream) {
+  AgParams p;
+  int rc = fill_ag_params(p, "dh_ag_push", shard, stage_ptrs, count_ptrs, stage_mc, M, K, rank, world, target_base);
+  if (rc) return rc;
+  if (ctas <= 0) ctas = 16;
+  ag_push_kernel<<<ctas, 256, 0, stream>>>(p);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) set_last_error("dh_ag_push launch failed: %s", cudaGetErrorString(e));
+  return (int)e;
+}
+
+int dh_wait_counters(const void* counters, int n, unsigned target, cudaStream_t stream) {
+  wait_counters_kernel<<<1, 256, 0, stream>>>((const uint32_t*)counters, n, target, reinterpret_cast<DeviceStatus*>(dh_status_device_ptr()));
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) set_last_error("dh_wait_counters launch failed: %s", cudaGetErrorString(e));
+  return (int)e;
 }
 
 // part_ptrs / arrived_ptrs: `world` device pointers.  A is [M, K] local, the result is this
@@ -579,10 +626,10 @@ int dh_gemm_rs_bf16(const void* a, int64_t lda, const void* b, int64_t ldb, int 
   const int num_tiles = p.tiles_m * p.tiles_n;
   const int grid = num_tiles < budget ? num_tiles : budget;
   static bool c0 = false, c1 = false;
-  int rc = b_mn_major ? configure(gemm_rs_kernel<true>, c1) : configure(gemm_rs_kernel<false>, c0);
+  int rc = b_mn_major ? configure(gemm_rs_kernel<true>, c1, RS_SMEM_BYTES) : configure(gemm_rs_kernel<false>, c0, RS_SMEM_BYTES);
   if (rc) return rc;
-  if (b_mn_major) gemm_rs_kernel<true><<<grid, THREADS, SMEM_BYTES, stream>>>(*ta, *tb, p);
-  else gemm_rs_kernel<false><<<grid, THREADS, SMEM_BYTES, stream>>>(*ta, *tb, p);
+  if (b_mn_major) gemm_rs_kernel<true><<<grid, THREADS, RS_SMEM_BYTES, stream>>>(*ta, *tb, p);
+  else gemm_rs_kernel<false><<<grid, THREADS, RS_SMEM_BYTES, stream>>>(*ta, *tb, p);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) set_last_error("dh_gemm_rs_bf16 launch failed: %s", cudaGetErrorString(e));
   return (int)e;

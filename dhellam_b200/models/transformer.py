@@ -135,12 +135,14 @@ def f_allgather_attn(run):
 def f_gemm_attn_c(run):
     env, p = run.env, run.params
     if env.fused_tp:
-        qkv, full = env.fused.ag_gemm(_use(run, run.v.pop("ln1_shard")), p.column_attn_weight, "attn_c",
-                                      sm_budget=run.budget("gemm_attn_c"))
+        # the gathered operand is not kept: the backward re-gathers the (8x smaller) shard
+        shard = _use(run, run.v.pop("ln1_shard"))
+        qkv, _ = env.fused.ag_gemm(shard, p.column_attn_weight, "attn_c", sm_budget=run.budget("gemm_attn_c"))
+        run.acts["ln1_shard"] = shard
     else:
         full = _use(run, run.v.pop("ln1_full"))
         qkv = G.gemm_nt(full, p.column_attn_weight, sm_budget=run.budget("gemm_attn_c"))
-    run.acts["ln1_full"] = full
+        run.acts["ln1_full"] = full
     run.v["qkv"] = qkv
 
 
@@ -211,12 +213,14 @@ def f_allgather_mlp(run):
 def f_gemm_mlp_c(run):
     env, p = run.env, run.params
     if env.fused_tp:
-        fc1, full = env.fused.ag_gemm(_use(run, run.v.pop("ln2_shard")), p.column_mlp_weight, "mlp_c",
-                                      sm_budget=run.budget("gemm_mlp_c"))
+        shard = _use(run, run.v.pop("ln2_shard"))
+        fc1, _ = env.fused.ag_gemm(shard, p.column_mlp_weight, "mlp_c", sm_budget=run.budget("gemm_mlp_c"))
+        run.acts["ln2_shard"] = shard
     else:
         full = _use(run, run.v.pop("ln2_full"))
         fc1 = G.gemm_nt(full, p.column_mlp_weight, sm_budget=run.budget("gemm_mlp_c"))
-    run.acts["ln2_full"], run.acts["fc1"] = full, fc1
+        run.acts["ln2_full"] = full
+    run.acts["fc1"] = fc1
     run.v["fc1"] = fc1
 
 
@@ -256,6 +260,12 @@ def f_bda_mlp(run):
 def b_bda_mlp_bwd(run):
     env = run.env
     dout = _use(run, run.v["dout"])
+    if env.fused_tp and "ln2_shard" in run.acts:
+        # re-gather the inputs of the two column-parallel layers for their weight gradients;
+        # the pushes run on the communication stream under the first backward GEMMs
+        comm = env.streams.s3 if getattr(env, "streams", None) is not None and env.streams.cuda else None
+        env.fused.gather_start(run.acts["ln2_shard"], "regather_mlp", stream=comm)
+        env.fused.gather_start(run.acts["ln1_shard"], "regather_attn", stream=comm)
     run.v["d_fc2"] = BDA.bda_bwd(dout, env.cfg.hidden_dropout, _seed(run, 2), env.training, sm_budget=run.budget("bda_mlp_bwd"))
     run.v["res_grad"] = dout
 
@@ -306,8 +316,12 @@ def b_gemm_dgrad_mlp_c(run):
 
 def b_gemm_wgrad_mlp_c(run):
     p = run.params
-    G.gemm_tn_acc(_use(run, run.v["d_fc1"]), _use(run, run.acts.pop("ln2_full")), p.column_mlp_weight.main_grad,
-                  sm_budget=run.budget("gemm_wgrad_mlp_c"))
+    if run.env.fused_tp:
+        run.acts.pop("ln2_shard")
+        full = run.env.fused.gather_wait("regather_mlp")
+    else:
+        full = _use(run, run.acts.pop("ln2_full"))
+    G.gemm_tn_acc(_use(run, run.v["d_fc1"]), full, p.column_mlp_weight.main_grad, sm_budget=run.budget("gemm_wgrad_mlp_c"))
 
 
 def b_reduce_scatter_mlp_c_bwd(run):
@@ -385,8 +399,12 @@ def b_gemm_dgrad_attn_c(run):
 
 def b_gemm_wgrad_attn_c(run):
     p = run.params
-    G.gemm_tn_acc(_use(run, run.v["d_qkv"]), _use(run, run.acts.pop("ln1_full")), p.column_attn_weight.main_grad,
-                  sm_budget=run.budget("gemm_wgrad_attn_c"))
+    if run.env.fused_tp:
+        run.acts.pop("ln1_shard")
+        full = run.env.fused.gather_wait("regather_attn")
+    else:
+        full = _use(run, run.acts.pop("ln1_full"))
+    G.gemm_tn_acc(_use(run, run.v["d_qkv"]), full, p.column_attn_weight.main_grad, sm_budget=run.budget("gemm_wgrad_attn_c"))
 
 
 def b_reduce_scatter_attn_c_bwd(run):

@@ -1,26 +1,33 @@
 """Tensor-parallel collectives fused into the GEMM kernels over NVLink peer memory.
 
-``FusedTP`` owns the symmetric memory of one tensor-parallel group (double-buffered
-all-gather staging, double-buffered reduce-scatter partial slots, arrival counters) and
-launches the two fused kernels of ``csrc/comm_fused.cu``:
+``FusedTP`` owns the symmetric memory of one tensor-parallel group and launches the kernels
+of ``csrc/comm_fused.cu``:
 
-* ``ag_gemm(shard, w)``  = ``all_gather(shard) @ op(w)`` and the gathered operand itself
-  (kept for the weight gradient), replacing ``allgather_* + gemm_*`` of the reference
+* ``ag_gemm(shard, w, tag)`` = ``all_gather(shard) @ op(w)``; the gathered operand stays in
+  the local staging buffer of ``tag`` and is returned as a view (valid until the second next
+  call with the same tag), replacing ``allgather_* + gemm_*`` of the reference
   (dhellam/core/dstb.py:412-425 + :80-107);
-* ``gemm_rs(a, w)``      = ``reduce_scatter(a @ op(w))``, replacing ``gemm_* + reduce_scatter``
-  (dstb.py:407-410).
+* ``gemm_rs(a, w)`` = ``reduce_scatter(a @ op(w))``, replacing ``gemm_* + reduce_scatter``
+  (dstb.py:407-410);
+* ``gather_start(shard, tag)`` / ``gather_wait(tag)``: the all-gather alone, pushed from a
+  few CTAs on the communication stream while other kernels run; used to re-gather the
+  sequence-parallel input of a column-parallel layer for its weight gradient instead of
+  keeping the gathered activation alive from the forward pass.
 
-Fused kernels wait on data that peers produce inside the *same* kernel, so two of them must
-never run in a different order on different ranks.  Every launch is therefore chained to the
-previous fused launch with an event, whichever stream it is on; other kernels still overlap
-with them freely.
+Every staging buffer is double-buffered per tag, with monotonically increasing arrival
+counters.  Kernels that wait for peers inside the kernel (``ag_gemm``, ``gemm_rs``) are
+chained to one another with events so that all ranks run them one at a time in the same
+order; pure pushes do not wait for anybody and are not chained.
 
-The peer pointers come from ``torch.distributed._symmetric_memory`` (one allocation, one
-rendezvous); NCCL stays the transport of everything that is not a named fused path.
+The NVSwitch multicast address of the buffer (``multimem.st``: one store reaches all ranks)
+is used when the platform provides it and ``DHELLAM_MULTIMEM`` is not ``0``; otherwise the
+push stores to every peer in turn.  Peer pointers come from
+``torch.distributed._symmetric_memory`` (one allocation, one rendezvous).
 """
 from __future__ import annotations
 
 import ctypes
+import os
 from ctypes import c_int, c_int64, c_uint, c_void_p
 
 import torch
@@ -28,17 +35,20 @@ import torch.distributed as dist
 
 from .. import kernels as K
 
+AG_TAGS = ("attn_c", "mlp_c", "attn_l_bwd", "mlp_l_bwd", "regather_attn", "regather_mlp", "head")
+
 
 def _align(n, a=1024):
     return (n + a - 1) // a * a
 
 
 class FusedTP:
-    def __init__(self, ps, cfg, train, device, max_rows: int | None = None, width: int | None = None, copy_ctas: int = 16):
+    def __init__(self, ps, cfg, train, device, max_rows: int | None = None, width: int | None = None, copy_ctas: int = 8,
+                 push_ctas: int = 16):
         import torch.distributed._symmetric_memory as symm_mem
         self.ps, self.device = ps, torch.device(device)
         self.world, self.rank = ps.tp, ps.tp_rank
-        self.copy_ctas = copy_ctas
+        self.copy_ctas, self.push_ctas = copy_ctas, push_ctas
         rows = max_rows or train.micro_batch_size * cfg.seq_length // max(ps.cp, 1)
         width = width or cfg.hidden_size
         assert rows % (self.world * 128) == 0, "rows per micro-batch must divide by tp x 128 for the fused kernels"
@@ -46,30 +56,53 @@ class FusedTP:
         self.blocks = rows // 128
         stage_bytes = rows * width * 2
         cnt_bytes = _align(max(self.blocks, self.world) * 4)
-        # layout: [stage0 | stage1 | part0 | part1 | ag_cnt0 | ag_cnt1 | rs_cnt0 | rs_cnt1]
-        self.off_stage = [0, stage_bytes]
-        self.off_part = [2 * stage_bytes, 3 * stage_bytes]
-        base = 4 * stage_bytes
-        self.off_agc = [base, base + cnt_bytes]
-        self.off_rsc = [base + 2 * cnt_bytes, base + 3 * cnt_bytes]
-        total = base + 4 * cnt_bytes
-        self.buf = symm_mem.empty(total, dtype=torch.uint8, device=self.device)
+        # layout: AG staging (tag x 2) | RS partial slots x 2 | AG counters (tag x 2) | RS counters x 2
+        self.off_stage, self.off_agc = {}, {}
+        off = 0
+        for t in AG_TAGS:
+            self.off_stage[t] = [off, off + stage_bytes]
+            off += 2 * stage_bytes
+        self.off_part = [off, off + stage_bytes]
+        off += 2 * stage_bytes
+        cnt_base = off
+        for t in AG_TAGS:
+            self.off_agc[t] = [off, off + cnt_bytes]
+            off += 2 * cnt_bytes
+        self.off_rsc = [off, off + cnt_bytes]
+        off += 2 * cnt_bytes
+        self.buf = symm_mem.empty(off, dtype=torch.uint8, device=self.device)
         group = ps.tp_group
         self.hdl = symm_mem.rendezvous(self.buf, group=group.group_name)
         self.ptrs = [int(p) for p in self.hdl.buffer_ptrs]
         assert len(self.ptrs) == self.world
-        self.buf[base:].zero_()
+        mc = 0
+        if os.environ.get("DHELLAM_MULTIMEM", "1") != "0":
+            try:
+                mc = int(self.hdl.multicast_ptr or 0)
+            except Exception:
+                mc = 0
+        self.mc_ptr = mc
+        self.buf[cnt_base:].zero_()
         torch.cuda.synchronize(self.device)
         dist.barrier(group=group)                 # nobody pushes before every rank's counters are zero
-        self.total_ag = [0, 0]          # counter value every row block of the slot has reached so far
-        self.total_rs = [0, 0]          # arrival count per source the slot has reached so far
-        self.n_ag = self.n_rs = 0
+        self.total_ag = {t: [0, 0] for t in AG_TAGS}     # counter value reached so far, per (tag, parity)
+        self.calls_ag = {t: 0 for t in AG_TAGS}
+        self.total_rs = [0, 0]
+        self.n_rs = 0
         self._last = None
         self._arr = ctypes.c_void_p * self.world
+        self._pending = {}
 
     # ------------------------------------------------------------------ helpers
     def _ptr_array(self, off):
         return self._arr(*[p + off for p in self.ptrs])
+
+    def _mc(self, off):
+        return (self.mc_ptr + off) if self.mc_ptr else 0
+
+    def _stage_view(self, tag, slot, M, Kd):
+        off = self.off_stage[tag][slot]
+        return self.buf[off:off + M * Kd * 2].view(torch.bfloat16).view(M, Kd)
 
     def _chain(self):
         s = torch.cuda.current_stream(self.device)
@@ -82,47 +115,41 @@ class FusedTP:
         ev.record(s)
         self._last = ev
 
+    def _next_ag(self, tag, M, Kd):
+        slot = self.calls_ag[tag] & 1
+        self.calls_ag[tag] += 1
+        before = self.total_ag[tag][slot]
+        slices = K.proto("dh_ag_slices", [c_int, c_int, c_int])(M, Kd, self.world)
+        self.total_ag[tag][slot] = before + slices
+        return slot, before
+
     # ------------------------------------------------------------------ fused ops
-    def ag_gemm(self, shard, w, tag: str = "", transpose_w: bool = False, sm_budget: int = 0, save: bool = True):
+    def ag_gemm(self, shard, w, tag: str, transpose_w: bool = False, sm_budget: int = 0):
         """``shard [M/t, K]``; ``w [N, K]`` (or ``[K, N']`` with ``transpose_w``: the product is
-        ``gathered @ w``).  Returns ``(out [M, N], gathered [M, K] or None)``."""
+        ``gathered @ w``).  Returns ``(out [M, N], gathered [M, K] view of the staging buffer)``."""
         rows_local, Kd = shard.shape
         M = rows_local * self.world
         assert M == self.rows, "the fused all-gather works on full micro-batches (fixed row count per group)"
-        assert Kd <= self.width and shard.dtype == torch.bfloat16 and shard.is_contiguous()
-        if transpose_w:
-            assert w.shape[0] == Kd
-            N = w.shape[1]
-        else:
-            assert w.shape[1] == Kd
-            N = w.shape[0]
+        assert Kd == self.width and shard.dtype == torch.bfloat16 and shard.is_contiguous()
+        N = w.shape[1] if transpose_w else w.shape[0]
+        assert (w.shape[0] if transpose_w else w.shape[1]) == Kd
         out = torch.empty((M, N), dtype=torch.bfloat16, device=self.device)
-        saved = torch.empty((M, Kd), dtype=torch.bfloat16, device=self.device) if save else None
-        slot = self.n_ag & 1
-        self.n_ag += 1
-        before = self.total_ag[slot]
-        slices = K.proto("dh_ag_gemm_slices", [c_int, c_int, c_int, c_int, c_int])(M, Kd, self.world, self.copy_ctas, int(sm_budget))
-        self.total_ag[slot] = before + slices
+        slot, before = self._next_ag(tag, M, Kd)
         s = self._chain()
         fn = K.proto("dh_ag_gemm_bf16", [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_void_p, c_int64, c_int,
                                           c_int, c_int, c_int, c_int, c_int, c_uint, c_int, c_void_p])
-        K.check(fn(shard.data_ptr(), self._ptr_array(self.off_stage[slot]), self._ptr_array(self.off_agc[slot]), K.ptr(saved),
-                   w.data_ptr(), w.stride(0), int(transpose_w), out.data_ptr(), out.stride(0), M, N, Kd, self.rank, self.world,
-                   self.copy_ctas, before, int(sm_budget), s.cuda_stream), "dh_ag_gemm_bf16")
+        K.check(fn(shard.data_ptr(), self._ptr_array(self.off_stage[tag][slot]), self._ptr_array(self.off_agc[tag][slot]),
+                   self._mc(self.off_stage[tag][slot]), w.data_ptr(), w.stride(0), int(transpose_w), out.data_ptr(), out.stride(0),
+                   M, N, Kd, self.rank, self.world, self.copy_ctas, before, int(sm_budget), s.cuda_stream), "dh_ag_gemm_bf16")
         self._done(s)
-        return out, saved
+        return out, self._stage_view(tag, slot, M, Kd)
 
     def gemm_rs(self, a, w, tag: str = "", transpose_w: bool = False, sm_budget: int = 0):
         """``a [M, K]``; returns this rank's ``[M/t, N]`` shard of ``sum_ranks(a @ op(w))``."""
         M, Kd = a.shape
         assert M == self.rows and a.dtype == torch.bfloat16 and a.stride(1) == 1
-        if transpose_w:
-            assert w.shape[0] == Kd
-            N = w.shape[1]
-        else:
-            assert w.shape[1] == Kd
-            N = w.shape[0]
-        assert N <= self.width
+        N = w.shape[1] if transpose_w else w.shape[0]
+        assert (w.shape[0] if transpose_w else w.shape[1]) == Kd and N <= self.width
         out = torch.empty((M // self.world, N), dtype=torch.bfloat16, device=self.device)
         slot = self.n_rs & 1
         self.n_rs += 1
@@ -136,3 +163,36 @@ class FusedTP:
                    int(sm_budget), s.cuda_stream), "dh_gemm_rs_bf16")
         self._done(s)
         return out
+
+    # ------------------------------------------------------------------ stand-alone gather
+    def gather_start(self, shard, tag: str, stream=None):
+        """Starts pushing ``shard [M/t, K]`` to every rank (on ``stream`` if given, else the
+        current one).  ``gather_wait(tag)`` on the consumer's stream returns the gathered view."""
+        rows_local, Kd = shard.shape
+        M = rows_local * self.world
+        assert M == self.rows and Kd == self.width and shard.dtype == torch.bfloat16 and shard.is_contiguous()
+        slot, before = self._next_ag(tag, M, Kd)
+        cur = torch.cuda.current_stream(self.device)
+        s = stream if stream is not None else cur
+        if s is not cur:
+            s.wait_stream(cur)
+            shard.record_stream(s)
+        fn = K.proto("dh_ag_push", [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_uint, c_void_p])
+        K.check(fn(shard.data_ptr(), self._ptr_array(self.off_stage[tag][slot]), self._ptr_array(self.off_agc[tag][slot]),
+                   self._mc(self.off_stage[tag][slot]), M, Kd, self.rank, self.world, self.push_ctas, before, s.cuda_stream),
+                "dh_ag_push")
+        ev = torch.cuda.Event()
+        ev.record(s)
+        self._pending[tag] = (slot, self.total_ag[tag][slot], M, Kd, ev)
+
+    def gather_wait(self, tag: str):
+        slot, target, M, Kd, ev = self._pending.pop(tag)
+        s = torch.cuda.current_stream(self.device)
+        s.wait_event(ev)
+        fn = K.proto("dh_wait_counters", [c_void_p, c_int, c_uint, c_void_p])
+        K.check(fn(self.ptrs[self.rank] + self.off_agc[tag][slot], M // 128, target, s.cuda_stream), "dh_wait_counters")
+        return self._stage_view(tag, slot, M, Kd)
+
+    def all_gather(self, shard, tag: str):
+        self.gather_start(shard, tag)
+        return self.gather_wait(tag)

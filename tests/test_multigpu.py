@@ -84,13 +84,18 @@ def _fused_worker(rank, world, rows, h, n_out, iters):
         w = (torch.randn(n_out, h, device=dev) * 0.05).to(torch.bfloat16)
         # all-gather -> GEMM, forward form (B K-major) and dgrad form (B MN-major)
         full_ref, _ = C.gather_along_first_dim(shard, ps.tp_group)
-        out, full = fused.ag_gemm(shard, w)
+        out, full = fused.ag_gemm(shard, w, "attn_c")
         torch.cuda.synchronize()
         assert torch.equal(full, full_ref), f"gathered operand differs (iter {it})"
         assert _rel(out, gemm_nt(full_ref, w)) < 1e-3
         wt = (torch.randn(h, n_out, device=dev) * 0.05).to(torch.bfloat16)
-        out2, _ = fused.ag_gemm(shard, wt, transpose_w=True)
+        out2, full2 = fused.ag_gemm(shard, wt, "mlp_l_bwd", transpose_w=True)
         assert _rel(out2, gemm_nn(full_ref, wt)) < 1e-3
+        assert torch.equal(full2, full_ref)
+        # the all-gather alone (push + counter wait), as used to re-gather for a weight gradient
+        full3 = fused.all_gather(shard, "regather_mlp")
+        torch.cuda.synchronize()
+        assert torch.equal(full3, full_ref), f"stand-alone gather differs (iter {it})"
         # GEMM -> reduce-scatter, both forms
         a = torch.randn(rows, n_out, device=dev).to(torch.bfloat16)
         w2 = (torch.randn(h, n_out, device=dev) * 0.05).to(torch.bfloat16)
