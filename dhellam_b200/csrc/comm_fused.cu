@@ -132,11 +132,11 @@ __device__ __forceinline__ void multimem_st_v4(void* mc_addr, const uint4& v) {
 
 // Pushes this rank's shard into every rank's staging buffer and raises the row-block counters.
 // Work items are (row block, column slice); `cta`/`ncta` spread them over the calling CTAs.
-// Four independent 16-byte loads are in flight per thread; with the multicast address one
+// Eight independent 16-byte loads are in flight per thread; with the multicast address one
 // store reaches all ranks, otherwise the registers are stored to each rank in turn (the rank
 // that consumes this shard earliest first).
 __device__ __forceinline__ void push_shard(const AgParams& p, int cta, int ncta) {
-  constexpr int U = 4;
+  constexpr int U = 8;
   const int items = p.blocks_per_rank * p.slices;
   const int cw = p.K / p.slices;                            // columns per slice (multiple of 8)
   const int vec_per_row = cw >> 3;

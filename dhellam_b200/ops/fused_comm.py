@@ -43,12 +43,14 @@ def _align(n, a=1024):
 
 
 class FusedTP:
-    def __init__(self, ps, cfg, train, device, max_rows: int | None = None, width: int | None = None, copy_ctas: int = 8,
-                 push_ctas: int = 16):
+    def __init__(self, ps, cfg, train, device, max_rows: int | None = None, width: int | None = None, copy_ctas: int = 0,
+                 push_ctas: int = 0):
         import torch.distributed._symmetric_memory as symm_mem
         self.ps, self.device = ps, torch.device(device)
         self.world, self.rank = ps.tp, ps.tp_rank
-        self.copy_ctas, self.push_ctas = copy_ctas, push_ctas
+        # the shard a rank pushes is 1/tp of the operand: fewer ranks -> more bytes per rank -> more copy CTAs
+        self.copy_ctas = copy_ctas or max(8, 64 // self.world)
+        self.push_ctas = push_ctas or max(16, 96 // self.world)
         rows = max_rows or train.micro_batch_size * cfg.seq_length // max(ps.cp, 1)
         width = width or cfg.hidden_size
         assert rows % (self.world * 128) == 0, "rows per micro-batch must divide by tp x 128 for the fused kernels"
