@@ -118,3 +118,42 @@ def merge_attention_partials(o_a, lse_a, o_b, lse_b):
     wb = torch.exp(lse_b - lse).permute(2, 0, 1).unsqueeze(-1)
     o = o_a.float() * wa + o_b.float() * wb
     return o.to(o_a.dtype), lse
+
+
+# ----------------------------------------------------------------------------- variable-length API
+def pymha_varlen_fwd(q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k, p_dropout: float = 0.0,
+                     softmax_scale: float | None = None, is_causal: bool = True, return_softmax: bool = False,
+                     math_sm_count: int = 0, profiling: bool = False):
+    """Packed variable-length attention with the reference's signature
+    (csrc/operators/ops.h:18-32): ``q [total_q, h, d]``, ``k, v [total_k, h_k, d]`` and
+    cumulative sequence offsets.  Returns ``(out [total_q, h, d], softmax_lse [b, h, max_q])``.
+    Each sequence runs as one strided call of the fixed-length kernel, so no padding copy
+    is made.  Attention dropout is not supported by the sm_100a kernel (``p_dropout`` must be 0)."""
+    assert p_dropout == 0.0, "attention dropout is not implemented"
+    cq = [int(x) for x in cu_seqlens_q.tolist()]
+    ck = [int(x) for x in cu_seqlens_k.tolist()]
+    b = len(cq) - 1
+    out = torch.empty_like(q)
+    lse = torch.full((b, q.shape[1], max_seqlen_q), float("-inf"), dtype=torch.float32, device=q.device)
+    for i in range(b):
+        qi, ki, vi = q[cq[i]:cq[i + 1]].unsqueeze(1), k[ck[i]:ck[i + 1]].unsqueeze(1), v[ck[i]:ck[i + 1]].unsqueeze(1)
+        o, l = attn_fwd(qi, ki, vi, is_causal, softmax_scale, sm_budget=abs(math_sm_count))
+        out[cq[i]:cq[i + 1]] = o.squeeze(1)
+        lse[i, :, : cq[i + 1] - cq[i]] = l[0]
+    return out, lse
+
+
+def pymha_varlen_bwd(dout, q, k, v, out, softmax_lse, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k, p_dropout: float = 0.0,
+                     softmax_scale: float | None = None, is_causal: bool = True, rng_state=None, deterministic: bool = False,
+                     math_sm_count: int = 0, profiling: bool = False, stream_ptr: int = 0):
+    """Backward of ``pymha_varlen_fwd`` (csrc/operators/ops.h:34-52).  Returns ``(dq, dk, dv)``."""
+    cq = [int(x) for x in cu_seqlens_q.tolist()]
+    ck = [int(x) for x in cu_seqlens_k.tolist()]
+    dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+    for i in range(len(cq) - 1):
+        sl_q, sl_k = slice(cq[i], cq[i + 1]), slice(ck[i], ck[i + 1])
+        lse_i = softmax_lse[i:i + 1, :, : cq[i + 1] - cq[i]].contiguous()
+        a, b_, c = attn_bwd(dout[sl_q].unsqueeze(1), q[sl_q].unsqueeze(1), k[sl_k].unsqueeze(1), v[sl_k].unsqueeze(1),
+                            out[sl_q].unsqueeze(1), lse_i, is_causal, softmax_scale, sm_budget=abs(math_sm_count))
+        dq[sl_q], dk[sl_k], dv[sl_k] = a.squeeze(1), b_.squeeze(1), c.squeeze(1)
+    return dq, dk, dv

@@ -97,3 +97,92 @@ def gemm_tn_acc(dy, x, main_grad, accumulate: bool = True, sm_budget: int = 0, s
     # contraction over M: A = dyᵀ stored [M][N] (MN-major), B = xᵀ stored [M][K] (MN-major)
     _launch(dy, True, x, True, main_grad, accumulate, N, Kd, M, sm_budget, stream)
     return main_grad
+
+
+# ----------------------------------------------------------------------------- reference-style wrappers
+def _timed(fn, profiling, stream):
+    """Runs ``fn`` on ``stream``; returns ``(result, elapsed ms or 0)`` timed with CUDA events
+    on that stream (the reference wraps its calls in host timers, layernorm_column.py:28-35)."""
+    if not torch.cuda.is_available():
+        return fn(), 0.0
+    stream = stream if stream is not None else torch.cuda.current_stream()
+    with torch.cuda.stream(stream):
+        if not profiling:
+            return fn(), 0.0
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        out = fn()
+        e1.record(stream)
+        e1.synchronize()
+        return out, e0.elapsed_time(e1)
+
+
+def gemm_fwd(args, input, weight, output=None, layout: str = "TN", profiling: bool = False, math_sm_count: int = 0,
+             is_matmul: bool = False, stream=None):
+    """``output = input @ weightᵀ`` for a ``[N, K]`` weight (layout "TN"), or ``input @ weight``
+    for layout "NN".  Signature of the reference's ``gemm_fwd`` (layernorm_column.py:7-62);
+    ``math_sm_count`` becomes the CTA budget, ``is_matmul`` is ignored (one kernel serves both)."""
+    x2 = input.reshape(-1, input.shape[-1])
+    fn = (lambda: gemm_nt(x2, weight, out=output, sm_budget=abs(math_sm_count))) if layout[0] == "T" else \
+         (lambda: gemm_nn(x2, weight, out=output, sm_budget=abs(math_sm_count)))
+    out, ms = _timed(fn, profiling, stream)
+    return out.view(*input.shape[:-1], out.shape[-1]), ms
+
+
+gemm_fwd_event = gemm_fwd
+
+
+def dgrad_bwd(args, input_grad, weight, dgrad_output=None, layout: str = "NN", profiling: bool = False, math_sm_count: int = 0,
+              is_matmul: bool = False, stream=None):
+    """``dgrad = input_grad @ weight`` (layernorm_column.py:209-263)."""
+    g2 = input_grad.reshape(-1, input_grad.shape[-1])
+    out, ms = _timed(lambda: gemm_nn(g2, weight, out=dgrad_output, sm_budget=abs(math_sm_count)), profiling, stream)
+    return out, ms
+
+
+def wgrad_bwd(args, input_grad, input_data, wgrad_output, grad_accumulate: bool = False, layout: str = "NT", profiling: bool = False,
+              math_sm_count: int = 0, is_matmul: bool = False, stream=None):
+    """``wgrad (+)= input_gradᵀ @ input_data`` into ``wgrad_output`` (fp32 ``main_grad`` in
+    training; layernorm_column.py:265-323)."""
+    g2 = input_grad.reshape(-1, input_grad.shape[-1])
+    x2 = input_data.reshape(-1, input_data.shape[-1])
+
+    def run():
+        if wgrad_output.dtype == torch.float32:
+            return gemm_tn_acc(g2, x2, wgrad_output, accumulate=grad_accumulate, sm_budget=abs(math_sm_count))
+        tmp = torch.zeros(wgrad_output.shape, dtype=torch.float32, device=wgrad_output.device)
+        gemm_tn_acc(g2, x2, tmp, accumulate=False, sm_budget=abs(math_sm_count))
+        if grad_accumulate:
+            wgrad_output.add_(tmp.to(wgrad_output.dtype))
+        else:
+            wgrad_output.copy_(tmp)
+        return wgrad_output
+    return _timed(run, profiling, stream)
+
+
+def gemm_bwd(args, input_grad, weight, input_data, dgrad_output, wgrad_output, grad_accumulate: bool = False, layout: str = "NNNT",
+             profiling: bool = False, math_sm_count: int = 0, is_matmul: bool = False):
+    """dgrad + wgrad pair (layernorm_column.py:121-207).  Returns
+    ``(dgrad, wgrad, dgrad ms, wgrad ms)``."""
+    d, t1 = dgrad_bwd(args, input_grad, weight, dgrad_output, layout[:2], profiling, math_sm_count)
+    w, t2 = wgrad_bwd(args, input_grad, input_data, wgrad_output, grad_accumulate, layout[2:], profiling, math_sm_count)
+    return d, w, t1, t2
+
+
+def pygemm(a, b, d, transa: bool = False, transb: bool = False, grad_accumulate: bool = False, math_sm_count: int = 0, stream=None,
+           profiling: bool = False):
+    """General entry of the native GEMM (``pygemm``, csrc/operators/gemm.cu:144-170):
+    ``d (+)= op(a) @ op(b)`` with row-major operands; ``trans*`` mean "use the transpose"."""
+    M = a.shape[1] if transa else a.shape[0]
+    Kd = a.shape[0] if transa else a.shape[1]
+    N = b.shape[0] if transb else b.shape[1]
+    if not _native(a, b, d):
+        r = (a.float().t() if transa else a.float()) @ (b.float().t() if transb else b.float())
+        d.copy_(d.float() + r if grad_accumulate else r)
+        return 0.0
+
+    def run():
+        # kernel form: D = opA[M,K] * opB[N,K]^T ; A stored [K][M] when transa; B stored [K][N] when not transb
+        _launch(a, transa, b, not transb, d, grad_accumulate, M, N, Kd, abs(math_sm_count), stream)
+    _, ms = _timed(run, profiling, stream)
+    return ms

@@ -115,9 +115,13 @@ class Strategy:
                         self.bwd_only or default_single(program, BWD))
 
     def validate(self, program: LayerProgram):
-        validate_blocks(self.dcblocks, program, need_fwd=True, need_bwd=True)
-        validate_blocks(self.fwd_only, program, need_fwd=True, need_bwd=False)
-        validate_blocks(self.bwd_only, program, need_fwd=False, need_bwd=True)
+        """Checks every part that is present (absent parts are filled by ``completed``)."""
+        if self.dcblocks:
+            validate_blocks(self.dcblocks, program, need_fwd=True, need_bwd=True)
+        if self.fwd_only:
+            validate_blocks(self.fwd_only, program, need_fwd=True, need_bwd=False)
+        if self.bwd_only:
+            validate_blocks(self.bwd_only, program, need_fwd=False, need_bwd=True)
 
 
 # --------------------------------------------------------------------------- defaults

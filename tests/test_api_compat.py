@@ -1,0 +1,68 @@
+"""Names and contracts kept from the reference package, on CPU."""
+import torch
+
+
+def test_package_facade_exports_reference_names():
+    import dhellam_b200 as d
+    for n in ("gemm_fwd", "gemm_bwd", "gemm_fwd_event", "pylayernorm_fwd", "pylayernorm_bwd", "gather_along_first_dim",
+              "reduce_scatter_along_first_dim", "pymha_varlen_fwd", "pymha_varlen_bwd", "_get_qkv_layout"):
+        assert hasattr(d, n), n
+    from dhellam_b200 import _Clib
+    for n in ("add_tensors", "pygemm", "pygelu", "pybda", "pymha_varlen_fwd", "pymha_varlen_bwd"):
+        assert hasattr(_Clib, n), n
+
+
+def test_gemm_wrappers_match_matmul():
+    from dhellam_b200 import gemm_bwd, gemm_fwd
+    x, w = torch.randn(6, 8), torch.randn(5, 8)
+    y, _ = gemm_fwd(None, x, w)
+    assert torch.allclose(y, x @ w.t(), atol=1e-5)
+    dy = torch.randn(6, 5)
+    wg = torch.ones(5, 8)
+    dx, wg2, _, _ = gemm_bwd(None, dy, w, x, None, wg, grad_accumulate=True)
+    assert torch.allclose(dx, dy @ w, atol=1e-5)
+    assert torch.allclose(wg2, 1 + dy.t() @ x, atol=1e-5)
+
+
+def test_varlen_attention_matches_per_sequence_reference():
+    from dhellam_b200 import pymha_varlen_bwd, pymha_varlen_fwd
+    from dhellam_b200.ops.attention import attn_fwd
+    torch.manual_seed(0)
+    lens = [5, 9, 3]
+    cu = torch.tensor([0, 5, 14, 17], dtype=torch.int32)
+    q, k, v = torch.randn(17, 4, 16), torch.randn(17, 2, 16), torch.randn(17, 2, 16)
+    out, lse = pymha_varlen_fwd(q, k, v, cu, cu, 9, 9, 0.0, 0.25, True)
+    o1, _ = attn_fwd(q[5:14].unsqueeze(1), k[5:14].unsqueeze(1), v[5:14].unsqueeze(1), True, 0.25)
+    assert torch.allclose(out[5:14], o1.squeeze(1), atol=1e-5)
+    dq, dk, dv = pymha_varlen_bwd(torch.randn_like(out), q, k, v, out, lse, cu, cu, 9, 9, 0.0, 0.25, True)
+    assert dq.shape == q.shape and dk.shape == k.shape and torch.isfinite(dv).all()
+
+
+def test_qkv_layout_probe():
+    from dhellam_b200 import _get_qkv_layout
+    s, b, h, d = 4, 2, 3, 8
+    packed = torch.randn(s, b, 3, h, d)
+    assert _get_qkv_layout(packed[:, :, 0], packed[:, :, 1], packed[:, :, 2]) == "sb3hd"
+    packed2 = torch.randn(s, b, h, 3, d)
+    assert _get_qkv_layout(packed2[..., 0, :], packed2[..., 1, :], packed2[..., 2, :]) == "sbh3d"
+    q = torch.randn(s, b, h, d)
+    kv = torch.randn(s, b, 2, h, d)
+    assert _get_qkv_layout(q, kv[:, :, 0], kv[:, :, 1]) == "sbhd_sb2hd"
+    assert _get_qkv_layout(q, torch.randn(s, b, h, d), torch.randn(s, b, h, d)) == "sbhd_sbhd_sbhd"
+
+
+def test_adaptor_parses_megatron_flags_and_builds_configs():
+    from dhellam_b200.adaptor import _add_dhellam_args, get_args, initialize_dhellam_megatron
+    from dhellam_b200.parallel import state as PS
+    PS.set_state(None)
+    args = initialize_dhellam_megatron(None, None, argv=[
+        "--num-layers", "4", "--hidden-size", "256", "--ffn-hidden-size", "688", "--num-attention-heads", "4",
+        "--group-query-attention", "--num-query-groups", "2", "--seq-length", "128", "--vocab-size", "1024", "--swiglu",
+        "--micro-batch-size", "2", "--global-batch-size", "8", "--tensor-model-parallel-size", "1", "--sequence-parallel",
+        "--dhellam", "--schedule-config", "x.json", "--bf16", "--use-distributed-optimizer", "--disable-bias-linear"])
+    assert args.dhellam and args.schedule_config == "x.json"
+    assert get_args() is args
+    cfg = args.model_config
+    assert (cfg.num_layers, cfg.num_query_groups, cfg.activation, cfg.norm) == (4, 2, "swiglu", "rmsnorm")
+    assert args.train_config.dtype == "bf16" and args.parallel_config.dp == 1
+    PS.set_state(None)
