@@ -1,0 +1,107 @@
+"""Strategy files, built-in schedules, the executor's launch order and the race checker."""
+import json
+
+import pytest
+
+from dhellam_b200.config import preset
+from dhellam_b200.models.transformer import build_layer_program
+from dhellam_b200.sched.checker import Launch, RaceError, check_schedule, check_trace, launches_of
+from dhellam_b200.sched.strategy import Block, Strategy, StrategyError, default_paired
+
+# the reference's built-in paired schedule (dhellam/core/dstb.py:1043-1059), as a strategy file
+REFERENCE_DEFAULT = {"DCBlocks": [
+    [["ln_attn"], "None", "None"],
+    ["None", ["bda_mlp_bwd"], ["allgather_attn"]],
+    [["gemm_attn_c", "fl_attn"], "None", ["allgather_mlp_bwd"]],
+    [["gemm_attn_l"], "None", "None"],
+    ["None", ["gemm_dgrad_mlp_l", "gemm_wgrad_mlp_l"], ["reduce_scatter_attn"]],
+    ["None", ["swiglu_bwd"], "None"],
+    ["None", ["gemm_dgrad_mlp_c"], "None"],
+    ["None", ["gemm_wgrad_mlp_c"], ["reduce_scatter_mlp_c_bwd"]],
+    [["bda_attn", "ln_mlp"], "None", "None"],
+    ["None", ["ln_mlp_bwd", "bda_attn_bwd"], ["allgather_mlp"]],
+    [["gemm_mlp_c"], "None", ["allgather_attn_bwd"]],
+    [["swiglu_mlp", "gemm_mlp_l"], "None", "None"],
+    ["None", ["gemm_dgrad_attn_l", "gemm_wgrad_attn_l", "attn_bwd"], ["reduce_scatter_mlp"]],
+    [["bda_mlp"], "None", "None"],
+    ["None", ["gemm_dgrad_attn_c"], "None"],
+    ["None", ["gemm_wgrad_attn_c"], ["reduce_scatter_attn_c_bwd"]],
+    ["None", ["ln_attn_bwd"], "None"]]}
+
+
+def _program(name="tiny-llama", cp=1):
+    return build_layer_program(preset(name), cp=cp)
+
+
+def test_reference_format_strategy_loads_validates_and_round_trips(tmp_path):
+    prog = _program()
+    s = Strategy.from_dict(REFERENCE_DEFAULT)
+    s.validate(prog)
+    p = tmp_path / "s.json"
+    s.save(str(p))
+    again = Strategy.load(str(p))
+    assert again.to_dict() == s.to_dict()
+    assert json.loads(p.read_text())["DCBlocks"][0] == [["ln_attn"], "None", "None"]
+    check_schedule(prog, s)
+
+
+def test_fused_search_names_are_split_and_budgets_parsed():
+    prog = _program()
+    d = json.loads(json.dumps(REFERENCE_DEFAULT))
+    d["DCBlocks"][7] = ["None", ["gemm_wgrad_mlp_c_reduce_scatter_mlp_c_bwd"], "None"]
+    d["DCBlocks"][2] = [["gemm_attn_c@96", "fl_attn"], "None", ["allgather_mlp_bwd"]]
+    s = Strategy.from_dict(d)
+    assert s.dcblocks[7].s2 == ["gemm_wgrad_mlp_c"] and s.dcblocks[7].s3 == ["reduce_scatter_mlp_c_bwd"]
+    s.validate(prog)
+
+
+def test_deferred_wgrad_marker_moves_the_op():
+    prog = _program()
+    d = json.loads(json.dumps(REFERENCE_DEFAULT))
+    d["DCBlocks"][13] = [["bda_mlp"], ["gemm_wgrad_mlp_l_n"], "None"]
+    s = Strategy.from_dict(d)
+    s.validate(prog)
+    names = [l.op for l in launches_of(prog, s.dcblocks)]
+    assert names.index("gemm_wgrad_mlp_l") > names.index("bda_attn_bwd")
+    check_schedule(prog, s)
+
+
+@pytest.mark.parametrize("bad", ["dup", "missing", "order", "lane"])
+def test_invalid_strategies_are_rejected(bad):
+    prog = _program()
+    d = json.loads(json.dumps(REFERENCE_DEFAULT))
+    if bad == "dup":
+        d["DCBlocks"][3] = [["gemm_attn_l", "ln_attn"], "None", "None"]
+    elif bad == "missing":
+        d["DCBlocks"][5] = ["None", "None", "None"]
+    elif bad == "order":
+        d["DCBlocks"][2], d["DCBlocks"][3] = d["DCBlocks"][3], d["DCBlocks"][2]
+    else:
+        d["DCBlocks"][0] = ["None", ["ln_attn"], "None"]
+    with pytest.raises(StrategyError):
+        Strategy.from_dict(d).validate(prog)
+
+
+@pytest.mark.parametrize("name,cp", [("tiny-llama", 1), ("tiny-llama", 2), ("tiny-llama", 4), ("tiny-gpt", 1), ("tiny-moe", 1)])
+def test_builtin_schedules_are_valid_and_race_free(name, cp):
+    prog = _program(name, cp)
+    for streams in (1, 2):
+        check_schedule(prog, Strategy(), compute_streams=streams)
+    blocks = default_paired(prog)
+    # no collective is launched in a block without compute of the other strand beside it, except at the ends
+    if cp == 1:
+        assert sum(1 for b in blocks if b.s3 and not (b.s1 or b.s2)) <= 1
+
+
+def test_checker_catches_missing_wait_and_accepts_the_fix():
+    racy = [Launch("ln", "S1"), Launch("allgather", "S3", waits=(), reads=("ln",))]
+    with pytest.raises(RaceError):
+        check_trace(racy)
+    assert check_trace([Launch("ln", "S1"), Launch("allgather", "S3", waits=("ln",), reads=("ln",))])
+    # transitive: gemm on S1 waits the collective, which waited ln
+    ok = [Launch("ln", "S1"), Launch("ag", "S3", ("ln",), ("ln",)), Launch("other", "S2"),
+          Launch("gemm", "S1", ("ag",), ("ag",)), Launch("wgrad", "S2", ("gemm",), ("ag", "gemm"))]
+    assert check_trace(ok)
+    bad = [Launch("ln", "S1"), Launch("ag", "S3", ("ln",), ("ln",)), Launch("wgrad", "S2", (), ("ag",))]
+    with pytest.raises(RaceError):
+        check_trace(bad)
