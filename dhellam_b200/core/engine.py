@@ -98,6 +98,7 @@ class DoubleStrandEngine:
         self.grad_scale = 1.0
         self._carry = (None, None)
         self._inbox = {"next": [None, None], "prev": [None, None]}
+        self.grad_reducer = None          # set by the trainer when data parallelism is on
 
     # ------------------------------------------------------------------ helpers
     @property
@@ -172,6 +173,8 @@ class DoubleStrandEngine:
                 x = frun.v["out"]
             if fb:
                 g = brun.v["dx"]
+                if b == N - 1 and self.grad_reducer is not None:
+                    self.grad_reducer.layer_final(b_idx, st.s2 if st.cuda else None)
         if fa and st.cuda:
             ev = torch.cuda.Event()
             ev.record(st.s1)
@@ -245,6 +248,8 @@ class DoubleStrandEngine:
         self.grad_scale = 1.0 / N
         self.env.grad_scale = self.grad_scale
         st = self.streams
+        if self.grad_reducer is not None:
+            self.grad_reducer.start_step()
         if st.cuda:
             st.fork_from(torch.cuda.current_stream())
         for t in range(PP.total_ticks(self.P, N)):

@@ -108,6 +108,8 @@ class MixedPrecisionAdam:
     def reduce_gradients(self):
         """Sequence-parallel norm gradients over TP, then data(+context)-parallel reduction."""
         ps, model = self.ps, self.model
+        reducer = getattr(self, "grad_reducer", None)
+        dp_done = reducer is not None and reducer.finish()       # also waits for the buckets still in flight
         if ps.tp > 1:
             bufs = [p.main_grad for _, p in model.named_parameters() if p.sequence_parallel or p.base_name == "router_weight"
                     or p.base_name == "position_embeddings"]
@@ -118,7 +120,10 @@ class MixedPrecisionAdam:
                 for b in bufs:
                     b.copy_(flat[o:o + b.numel()].view_as(b))
                     o += b.numel()
-        if self.gsize > 1:
+        if dp_done:
+            # buckets were summed under the backward pass; only the data-parallel average is left
+            model.flat_grad.mul_(1.0 / ps.dp)
+        elif self.gsize > 1:
             g = model.flat_grad
             if model.cfg.is_moe and ps.ep > 1:
                 self._reduce_moe(g)

@@ -42,6 +42,11 @@ class Trainer:
         self.engine = DoubleStrandEngine(self.model, self.env, strategy, single_stream=single_stream or not train.dhellam,
                                          profile=profile, trace=trace, compute_streams=train.compute_streams)
         self.optimizer = MixedPrecisionAdam(self.model, train, self.ps, distributed=distributed_optimizer)
+        if self.ps.dp * self.ps.cp > 1 and not distributed_optimizer:
+            from .parallel.dp import OverlappedGradReducer
+            reducer = OverlappedGradReducer(self.model, self.ps, self.engine.streams)
+            self.engine.grad_reducer = reducer
+            self.optimizer.grad_reducer = reducer
         self.iteration = 0
         self.last_grad_norm = None
 
