@@ -10,18 +10,21 @@
 //                            output kept in registers and rescaled once per block
 //   S_{j+1} and P_{j-1} V_{j-1} run on the tensor cores while the softmax warps work on S_j.
 //
-// Backward, one CTA per (128 keys, batch, KV head); it loops over the query heads of the
-// group and the query blocks that see these keys:
-//   S = Q K^T and dP = dO V^T into TMEM; threads form P = exp2(S - lse) and
-//   dS = P (dP - delta) into ONE swizzled shared-memory image each, which serves both as a
-//   K-major operand (dQ = dS K) and as an MN-major operand (dV += P^T dO, dK += dS^T Q), so
-//   no transposed copies exist anywhere; dK / dV accumulate in TMEM over the whole loop
-//   (this also sums the query heads of a KV group), dQ is added to an fp32 scratch with
-//   vector atomics and converted at the end.
+// Backward is two kernels that share delta = rowsum(dO * O):
+//   dK/dV: one CTA per (128 keys, batch, KV head) loops over the query heads of the group and
+//     the query blocks that see these keys: S = Q K^T and dP = dO V^T into TMEM; eight math
+//     warps form P = exp2(S - lse) and dS = P (dP - delta) into swizzled shared-memory images
+//     that are consumed as MN-major operands (dV += P^T dO, dK += dS^T Q), so no transposed
+//     copies exist anywhere; dK / dV accumulate in TMEM over the whole loop, which also sums
+//     the query heads of a KV group.
+//   dQ: one CTA per (128 queries, batch, query head) loops over the key blocks, recomputes S
+//     and dP and accumulates dQ += dS K in TMEM.  Recomputing two products per tile pair
+//     replaces an fp32 atomic accumulation of dQ, which was bound by L2 atomic throughput.
 //
 // Role in the reference: the bundled flash-attention 2 sm80 kernels behind
-// pymha_varlen_fwd / pymha_varlen_bwd (csrc/operators/flash_atten.cu:220-434, 479-757),
-// including its fp32 dq_accum and the separate GQA reduction (:637-652, 742-745).
+// pymha_varlen_fwd / pymha_varlen_bwd (csrc/operators/flash_atten.cu:220-434, 479-757);
+// its fp32 dq_accum and its separate GQA reduction pass (:637-652, 742-745) have no
+// counterpart here.
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <float.h>
@@ -38,6 +41,7 @@ constexpr int BQ = 128, BKV = 128, D = 128;
 constexpr int HALF_BYTES = 128 * 128;        // one [128 rows][64 elems] swizzled box
 constexpr int TILE_BYTES = 2 * HALF_BYTES;   // [128][128] bf16
 constexpr int THREADS = 192;
+constexpr int BWD_THREADS = 320;           // TMA warp + MMA warp + 8 math warps (two per TMEM lane quarter)
 constexpr float LOG2E = 1.4426950408889634f;
 
 struct Geometry {
@@ -312,27 +316,8 @@ __global__ void __launch_bounds__(256) attn_delta_kernel(const __nv_bfloat16* __
   if (lane == 0) delta[((long long)b * Hq + h) * Sq + s] = v;
 }
 
-// fp32 scratch -> bf16 strided output, times `scale`
-__global__ void __launch_bounds__(256) attn_dq_convert_kernel(const float* __restrict__ acc, __nv_bfloat16* __restrict__ dq, int B, int Hq,
-                                                              int Sq, long long s_s, long long s_b, long long s_h, float scale) {
-  const long long total = (long long)B * Hq * Sq * (D / 8);
-  for (long long i = (long long)blockIdx.x * 256 + threadIdx.x; i < total; i += (long long)gridDim.x * 256) {
-    const int c = (int)(i % (D / 8));
-    const long long row = i / (D / 8);                 // (s, b, h) flattened as [Sq][B][Hq]
-    const int h = (int)(row % Hq);
-    const int b = (int)((row / Hq) % B);
-    const long long s = row / ((long long)Hq * B);
-    const float4 x = reinterpret_cast<const float4*>(acc + row * D)[c * 2];
-    const float4 y = reinterpret_cast<const float4*>(acc + row * D)[c * 2 + 1];
-    uint4 u;
-    u.x = pack_bf16x2(x.x * scale, x.y * scale); u.y = pack_bf16x2(x.z * scale, x.w * scale);
-    u.z = pack_bf16x2(y.x * scale, y.y * scale); u.w = pack_bf16x2(y.z * scale, y.w * scale);
-    reinterpret_cast<uint4*>(dq + s * s_s + b * s_b + h * s_h)[c] = u;
-  }
-}
-
 struct BwdCtl {
-  uint64_t kv_full, qdo_full, qdo_empty, sdp_full, pds_ready, dq_full, dq_read, acc_full;
+  uint64_t kv_full, qdo_full, qdo_empty, sdp_full, pds_ready, acc_full;
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -345,10 +330,10 @@ struct BwdGeometry {
   DeviceStatus* status;
 };
 
-__global__ void __launch_bounds__(THREADS, 1)
+__global__ void __launch_bounds__(BWD_THREADS, 1)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ CUtensorMap tk, const __grid_constant__ CUtensorMap tv,
                 const __grid_constant__ CUtensorMap tdo, const float* __restrict__ lse, const float* __restrict__ delta,
-                float* __restrict__ dq_acc, __nv_bfloat16* __restrict__ dk, __nv_bfloat16* __restrict__ dv, const BwdGeometry g) {
+                __nv_bfloat16* __restrict__ dk, __nv_bfloat16* __restrict__ dv, const BwdGeometry g) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sK = smem;
@@ -374,8 +359,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
 
   if (threadIdx.x == 0) {
     mbar_init(&ctl->kv_full, 1); mbar_init(&ctl->qdo_full, 1); mbar_init(&ctl->qdo_empty, 1);
-    mbar_init(&ctl->sdp_full, 1); mbar_init(&ctl->pds_ready, 4); mbar_init(&ctl->dq_full, 1);
-    mbar_init(&ctl->dq_read, 4); mbar_init(&ctl->acc_full, 1);
+    mbar_init(&ctl->sdp_full, 1); mbar_init(&ctl->pds_ready, 8); mbar_init(&ctl->acc_full, 1);
     ctl->abort_flag = 0;
     mbar_fence_init();
   }
@@ -385,7 +369,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
   tc_fence_after();
   const uint32_t tmem = ctl->tmem_base;
   volatile int* abort_flag = &ctl->abort_flag;
-  // TMEM columns: [0,128) S then dQ, [128,256) dP, [256,384) dV, [384,512) dK
+  // TMEM columns: [0,128) S, [128,256) dP, [256,384) dV, [384,512) dK
 
   if (warp == 0) {
     if (lane == 0 && n_iter > 0) {
@@ -411,15 +395,12 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
     if (lane == 0 && n_iter > 0) {
       constexpr uint32_t id_kk = umma_idesc_bf16(128, 128, 0, 0);   // S, dP: both operands K-major
       constexpr uint32_t id_mm = umma_idesc_bf16(128, 128, 1, 1);   // dV, dK: both operands MN-major
-      constexpr uint32_t id_km = umma_idesc_bf16(128, 128, 0, 1);   // dQ: dS K-major, K MN-major
       const uint32_t k_base = smem_u32(sK), v_base = smem_u32(sV), q_base = smem_u32(sQ), do_base = smem_u32(sDO);
       const uint32_t p_base = smem_u32(sP), ds_base = smem_u32(sDS);
       bool ok = mbar_wait(&ctl->kv_full, 0, abort_flag, g.status, 510);
       for (int it = 0; it < n_iter && ok; ++it) {
         const uint32_t ph = it & 1;
         if (!mbar_wait(&ctl->qdo_full, ph, abort_flag, g.status, 511)) break;
-        // the S columns are reused for dQ: wait until the threads have drained the previous dQ
-        if (!mbar_wait(&ctl->dq_read, ph ^ 1, abort_flag, g.status, 512)) break;
         tc_fence_after();
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) umma_bf16(tmem + 0, desc_kmajor(q_base, kk), desc_kmajor(k_base, kk), id_kk, kk > 0);
@@ -432,16 +413,16 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
         for (int kk = 0; kk < 8; ++kk) umma_bf16(tmem + 256, desc_mnmajor(p_base, kk), desc_mnmajor(do_base, kk), id_mm, (it | kk) != 0);
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) umma_bf16(tmem + 384, desc_mnmajor(ds_base, kk), desc_mnmajor(q_base, kk), id_mm, (it | kk) != 0);
-#pragma unroll
-        for (int kk = 0; kk < 8; ++kk) umma_bf16(tmem + 0, desc_kmajor(ds_base, kk), desc_mnmajor(k_base, kk), id_km, kk > 0);
-        umma_commit(&ctl->qdo_empty);
-        umma_commit(&ctl->dq_full);
+        umma_commit(&ctl->qdo_empty);           // Q and dO are free once dV and dK have read them
       }
       if (ok) umma_commit(&ctl->acc_full);
     }
     __syncwarp();
   } else {
+    // warps 2..5 and 6..9 cover the four TMEM lane quarters twice: the first set works on
+    // columns [0, 64), the second on [64, 128) of every 128-column tile
     const int quarter = warp & 3;
+    const int c_lo = ((warp - 2) >> 2) * 2;
     const int r = quarter * 32 + lane;
     const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
     const float sl2 = g.scale * LOG2E;
@@ -462,7 +443,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
       if (g.causal) limit = min(limit, qi + off - key0 + 1);
       if (!row_ok) limit = 0;
 #pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
+      for (int c = c_lo; c < c_lo + 2; ++c) {
         uint32_t sv[32], dpv[32];
         tmem_ld32(tmem + 0 + lane_base + c * 32, sv);
         tmem_ld32(tmem + 128 + lane_base + c * 32, dpv);
@@ -490,26 +471,6 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
       fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) mbar_arrive(&ctl->pds_ready);
-      // dQ tile of this (query block, head): add into the fp32 scratch
-      if (!mbar_wait(&ctl->dq_full, ph, abort_flag, g.status, 521)) { ok = false; break; }
-      tc_fence_after();
-      float* dst = dq_acc + (((long long)qi * g.B + b) * g.Hq + hq) * D;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t v[32];
-        tmem_ld32(tmem + 0 + lane_base + c * 32, v);
-        tmem_ld_wait();
-        if (row_ok) {
-#pragma unroll
-          for (int q4 = 0; q4 < 8; ++q4)
-            atomicAdd(reinterpret_cast<float4*>(dst + c * 32) + q4,
-                      make_float4(__uint_as_float(v[q4 * 4]), __uint_as_float(v[q4 * 4 + 1]), __uint_as_float(v[q4 * 4 + 2]),
-                                  __uint_as_float(v[q4 * 4 + 3])));
-        }
-      }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&ctl->dq_read);
     }
     // dK (times scale) and dV of this key block
     const int kj = kb * BKV + r;
@@ -519,7 +480,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
         __nv_bfloat16* dvr = dv + (long long)kj * g.dv_s + (long long)b * g.dv_b + (long long)hk * g.dv_h;
         __nv_bfloat16* dkr = dk + (long long)kj * g.dk_s + (long long)b * g.dk_b + (long long)hk * g.dk_h;
 #pragma unroll 1
-        for (int c = 0; c < 4; ++c) {
+        for (int c = c_lo; c < c_lo + 2; ++c) {
           uint32_t a[32], bb[32];
           tmem_ld32(tmem + 256 + lane_base + c * 32, a);
           tmem_ld32(tmem + 384 + lane_base + c * 32, bb);
@@ -543,7 +504,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
           }
         }
       }
-    } else if (n_iter == 0 && kj < g.Sk) {
+    } else if (n_iter == 0 && kj < g.Sk && c_lo == 0) {
       __nv_bfloat16* dvr = dv + (long long)kj * g.dv_s + (long long)b * g.dv_b + (long long)hk * g.dv_h;
       __nv_bfloat16* dkr = dk + (long long)kj * g.dk_s + (long long)b * g.dk_b + (long long)hk * g.dk_h;
       for (int i = 0; i < D / 8; ++i) {
@@ -556,6 +517,189 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
   __syncthreads();
   if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem, 512); }
 }
+
+// ----------------------------------------------------------------------- backward, dQ
+// One CTA per (128 query rows, batch, query head); it loops over the key blocks these
+// queries see, recomputes S = Q K^T and dP = dO V^T, forms dS = P (dP - delta) and
+// accumulates dQ += dS K in TMEM over the whole loop, so that no atomics and no fp32 scratch
+// are needed for dQ (two extra MMAs per tile pair buy that).
+struct DqCtl {
+  uint64_t qdo_full;
+  uint64_t kv_full[2], kv_empty[2];
+  uint64_t sdp_full, ds_ready, dq_full;
+  uint32_t tmem_base;
+  int abort_flag;
+};
+constexpr int DQ_SMEM = TILE_BYTES * 7 + 1024 + 256;    // Q, dO, K x2, V x2, dS
+
+struct DqGeometry {
+  int B, Hq, Hk, Sq, Sk, causal;
+  float scale;
+  long long dq_s, dq_b, dq_h;
+  DeviceStatus* status;
+};
+
+__global__ void __launch_bounds__(BWD_THREADS, 1)
+attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ CUtensorMap tk, const __grid_constant__ CUtensorMap tv,
+                   const __grid_constant__ CUtensorMap tdo, const float* __restrict__ lse, const float* __restrict__ delta,
+                   __nv_bfloat16* __restrict__ dq, const DqGeometry g) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sQ = smem;
+  uint8_t* sDO = smem + TILE_BYTES;
+  uint8_t* sK = smem + 2 * TILE_BYTES;
+  uint8_t* sV = smem + 4 * TILE_BYTES;
+  uint8_t* sDS = smem + 6 * TILE_BYTES;
+  DqCtl* ctl = reinterpret_cast<DqCtl*>(smem + 7 * TILE_BYTES);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nqb = (g.Sq + BQ - 1) / BQ;
+  const int qb = nqb - 1 - (int)blockIdx.x;
+  const int hq = blockIdx.y, b = blockIdx.z;
+  const int hk = hq / (g.Hq / g.Hk);
+  const int off = g.Sk - g.Sq;
+  int nblk = (g.Sk + BKV - 1) / BKV;
+  if (g.causal) {
+    const int last_key = qb * BQ + BQ - 1 + off;
+    nblk = last_key < 0 ? 0 : min(nblk, last_key / BKV + 1);
+  }
+
+  if (threadIdx.x == 0) {
+    mbar_init(&ctl->qdo_full, 1);
+    for (int i = 0; i < 2; ++i) { mbar_init(&ctl->kv_full[i], 1); mbar_init(&ctl->kv_empty[i], 1); }
+    mbar_init(&ctl->sdp_full, 1); mbar_init(&ctl->ds_ready, 8); mbar_init(&ctl->dq_full, 1);
+    ctl->abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) { tmem_alloc(&ctl->tmem_base, 512); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = ctl->tmem_base;
+  volatile int* abort_flag = &ctl->abort_flag;
+  // TMEM columns: [0,128) S, [128,256) dP, [256,384) dQ
+
+  if (warp == 0) {
+    if (lane == 0 && nblk > 0) {
+      tma_prefetch_desc(&tq); tma_prefetch_desc(&tk); tma_prefetch_desc(&tv); tma_prefetch_desc(&tdo);
+      mbar_expect_tx(&ctl->qdo_full, 2 * TILE_BYTES);
+      tma_load_4d(sQ, &tq, &ctl->qdo_full, 0, hq, b, qb * BQ);
+      tma_load_4d(sQ + HALF_BYTES, &tq, &ctl->qdo_full, 64, hq, b, qb * BQ);
+      tma_load_4d(sDO, &tdo, &ctl->qdo_full, 0, hq, b, qb * BQ);
+      tma_load_4d(sDO + HALF_BYTES, &tdo, &ctl->qdo_full, 64, hq, b, qb * BQ);
+      for (int j = 0; j < nblk; ++j) {
+        const int s = j & 1;
+        if (!mbar_wait(&ctl->kv_empty[s], ((j >> 1) & 1) ^ 1, abort_flag, g.status, 800)) break;
+        mbar_expect_tx(&ctl->kv_full[s], 2 * TILE_BYTES);
+        tma_load_4d(sK + s * TILE_BYTES, &tk, &ctl->kv_full[s], 0, hk, b, j * BKV);
+        tma_load_4d(sK + s * TILE_BYTES + HALF_BYTES, &tk, &ctl->kv_full[s], 64, hk, b, j * BKV);
+        tma_load_4d(sV + s * TILE_BYTES, &tv, &ctl->kv_full[s], 0, hk, b, j * BKV);
+        tma_load_4d(sV + s * TILE_BYTES + HALF_BYTES, &tv, &ctl->kv_full[s], 64, hk, b, j * BKV);
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    if (lane == 0 && nblk > 0) {
+      constexpr uint32_t id_kk = umma_idesc_bf16(128, 128, 0, 0);   // S, dP
+      constexpr uint32_t id_km = umma_idesc_bf16(128, 128, 0, 1);   // dQ: dS K-major, K MN-major
+      const uint32_t q_base = smem_u32(sQ), do_base = smem_u32(sDO), ds_base = smem_u32(sDS);
+      bool ok = mbar_wait(&ctl->qdo_full, 0, abort_flag, g.status, 810);
+      for (int j = 0; j < nblk && ok; ++j) {
+        const int s = j & 1;
+        if (!mbar_wait(&ctl->kv_full[s], (j >> 1) & 1, abort_flag, g.status, 811)) break;
+        tc_fence_after();
+        const uint32_t k_base = smem_u32(sK + s * TILE_BYTES), v_base = smem_u32(sV + s * TILE_BYTES);
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) umma_bf16(tmem + 0, desc_kmajor(q_base, kk), desc_kmajor(k_base, kk), id_kk, kk > 0);
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) umma_bf16(tmem + 128, desc_kmajor(do_base, kk), desc_kmajor(v_base, kk), id_kk, kk > 0);
+        umma_commit(&ctl->sdp_full);
+        if (!mbar_wait(&ctl->ds_ready, j & 1, abort_flag, g.status, 812)) break;
+        tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) umma_bf16(tmem + 256, desc_kmajor(ds_base, kk), desc_mnmajor(k_base, kk), id_km, (j | kk) != 0);
+        umma_commit(&ctl->kv_empty[s]);
+      }
+      if (ok) umma_commit(&ctl->dq_full);
+    }
+    __syncwarp();
+  } else {
+    const int quarter = warp & 3;
+    const int c_lo = ((warp - 2) >> 2) * 2;
+    const int r = quarter * 32 + lane;
+    const int qi = qb * BQ + r;
+    const bool row_ok = qi < g.Sq;
+    const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
+    const float sl2 = g.scale * LOG2E;
+    const long long stat = ((long long)b * g.Hq + hq) * g.Sq + qi;
+    const float L = row_ok ? lse[stat] * LOG2E : 0.f;
+    const float dl = row_ok ? delta[stat] : 0.f;
+    bool ok = nblk > 0;
+    for (int j = 0; j < nblk && ok; ++j) {
+      if (!mbar_wait(&ctl->sdp_full, j & 1, abort_flag, g.status, 820)) { ok = false; break; }
+      tc_fence_after();
+      const int key0 = j * BKV;
+      int limit = g.Sk - key0;
+      if (g.causal) limit = min(limit, qi + off - key0 + 1);
+      if (!row_ok) limit = 0;
+#pragma unroll 1
+      for (int c = c_lo; c < c_lo + 2; ++c) {
+        uint32_t sv[32], dpv[32];
+        tmem_ld32(tmem + 0 + lane_base + c * 32, sv);
+        tmem_ld32(tmem + 128 + lane_base + c * 32, dpv);
+        tmem_ld_wait();
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) {
+          float ds[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int col = c * 32 + q4 * 8 + i;
+            float pe = exp2f(__uint_as_float(sv[q4 * 8 + i]) * sl2 - L);
+            if (col >= limit) pe = 0.f;
+            ds[i] = pe * (__uint_as_float(dpv[q4 * 8 + i]) - dl);
+          }
+          uint4 ud;
+          ud.x = pack_bf16x2(ds[0], ds[1]); ud.y = pack_bf16x2(ds[2], ds[3]); ud.z = pack_bf16x2(ds[4], ds[5]); ud.w = pack_bf16x2(ds[6], ds[7]);
+          *reinterpret_cast<uint4*>(sDS + swz_off(r, c * 4 + q4)) = ud;
+        }
+      }
+      tc_fence_before();
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&ctl->ds_ready);
+    }
+    __nv_bfloat16* dqr = dq + (long long)qi * g.dq_s + (long long)b * g.dq_b + (long long)hq * g.dq_h;
+    if (ok && nblk > 0) {
+      if (mbar_wait(&ctl->dq_full, 0, abort_flag, g.status, 821)) {
+        tc_fence_after();
+#pragma unroll 1
+        for (int c = c_lo; c < c_lo + 2; ++c) {
+          uint32_t a[32];
+          tmem_ld32(tmem + 256 + lane_base + c * 32, a);
+          tmem_ld_wait();
+          if (row_ok) {
+#pragma unroll
+            for (int q4 = 0; q4 < 4; ++q4) {
+              uint4 u;
+              const int i0 = q4 * 8;
+              u.x = pack_bf16x2(__uint_as_float(a[i0]) * g.scale, __uint_as_float(a[i0 + 1]) * g.scale);
+              u.y = pack_bf16x2(__uint_as_float(a[i0 + 2]) * g.scale, __uint_as_float(a[i0 + 3]) * g.scale);
+              u.z = pack_bf16x2(__uint_as_float(a[i0 + 4]) * g.scale, __uint_as_float(a[i0 + 5]) * g.scale);
+              u.w = pack_bf16x2(__uint_as_float(a[i0 + 6]) * g.scale, __uint_as_float(a[i0 + 7]) * g.scale);
+              reinterpret_cast<uint4*>(dqr + c * 32)[q4] = u;
+            }
+          }
+        }
+      }
+    } else if (nblk == 0 && row_ok && c_lo == 0) {
+      for (int i = 0; i < D / 8; ++i) reinterpret_cast<uint4*>(dqr)[i] = make_uint4(0, 0, 0, 0);
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem, 512); }
+}
+
 
 static const CUtensorMap* tensor_map_sbhd(const void* p, int S, int B, int H, long long s_s, long long s_b, long long s_h) {
   const uint64_t dims[4] = {(uint64_t)D, (uint64_t)H, (uint64_t)B, (uint64_t)S};
@@ -600,11 +744,8 @@ int dh_attn_fwd(const void* q, const void* k, const void* v, void* out, void* ls
   return (int)e;
 }
 
-// Scratch layout: delta [B*Hq*Sq] fp32 followed (256-byte aligned) by dq_acc [Sq*B*Hq*128] fp32.
-int64_t dh_attn_bwd_scratch_bytes(int B, int Hq, int Sq) {
-  const int64_t delta = ((int64_t)B * Hq * Sq * 4 + 255) / 256 * 256;
-  return delta + (int64_t)Sq * B * Hq * D * 4;
-}
+// Scratch: delta [B*Hq*Sq] fp32 (row dot products of dO and O), rounded up to 256 bytes.
+int64_t dh_attn_bwd_scratch_bytes(int B, int Hq, int Sq) { return ((int64_t)B * Hq * Sq * 4 + 255) / 256 * 256; }
 
 int dh_attn_bwd(const void* dout, const void* q, const void* k, const void* v, const void* out, const void* lse, void* dq, void* dk,
                 void* dv, void* scratch, const int64_t* strides /* 8 tensors x (s,b,h): do,q,k,v,o,dq,dk,dv */, int B, int Hq, int Hk,
@@ -623,29 +764,28 @@ int dh_attn_bwd(const void* dout, const void* q, const void* k, const void* v, c
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(attn_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, BWD_SMEM);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_bwd_dq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, DQ_SMEM);
     if (e != cudaSuccess) { set_last_error("dh_attn_bwd: shared memory opt-in failed: %s", cudaGetErrorString(e)); return (int)e; }
     configured = true;
   }
   float* delta = reinterpret_cast<float*>(scratch);
-  const int64_t delta_bytes = ((int64_t)B * Hq * Sq * 4 + 255) / 256 * 256;
-  float* dq_acc = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(scratch) + delta_bytes);
-  cudaError_t e = cudaMemsetAsync(dq_acc, 0, (size_t)Sq * B * Hq * D * 4, stream);
-  if (e != cudaSuccess) { set_last_error("dh_attn_bwd: memset failed: %s", cudaGetErrorString(e)); return (int)e; }
   const int rows = B * Hq * Sq;
   attn_delta_kernel<<<(rows * 32 + 255) / 256, 256, 0, stream>>>((const __nv_bfloat16*)dout, (const __nv_bfloat16*)out, delta, B, Hq, Sq,
                                                                  sdo[0], sdo[1], sdo[2], so[0], so[1], so[2]);
+  DeviceStatus* st = reinterpret_cast<DeviceStatus*>(dh_status_device_ptr());
   BwdGeometry g;
   g.B = B; g.Hq = Hq; g.Hk = Hk; g.Sq = Sq; g.Sk = Sk; g.causal = causal; g.scale = scale;
   g.dk_s = sdk[0]; g.dk_b = sdk[1]; g.dk_h = sdk[2]; g.dv_s = sdv[0]; g.dv_b = sdv[1]; g.dv_h = sdv[2];
-  g.status = reinterpret_cast<DeviceStatus*>(dh_status_device_ptr());
-  dim3 grid((Sk + BKV - 1) / BKV, Hk, B);
-  attn_bwd_kernel<<<grid, THREADS, BWD_SMEM, stream>>>(*tq, *tk, *tv, *tdo, (const float*)lse, delta, dq_acc, (__nv_bfloat16*)dk,
-                                                       (__nv_bfloat16*)dv, g);
-  const long long total = (long long)rows * (D / 8);
-  int cgrid = (int)((total + 255) / 256);
-  if (cgrid > dh_sm_count() * 16) cgrid = dh_sm_count() * 16;
-  attn_dq_convert_kernel<<<cgrid, 256, 0, stream>>>(dq_acc, (__nv_bfloat16*)dq, B, Hq, Sq, sdq[0], sdq[1], sdq[2], scale);
-  e = cudaGetLastError();
+  g.status = st;
+  attn_bwd_kernel<<<dim3((Sk + BKV - 1) / BKV, Hk, B), BWD_THREADS, BWD_SMEM, stream>>>(*tq, *tk, *tv, *tdo, (const float*)lse, delta,
+                                                                                      (__nv_bfloat16*)dk, (__nv_bfloat16*)dv, g);
+  DqGeometry gq;
+  gq.B = B; gq.Hq = Hq; gq.Hk = Hk; gq.Sq = Sq; gq.Sk = Sk; gq.causal = causal; gq.scale = scale;
+  gq.dq_s = sdq[0]; gq.dq_b = sdq[1]; gq.dq_h = sdq[2];
+  gq.status = st;
+  attn_bwd_dq_kernel<<<dim3((Sq + BQ - 1) / BQ, Hq, B), BWD_THREADS, DQ_SMEM, stream>>>(*tq, *tk, *tv, *tdo, (const float*)lse, delta,
+                                                                                      (__nv_bfloat16*)dq, gq);
+  cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) set_last_error("dh_attn_bwd launch failed: %s", cudaGetErrorString(e));
   return (int)e;
 }
@@ -685,8 +825,7 @@ extern "C" int dh_attn_bwd_noalloc(const void* dout, const void* q, const void* 
   if (Hk <= 0 || Hq % Hk != 0) { set_last_error("dh_attn_bwd_noalloc: query heads must be a multiple of KV heads"); return (int)cudaErrorInvalidValue; }
   if (B <= 0 || Sq <= 0 || Sk <= 0) return 0;
   const int64_t rows = (int64_t)B * Hq * Sq;
-  const int64_t delta_bytes = (rows * 4 + 255) / 256 * 256;
-  const int64_t need = delta_bytes + rows * D * 4;
+  const int64_t need = (rows * 4 + 255) / 256 * 256;
   if (need > (int64_t)DH_ATTN_NOALLOC_SCRATCH_BYTES) {
     set_last_error("dh_attn_bwd_noalloc: B*Hq*Sq = %lld rows need %lld bytes of scratch, the built-in array holds %u; "
                    "use dh_attn_bwd with a caller-provided buffer", (long long)rows, (long long)need, DH_ATTN_NOALLOC_SCRATCH_BYTES);
@@ -701,6 +840,7 @@ extern "C" int dh_attn_bwd_noalloc(const void* dout, const void* q, const void* 
     e = cudaGetSymbolAddress(&ptr, g_noalloc_scratch);
     if (e != cudaSuccess || ptr == nullptr) { set_last_error("dh_attn_bwd_noalloc: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e)); return (int)e; }
     e = cudaFuncSetAttribute(attn_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, BWD_SMEM);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_bwd_dq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, DQ_SMEM);
     if (e != cudaSuccess) { set_last_error("dh_attn_bwd_noalloc: shared memory opt-in failed: %s", cudaGetErrorString(e)); return (int)e; }
     g_noalloc_addr[dev] = ptr;
     g_noalloc_ready[dev] = true;
@@ -711,24 +851,22 @@ extern "C" int dh_attn_bwd_noalloc(const void* dout, const void* q, const void* 
   if (!map_sbhd_into(&tq, q, Sq, B, Hq, sq) || !map_sbhd_into(&tk, k, Sk, B, Hk, sk) || !map_sbhd_into(&tv, v, Sk, B, Hk, sv) ||
       !map_sbhd_into(&tdo, dout, Sq, B, Hq, sdo))
     return (int)cudaErrorInvalidValue;
-  unsigned char* base = reinterpret_cast<unsigned char*>(g_noalloc_addr[dev]);
-  float* delta = reinterpret_cast<float*>(base);
-  float* dq_acc = reinterpret_cast<float*>(base + delta_bytes);
-  e = cudaMemsetAsync(dq_acc, 0, (size_t)rows * D * 4, stream);           // the accumulator must start at zero
-  if (e != cudaSuccess) { set_last_error("dh_attn_bwd_noalloc: memset failed: %s", cudaGetErrorString(e)); return (int)e; }
+  // delta is fully rewritten by every call, so nothing in the shared array needs clearing
+  float* delta = reinterpret_cast<float*>(g_noalloc_addr[dev]);
   attn_delta_kernel<<<(unsigned)((rows * 32 + 255) / 256), 256, 0, stream>>>((const __nv_bfloat16*)dout, (const __nv_bfloat16*)out, delta, B,
                                                                              Hq, Sq, sdo[0], sdo[1], sdo[2], so[0], so[1], so[2]);
   BwdGeometry g;
   g.B = B; g.Hq = Hq; g.Hk = Hk; g.Sq = Sq; g.Sk = Sk; g.causal = causal; g.scale = scale;
   g.dk_s = sdk[0]; g.dk_b = sdk[1]; g.dk_h = sdk[2]; g.dv_s = sdv[0]; g.dv_b = sdv[1]; g.dv_h = sdv[2];
   g.status = nullptr;
-  dim3 grid((Sk + BKV - 1) / BKV, Hk, B);
-  attn_bwd_kernel<<<grid, THREADS, BWD_SMEM, stream>>>(tq, tk, tv, tdo, (const float*)lse, delta, dq_acc, (__nv_bfloat16*)dk,
-                                                       (__nv_bfloat16*)dv, g);
-  const long long total = (long long)rows * (D / 8);
-  int cgrid = (int)((total + 255) / 256);
-  if (cgrid > 148 * 16) cgrid = 148 * 16;
-  attn_dq_convert_kernel<<<cgrid, 256, 0, stream>>>(dq_acc, (__nv_bfloat16*)dq, B, Hq, Sq, sdq[0], sdq[1], sdq[2], scale);
+  attn_bwd_kernel<<<dim3((Sk + BKV - 1) / BKV, Hk, B), BWD_THREADS, BWD_SMEM, stream>>>(tq, tk, tv, tdo, (const float*)lse, delta,
+                                                                                      (__nv_bfloat16*)dk, (__nv_bfloat16*)dv, g);
+  DqGeometry gq;
+  gq.B = B; gq.Hq = Hq; gq.Hk = Hk; gq.Sq = Sq; gq.Sk = Sk; gq.causal = causal; gq.scale = scale;
+  gq.dq_s = sdq[0]; gq.dq_b = sdq[1]; gq.dq_h = sdq[2];
+  gq.status = nullptr;
+  attn_bwd_dq_kernel<<<dim3((Sq + BQ - 1) / BQ, Hq, B), BWD_THREADS, DQ_SMEM, stream>>>(tq, tk, tv, tdo, (const float*)lse, delta,
+                                                                                      (__nv_bfloat16*)dq, gq);
   e = cudaGetLastError();
   if (e != cudaSuccess) set_last_error("dh_attn_bwd_noalloc launch failed: %s", cudaGetErrorString(e));
   return (int)e;

@@ -11,24 +11,24 @@
 // from inside the library would fail.  For them the scratch lives inside the library image.
 //
 // What it does.  Same maths and same kernels as dh_attn_bwd (head size 128, bf16, strided
-// [S, B, heads, d] operands, causal or full, grouped KV heads).  The scratch (softmax
-// row-dot products and the fp32 dQ accumulator) is a file-scope
+// [S, B, heads, d] operands, causal or full, grouped KV heads).  The scratch (one fp32 per
+// query row and head: the dot product of dO and O that both backward kernels read) is a
+// file-scope
 //     static __device__ __align__(256) unsigned char[DH_ATTN_NOALLOC_SCRATCH_BYTES]
 // in attention_sm100.cu.  Every GPU that loads the library holds those bytes until the
 // process exits, which is why the limit is modest.
 //
 // Limits and rules.
-//   * B * Hq * Sq rows need  rows*4 (rounded up to 256) + rows*128*4  bytes; a call that
-//     needs more than DH_ATTN_NOALLOC_SCRATCH_BYTES is rejected with cudaErrorInvalidValue
-//     and a message in dh_last_error_string().  40 MiB covers 65536 rows, for example
-//     Sq = 4096, B = 2, Hq = 8.
+//   * B * Hq * Sq rows need  rows*4 bytes (rounded up to 256); a call that needs more than
+//     DH_ATTN_NOALLOC_SCRATCH_BYTES is rejected with cudaErrorInvalidValue and a message in
+//     dh_last_error_string().  1 MiB covers 262144 rows, for example Sq = 4096, B = 8, Hq = 8.
 //   * The first call on each device resolves the scratch's device address
 //     (cudaGetSymbolAddress, with that device current) and opts the kernels into their
 //     shared-memory size.  Make that first call before any stream capture begins.
 //   * The function calls no cudaMalloc / cudaFree and no allocating library routine; the TMA
 //     descriptors are built on the caller's stack.
-//   * All calls on a device share the one array and it keeps the last call's contents.  The
-//     parts that must start at zero are cleared at the start of every call.  Two calls whose
+//   * All calls on a device share the one array and it keeps the last call's contents.
+//     Nothing in it has to start at zero: every call rewrites all the rows it reads.  Two calls whose
 //     GPU work overlaps (different streams, no ordering between them) race on the array:
 //     order them on one stream or with events.
 //   * Timed-out device waits are not reported through the status word by this entry point
@@ -37,7 +37,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
-#define DH_ATTN_NOALLOC_SCRATCH_BYTES (40u * 1024u * 1024u)
+#define DH_ATTN_NOALLOC_SCRATCH_BYTES (1u * 1024u * 1024u)
 
 #ifdef __cplusplus
 extern "C" {

@@ -1,8 +1,8 @@
 """ctypes glue for the sm_100a attention backward (csrc/attention_sm100.cu).
 
-The backward needs scratch memory beyond its inputs and outputs: ``delta = rowsum(dO * O)``
-and an fp32 accumulator for dQ that the key-block CTAs add into.  The scratch is taken from
-a small per-device cache here so that the hot path does not allocate.
+The backward needs scratch memory beyond its inputs and outputs: ``delta = rowsum(dO * O)``,
+one fp32 per query row and head, which both backward kernels read.  The scratch is taken
+from a small per-device cache here so that the hot path does not allocate.
 """
 from __future__ import annotations
 

@@ -156,9 +156,43 @@ def default_single(program: LayerProgram, strand: str) -> List[Block]:
     return blocks
 
 
+def _dense_tp_paired(program: LayerProgram) -> Optional[List[Block]]:
+    """Built-in pairing for the dense transformer layer (no ring steps, no experts).
+
+    Every collective but the very first is launched beside work that does not wait for it
+    and that lasts longer than the transfer at the headline shapes: the big GEMM groups of
+    the other strand, or a weight-gradient GEMM, which nothing downstream waits for.  The
+    row-parallel MLP weight gradient is deferred (``gemm_wgrad_mlp_l_n``) to sit beside the
+    last reduce-scatter together with the QKV weight gradient.  The reference's built-in
+    schedule (dhellam/core/dstb.py:1043-1059) follows the same idea with fewer fillers."""
+    act_f = "swiglu_mlp" if program.has("swiglu_mlp") else "gelu_mlp"
+    act_b = "swiglu_bwd" if program.has("swiglu_bwd") else "gelu_bwd"
+    needed = ["ln_attn", "allgather_attn", "gemm_attn_c", "fl_attn", "gemm_attn_l", "reduce_scatter_attn", "bda_attn", "ln_mlp",
+              "allgather_mlp", "gemm_mlp_c", act_f, "gemm_mlp_l", "reduce_scatter_mlp", "bda_mlp", "attn_bwd", act_b]
+    if not all(program.has(n) for n in needed) or len(program.fwd) != 14 or len(program.bwd) != 18:
+        return None
+    return [
+        Block(s1=["ln_attn"]),
+        Block(s2=["bda_mlp_bwd"], s3=["allgather_attn"]),
+        Block(s1=["gemm_attn_c", "fl_attn", "gemm_attn_l"], s3=["allgather_mlp_bwd"]),
+        Block(s2=["gemm_dgrad_mlp_l", "gemm_wgrad_mlp_l", act_b, "gemm_dgrad_mlp_c"], s3=["reduce_scatter_attn"]),
+        Block(s1=["bda_attn", "ln_mlp"], s3=["reduce_scatter_mlp_c_bwd"]),
+        Block(s2=["gemm_wgrad_mlp_c"], s3=["allgather_mlp"]),
+        Block(s2=["ln_mlp_bwd", "bda_attn_bwd"]),
+        Block(s1=["gemm_mlp_c", act_f, "gemm_mlp_l"], s3=["allgather_attn_bwd"]),
+        Block(s2=["gemm_dgrad_attn_l", "gemm_wgrad_attn_l", "attn_bwd", "gemm_dgrad_attn_c"], s3=["reduce_scatter_mlp"]),
+        Block(s1=["bda_mlp"], s2=["gemm_wgrad_attn_c", "gemm_wgrad_mlp_l_n"], s3=["reduce_scatter_attn_c_bwd"]),
+        Block(s2=["ln_attn_bwd"]),
+    ]
+
+
 def default_paired(program: LayerProgram) -> List[Block]:
-    """Alternating schedule: each strand's collective is launched together with the other
-    strand's next compute segment, so no collective runs without compute beside it."""
+    """Built-in paired schedule.  Dense layers get the hand-placed pairing above; any other
+    program gets the generic alternation: each strand's collective is launched together with
+    the other strand's next compute segment."""
+    dense = _dense_tp_paired(program)
+    if dense is not None:
+        return dense
     f = _segments(program, FWD)
     b = _segments(program, BWD)
     blocks: List[Block] = []
