@@ -42,6 +42,12 @@ def _launch(a, a_mn, b, b_mn, d, accumulate, M, N, Kdim, sm_budget, stream):
     K.check(rc, "dh_gemm_bf16")
 
 
+def set_gemm_mode(mode: int):
+    """Kernel choice on the GPU: 0 per problem (default), 1 single-CTA 128x256 tiles only,
+    2 CTA-pair 256x256 tiles (``tcgen05`` ``cta_group::2``) whenever M > 128."""
+    K.proto("dh_gemm_set_mode", [c_int], None)(int(mode))
+
+
 def gemm_nt(x, w, out=None, sm_budget: int = 0, stream=None, out_dtype=None):
     """``x [M,K] @ w[N,K]ᵀ -> [M,N]``."""
     M, Kd = x.shape

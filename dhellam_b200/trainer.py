@@ -36,6 +36,12 @@ class Trainer:
         if train.fused_comm and self.device.type == "cuda" and self.ps.tp > 1:
             from .ops.fused_comm import FusedTP
             fused = FusedTP(self.ps, cfg, train, self.device)
+        elif self.device.type == "cuda" and self.ps.world > 1 and train.dhellam:
+            # Library collectives co-run with the GEMMs and occupy one SM of many SM pairs;
+            # a CTA-pair GEMM then cannot place its clusters (measured 1.6x slower step),
+            # so that path keeps the single-CTA tiles.
+            from .ops.gemm import set_gemm_mode
+            set_gemm_mode(1)
         self.env = Env(cfg, self.ps, train, self.device, self.model.dtype, fused=fused)
         if strategy is None and train.schedule_config:
             strategy = Strategy.load(train.schedule_config)

@@ -29,8 +29,17 @@ def _seed_and_status():
     assert st.code == 0, f"device status {st.code} at {st.where}"
 
 
-@pytest.mark.parametrize("M,N,K_", [(128, 256, 64), (384, 1280, 1024), (200, 264, 136), (1024, 1024, 4096), (8, 4096, 256)])
-def test_gemm_three_layouts(M, N, K_):
+@pytest.fixture(params=[1, 2], ids=["single_cta", "cta_pair"])
+def gemm_mode(request):
+    from dhellam_b200.ops.gemm import set_gemm_mode
+    set_gemm_mode(request.param)
+    yield request.param
+    set_gemm_mode(0)
+
+
+@pytest.mark.parametrize("M,N,K_", [(128, 256, 64), (384, 1280, 1024), (200, 264, 136), (1024, 1024, 4096), (8, 4096, 256),
+                                    (2048, 1536, 2048), (1100, 520, 328)])
+def test_gemm_three_layouts(M, N, K_, gemm_mode):
     from dhellam_b200.ops.gemm import gemm_nn, gemm_nt, gemm_tn_acc
     x, w, dy = bf(M, K_), bf(N, K_), bf(M, N)
     assert rel(gemm_nt(x, w), x.float() @ w.float().t()) < 5e-3
@@ -43,7 +52,7 @@ def test_gemm_three_layouts(M, N, K_):
     assert rel(g2, dy.float().t() @ x.float()) < 1e-4
 
 
-def test_gemm_sm_budget_and_strided_output():
+def test_gemm_sm_budget_and_strided_output(gemm_mode):
     from dhellam_b200.ops.gemm import gemm_nt
     x, w = bf(512, 512), bf(768, 512)
     big = torch.zeros(512, 1024, dtype=torch.bfloat16, device=DEV)

@@ -32,6 +32,9 @@ def lr_at(args, it):
 
 
 def main(argv=None):
+    import os
+    if int(os.environ.get("WORLD_SIZE", "1")) == 1:   # library collectives are slow on growable segments
+        os.environ.setdefault("PYTORCH_CUDA_ALLOC_CONF", "expandable_segments:True")
     import torch
     import torch.distributed as dist
     from dhellam_b200.adaptor import initialize_dhellam_megatron
