@@ -43,6 +43,8 @@ def parse():
     ap.add_argument("--seq", type=int, default=0)
     ap.add_argument("--layers", type=int, default=0, help="override the layer count (debugging only; marks the run)")
     ap.add_argument("--no-fused-comm", action="store_true", help="library collectives instead of in-kernel ones")
+    ap.add_argument("--fused-policy", default=None, choices=["auto", "fused", "split"],
+                    help="in-kernel collectives: inside the GEMM kernels, as own kernels on the communication stream, or per site")
     ap.add_argument("--no-dual-strand", action="store_true", help="one stream, no forward/backward pairing")
     ap.add_argument("--schedule-config", default=None)
     ap.add_argument("--compute-streams", type=int, default=1, help="2 = let compute kernels of the two strands co-run")
@@ -117,6 +119,8 @@ def main():
     # (Only there: library collectives were measured ~1.7x slower on such segments.)
     if int(os.environ.get("WORLD_SIZE", "1")) == 1:
         os.environ.setdefault("PYTORCH_CUDA_ALLOC_CONF", "expandable_segments:True")
+    if args.fused_policy:
+        os.environ["DHELLAM_FUSED_POLICY"] = args.fused_policy
     import torch
     import torch.distributed as dist
     from dhellam_b200 import kernels as K
@@ -238,7 +242,8 @@ def main():
                        "heads": cfg.num_attention_heads, "kv_heads": cfg.num_query_groups, "vocab": cfg.vocab_size,
                        "global_batch": args.global_batch, "micro_batch": mbs, "seq_len": cfg.seq_length,
                        "parallelism": f"tp{N}+sp" if N > 1 else "single", "optimizer": "adam, fp32 master + fp32 main_grad",
-                       "fused_comm": bool(tr.env.fused_tp), "dual_strand": train.dhellam, "compute_streams": train.compute_streams,
+                       "fused_comm": bool(tr.env.fused_tp),
+                       "fused_policy": (tr.env.fused.policy if tr.env.fused_tp else None), "dual_strand": train.dhellam, "compute_streams": train.compute_streams,
                        "l2": "working set per step (weights + activations, tens of GB) is far larger than the 126 MB L2"},
             "clocks": clocks, "e2e": e2e, "gpu_launches": launches,
             "peak_mem_gib": round(torch.cuda.max_memory_allocated() / 2**30, 1),

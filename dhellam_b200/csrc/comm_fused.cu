@@ -188,6 +188,88 @@ __global__ void __launch_bounds__(256) wait_counters_kernel(const uint32_t* coun
   for (int i = threadIdx.x; i < n; i += blockDim.x) wait_counter_sys(count + i, target, nullptr, st, 640);
 }
 
+
+// Stand-alone sequence reduce-scatter over partial products that every rank wrote into its
+// own symmetric buffer `part[rank]` ([M][N], all rows).  The kernel first tells every peer
+// that this rank's partial is complete (it runs after the producing GEMM in stream order),
+// waits (bounded) for the same announcement from every peer, and then reduces its own
+// M/world rows: with a multicast alias of the buffers one `multimem.ld_reduce` per 16 bytes
+// lets the NVSwitch add the eight copies in fp32 and return the sum, so a GPU receives
+// M/world x N values instead of (world-1) times that; without the alias it reads the rows of
+// every peer with plain loads and adds in fp32.  A few CTAs without shared memory: they
+// share SMs with a GEMM that is running on the compute stream.
+struct RsrParams {
+  const __nv_bfloat16* part[MAX_RANKS];
+  const __nv_bfloat16* part_mc;
+  uint32_t* flag[MAX_RANKS];      // flag[p]: rank p's array of `world` announcement words
+  __nv_bfloat16* out;
+  int M, N, rank, world;
+  uint32_t target;
+  DeviceStatus* status;
+};
+
+__device__ __forceinline__ uint4 multimem_ld_reduce_bf16x8(const void* mc_addr) {
+  uint4 v;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(mc_addr)
+               : "memory");
+  return v;
+}
+__device__ __forceinline__ uint4 ld_relaxed_sys_v4(const void* p) {
+  uint4 v;
+  asm volatile("ld.relaxed.sys.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+  return v;
+}
+
+__global__ void __launch_bounds__(256) rs_reduce_kernel(const RsrParams p) {
+  __shared__ int ok_s;
+  if (threadIdx.x == 0) ok_s = 1;
+  if (blockIdx.x == 0 && threadIdx.x < p.world) {
+    asm volatile("fence.acq_rel.sys;" ::: "memory");
+    st_release_sys(p.flag[threadIdx.x] + p.rank, p.target);
+  }
+  __syncthreads();
+  if (threadIdx.x < p.world) {
+    if (!wait_counter_sys(p.flag[p.rank] + threadIdx.x, p.target, nullptr, p.status, 650)) ok_s = 0;
+  }
+  __syncthreads();
+  if (!ok_s) return;
+  const int rows = p.M / p.world;
+  const long long nvec = (long long)rows * p.N / 8;
+  const long long base = (long long)p.rank * rows * p.N;       // element offset of this rank's rows
+  constexpr int U = 4;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i0 = (long long)blockIdx.x * blockDim.x + threadIdx.x; i0 < nvec; i0 += stride * U) {
+    uint4 v[U];
+    if (p.part_mc != nullptr) {
+#pragma unroll
+      for (int u = 0; u < U; ++u)
+        if (i0 + u * stride < nvec) v[u] = multimem_ld_reduce_bf16x8(p.part_mc + base + (i0 + u * stride) * 8);
+    } else {
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        if (i0 + u * stride >= nvec) continue;
+        float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        for (int r = 0; r < p.world; ++r) {
+          const uint4 w = ld_relaxed_sys_v4(p.part[(p.rank + r) % p.world] + base + (i0 + u * stride) * 8);
+          const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float2 f = unpack_bf16x2(ww[j]);
+            acc[2 * j] += f.x;
+            acc[2 * j + 1] += f.y;
+          }
+        }
+        v[u] = make_uint4(pack_bf16x2(acc[0], acc[1]), pack_bf16x2(acc[2], acc[3]), pack_bf16x2(acc[4], acc[5]), pack_bf16x2(acc[6], acc[7]));
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u)
+      if (i0 + u * stride < nvec) st_v4(p.out + (i0 + u * stride) * 8, v[u]);
+  }
+}
+
 template <bool B_MN>
 __global__ void __launch_bounds__(THREADS, 1)
 ag_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, const AgParams p) {
@@ -632,6 +714,31 @@ int dh_gemm_rs_bf16(const void* a, int64_t lda, const void* b, int64_t ldb, int 
   else gemm_rs_kernel<false><<<grid, THREADS, RS_SMEM_BYTES, stream>>>(*ta, *tb, p);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) set_last_error("dh_gemm_rs_bf16 launch failed: %s", cudaGetErrorString(e));
+  return (int)e;
+}
+
+// Reduce-scatter of per-rank partial products that already sit in symmetric memory.
+// part_ptrs / flag_ptrs: `world` device pointers (every rank's partial buffer [M][N] and
+// announcement words); part_mc: multicast alias of the partial buffers or null; `target` is
+// the announcement value of this call (strictly increasing per buffer).
+int dh_rs_reduce(void* const* part_ptrs, const void* part_mc, void* const* flag_ptrs, void* out, int M, int N, int rank, int world,
+                 unsigned target, int ctas, cudaStream_t stream) {
+  if (world < 2 || world > MAX_RANKS) { set_last_error("dh_rs_reduce: world size %d not in [2, %d]", world, MAX_RANKS); return (int)cudaErrorInvalidValue; }
+  if (M % world != 0 || N % 8 != 0) { set_last_error("dh_rs_reduce: M must divide by world and N by 8 (M=%d N=%d)", M, N); return (int)cudaErrorInvalidValue; }
+  RsrParams p;
+  for (int i = 0; i < MAX_RANKS; ++i) {
+    p.part[i] = i < world ? (const __nv_bfloat16*)part_ptrs[i] : nullptr;
+    p.flag[i] = i < world ? (uint32_t*)flag_ptrs[i] : nullptr;
+  }
+  p.part_mc = (const __nv_bfloat16*)part_mc;
+  p.out = (__nv_bfloat16*)out;
+  p.M = M; p.N = N; p.rank = rank; p.world = world;
+  p.target = target;
+  p.status = reinterpret_cast<DeviceStatus*>(dh_status_device_ptr());
+  if (ctas <= 0) ctas = 32;
+  rs_reduce_kernel<<<ctas, 256, 0, stream>>>(p);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) set_last_error("dh_rs_reduce launch failed: %s", cudaGetErrorString(e));
   return (int)e;
 }
 

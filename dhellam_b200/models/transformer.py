@@ -124,9 +124,19 @@ def f_ln_attn(run):
     run.v["ln1"] = y
 
 
+def _split_site(env, w, transpose_w=False):
+    """True when the collective beside the GEMM with weight ``w`` runs as its own kernel on the
+    communication stream (decided per site by ``FusedTP.split``), False when it is fused into
+    the GEMM kernel."""
+    n, k = (w.shape[1], w.shape[0]) if transpose_w else (w.shape[0], w.shape[1])
+    return env.fused.split(env.fused.rows, n, k)
+
+
 def f_allgather_attn(run):
     env = run.env
     if env.fused_tp:
+        if _split_site(env, run.params.column_attn_weight):
+            env.fused.gather_start(_use(run, run.v["ln1"]), "attn_c")
         run.v["ln1_shard"] = run.v.pop("ln1")
     else:
         run.v["ln1_full"], _ = C.gather_along_first_dim(_use(run, run.v.pop("ln1")), env.ps.tp_group)
@@ -137,7 +147,10 @@ def f_gemm_attn_c(run):
     if env.fused_tp:
         # the gathered operand is not kept: the backward re-gathers the (8x smaller) shard
         shard = _use(run, run.v.pop("ln1_shard"))
-        qkv, _ = env.fused.ag_gemm(shard, p.column_attn_weight, "attn_c", sm_budget=run.budget("gemm_attn_c"))
+        if _split_site(env, p.column_attn_weight):
+            qkv = G.gemm_nt(env.fused.gather_wait("attn_c"), p.column_attn_weight, sm_budget=run.budget("gemm_attn_c"))
+        else:
+            qkv, _ = env.fused.ag_gemm(shard, p.column_attn_weight, "attn_c", sm_budget=run.budget("gemm_attn_c"))
         run.acts["ln1_shard"] = shard
     else:
         full = _use(run, run.v.pop("ln1_full"))
@@ -175,7 +188,10 @@ def f_fl_attn(run):
 def f_gemm_attn_l(run):
     env, p = run.env, run.params
     a = _use(run, run.v.pop("attn_out"))
-    if env.fused_tp:
+    if env.fused_tp and _split_site(env, p.linear_attn_weight):
+        part = env.fused.partial_buffer("attn_l", a.shape[0], p.linear_attn_weight.shape[0])
+        G.gemm_nt(a, p.linear_attn_weight, out=part, sm_budget=run.budget("gemm_attn_l"))
+    elif env.fused_tp:
         run.v["proj"] = env.fused.gemm_rs(a, p.linear_attn_weight, "attn_l", sm_budget=run.budget("gemm_attn_l"))
     else:
         run.v["proj_partial"] = G.gemm_nt(a, p.linear_attn_weight, sm_budget=run.budget("gemm_attn_l"))
@@ -185,6 +201,8 @@ def f_reduce_scatter_attn(run):
     env = run.env
     if not env.fused_tp:
         run.v["proj"], _ = C.reduce_scatter_along_first_dim(_use(run, run.v.pop("proj_partial")), env.ps.tp_group)
+    elif "proj" not in run.v:
+        run.v["proj"] = env.fused.rs_reduce("attn_l")
 
 
 def f_bda_attn(run):
@@ -205,6 +223,8 @@ def f_ln_mlp(run):
 def f_allgather_mlp(run):
     env = run.env
     if env.fused_tp:
+        if _split_site(env, run.params.column_mlp_weight):
+            env.fused.gather_start(_use(run, run.v["ln2"]), "mlp_c")
         run.v["ln2_shard"] = run.v.pop("ln2")
     else:
         run.v["ln2_full"], _ = C.gather_along_first_dim(_use(run, run.v.pop("ln2")), env.ps.tp_group)
@@ -214,7 +234,10 @@ def f_gemm_mlp_c(run):
     env, p = run.env, run.params
     if env.fused_tp:
         shard = _use(run, run.v.pop("ln2_shard"))
-        fc1, _ = env.fused.ag_gemm(shard, p.column_mlp_weight, "mlp_c", sm_budget=run.budget("gemm_mlp_c"))
+        if _split_site(env, p.column_mlp_weight):
+            fc1 = G.gemm_nt(env.fused.gather_wait("mlp_c"), p.column_mlp_weight, sm_budget=run.budget("gemm_mlp_c"))
+        else:
+            fc1, _ = env.fused.ag_gemm(shard, p.column_mlp_weight, "mlp_c", sm_budget=run.budget("gemm_mlp_c"))
         run.acts["ln2_shard"] = shard
     else:
         full = _use(run, run.v.pop("ln2_full"))
@@ -237,7 +260,10 @@ def f_act_mlp(run):
 def f_gemm_mlp_l(run):
     env, p = run.env, run.params
     a = _use(run, run.v.pop("act"))
-    if env.fused_tp:
+    if env.fused_tp and _split_site(env, p.linear_mlp_weight):
+        part = env.fused.partial_buffer("mlp_l", a.shape[0], p.linear_mlp_weight.shape[0])
+        G.gemm_nt(a, p.linear_mlp_weight, out=part, sm_budget=run.budget("gemm_mlp_l"))
+    elif env.fused_tp:
         run.v["fc2"] = env.fused.gemm_rs(a, p.linear_mlp_weight, "mlp_l", sm_budget=run.budget("gemm_mlp_l"))
     else:
         run.v["fc2_partial"] = G.gemm_nt(a, p.linear_mlp_weight, sm_budget=run.budget("gemm_mlp_l"))
@@ -247,6 +273,8 @@ def f_reduce_scatter_mlp(run):
     env = run.env
     if not env.fused_tp:
         run.v["fc2"], _ = C.reduce_scatter_along_first_dim(_use(run, run.v.pop("fc2_partial")), env.ps.tp_group)
+    elif "fc2" not in run.v:
+        run.v["fc2"] = env.fused.rs_reduce("mlp_l")
 
 
 def f_bda_mlp(run):
@@ -273,6 +301,8 @@ def b_bda_mlp_bwd(run):
 def b_allgather_mlp_bwd(run):
     env = run.env
     if env.fused_tp:
+        if _split_site(env, run.params.linear_mlp_weight, True):
+            env.fused.gather_start(_use(run, run.v["d_fc2"]), "mlp_l_bwd")
         run.v["d_fc2_shard"] = run.v.pop("d_fc2")
     else:
         run.v["d_fc2_full"], _ = C.gather_along_first_dim(_use(run, run.v.pop("d_fc2")), env.ps.tp_group)
@@ -280,7 +310,12 @@ def b_allgather_mlp_bwd(run):
 
 def b_gemm_dgrad_mlp_l(run):
     env, p = run.env, run.params
-    if env.fused_tp:
+    if env.fused_tp and _split_site(env, p.linear_mlp_weight, True):
+        _use(run, run.v.pop("d_fc2_shard"))
+        full = env.fused.gather_wait("mlp_l_bwd")
+        d_act = G.gemm_nn(full, p.linear_mlp_weight, sm_budget=run.budget("gemm_dgrad_mlp_l"))
+        run.v["d_fc2_full"] = full
+    elif env.fused_tp:
         d_act, full = env.fused.ag_gemm(_use(run, run.v.pop("d_fc2_shard")), p.linear_mlp_weight, "mlp_l_bwd", transpose_w=True,
                                         sm_budget=run.budget("gemm_dgrad_mlp_l"))
         run.v["d_fc2_full"] = full
@@ -307,7 +342,10 @@ def b_act_bwd(run):
 def b_gemm_dgrad_mlp_c(run):
     env, p = run.env, run.params
     d_fc1 = _use(run, run.v["d_fc1"])
-    if env.fused_tp:
+    if env.fused_tp and _split_site(env, p.column_mlp_weight, True):
+        part = env.fused.partial_buffer("mlp_c_bwd", d_fc1.shape[0], p.column_mlp_weight.shape[1])
+        G.gemm_nn(d_fc1, p.column_mlp_weight, out=part, sm_budget=run.budget("gemm_dgrad_mlp_c"))
+    elif env.fused_tp:
         run.v["d_ln2"] = env.fused.gemm_rs(d_fc1, p.column_mlp_weight, "mlp_c_bwd", transpose_w=True,
                                            sm_budget=run.budget("gemm_dgrad_mlp_c"))
     else:
@@ -328,6 +366,8 @@ def b_reduce_scatter_mlp_c_bwd(run):
     env = run.env
     if not env.fused_tp:
         run.v["d_ln2"], _ = C.reduce_scatter_along_first_dim(_use(run, run.v.pop("d_ln2_partial")), env.ps.tp_group)
+    elif "d_ln2" not in run.v:
+        run.v["d_ln2"] = env.fused.rs_reduce("mlp_c_bwd")
 
 
 def b_ln_mlp_bwd(run):
@@ -347,6 +387,8 @@ def b_bda_attn_bwd(run):
 def b_allgather_attn_bwd(run):
     env = run.env
     if env.fused_tp:
+        if _split_site(env, run.params.linear_attn_weight, True):
+            env.fused.gather_start(_use(run, run.v["d_proj"]), "attn_l_bwd")
         run.v["d_proj_shard"] = run.v.pop("d_proj")
     else:
         run.v["d_proj_full"], _ = C.gather_along_first_dim(_use(run, run.v.pop("d_proj")), env.ps.tp_group)
@@ -354,7 +396,12 @@ def b_allgather_attn_bwd(run):
 
 def b_gemm_dgrad_attn_l(run):
     env, p = run.env, run.params
-    if env.fused_tp:
+    if env.fused_tp and _split_site(env, p.linear_attn_weight, True):
+        _use(run, run.v.pop("d_proj_shard"))
+        full = env.fused.gather_wait("attn_l_bwd")
+        d_o = G.gemm_nn(full, p.linear_attn_weight, sm_budget=run.budget("gemm_dgrad_attn_l"))
+        run.v["d_proj_full"] = full
+    elif env.fused_tp:
         d_o, full = env.fused.ag_gemm(_use(run, run.v.pop("d_proj_shard")), p.linear_attn_weight, "attn_l_bwd", transpose_w=True,
                                       sm_budget=run.budget("gemm_dgrad_attn_l"))
         run.v["d_proj_full"] = full
@@ -390,7 +437,10 @@ def b_attn_bwd(run):
 def b_gemm_dgrad_attn_c(run):
     env, p = run.env, run.params
     d_qkv = _use(run, run.v["d_qkv"])
-    if env.fused_tp:
+    if env.fused_tp and _split_site(env, p.column_attn_weight, True):
+        part = env.fused.partial_buffer("attn_c_bwd", d_qkv.shape[0], p.column_attn_weight.shape[1])
+        G.gemm_nn(d_qkv, p.column_attn_weight, out=part, sm_budget=run.budget("gemm_dgrad_attn_c"))
+    elif env.fused_tp:
         run.v["d_ln1"] = env.fused.gemm_rs(d_qkv, p.column_attn_weight, "attn_c_bwd", transpose_w=True,
                                            sm_budget=run.budget("gemm_dgrad_attn_c"))
     else:
@@ -411,6 +461,8 @@ def b_reduce_scatter_attn_c_bwd(run):
     env = run.env
     if not env.fused_tp:
         run.v["d_ln1"], _ = C.reduce_scatter_along_first_dim(_use(run, run.v.pop("d_ln1_partial")), env.ps.tp_group)
+    elif "d_ln1" not in run.v:
+        run.v["d_ln1"] = env.fused.rs_reduce("attn_c_bwd")
 
 
 def b_ln_attn_bwd(run):

@@ -36,6 +36,13 @@ import torch.distributed as dist
 from .. import kernels as K
 
 AG_TAGS = ("attn_c", "mlp_c", "attn_l_bwd", "mlp_l_bwd", "regather_attn", "regather_mlp", "head")
+RS_TAGS = ("attn_l", "mlp_l", "mlp_c_bwd", "attn_c_bwd")
+
+
+def _site_times(M, N, Kd, world, width):
+    """Rough per-rank times (s) of a TP GEMM and of the collective beside it: the GEMM at
+    1.3 PFLOP/s, the transfer of (world-1)/world of an [M, width] bf16 operand at 600 GB/s."""
+    return 2.0 * M * N * Kd / 1.3e15, (world - 1) / world * M * width * 2 / 6.0e11
 
 
 def _align(n, a=1024):
@@ -72,6 +79,15 @@ class FusedTP:
             off += 2 * cnt_bytes
         self.off_rsc = [off, off + cnt_bytes]
         off += 2 * cnt_bytes
+        self.off_rsflag = {}
+        for t in RS_TAGS:
+            self.off_rsflag[t] = [off, off + cnt_bytes]
+            off += 2 * cnt_bytes
+        self.off_split = {}
+        for t in RS_TAGS:                       # partial products of the split reduce-scatter, [rows, width] each
+            self.off_split[t] = [off, off + stage_bytes]
+            off += 2 * stage_bytes
+        cnt_end = self.off_split[RS_TAGS[0]][0]
         self.buf = symm_mem.empty(off, dtype=torch.uint8, device=self.device)
         group = ps.tp_group
         self.hdl = symm_mem.rendezvous(self.buf, group=group.group_name)
@@ -84,7 +100,7 @@ class FusedTP:
             except Exception:
                 mc = 0
         self.mc_ptr = mc
-        self.buf[cnt_base:].zero_()
+        self.buf[cnt_base:cnt_end].zero_()
         torch.cuda.synchronize(self.device)
         dist.barrier(group=group)                 # nobody pushes before every rank's counters are zero
         self.total_ag = {t: [0, 0] for t in AG_TAGS}     # counter value reached so far, per (tag, parity)
@@ -94,6 +110,23 @@ class FusedTP:
         self._last = None
         self._arr = ctypes.c_void_p * self.world
         self._pending = {}
+        self.calls_split = {t: 0 for t in RS_TAGS}
+        self._split_pending = {}
+        # "fused": every collective inside its GEMM kernel; "split": every collective as its own
+        # small kernel on the communication stream (the GEMM stays a plain local GEMM), so that the
+        # schedule can hide it behind the other strand; "auto": split where the transfer outlasts
+        # half of the GEMM it belongs to.
+        self.policy = os.environ.get("DHELLAM_FUSED_POLICY", "auto")
+        self.rs_ctas = int(os.environ.get("DHELLAM_RS_CTAS", "0")) or max(16, 128 // self.world)
+
+    def split(self, M: int, N: int, Kd: int) -> bool:
+        """Whether the collective beside the GEMM ``[M, Kd] x [Kd, N]`` runs as its own kernel."""
+        if self.policy == "split":
+            return True
+        if self.policy == "fused":
+            return False
+        t_gemm, t_comm = _site_times(M, N, Kd, self.world, self.width)
+        return t_comm > 0.5 * t_gemm
 
     # ------------------------------------------------------------------ helpers
     def _ptr_array(self, off):
@@ -198,3 +231,25 @@ class FusedTP:
     def all_gather(self, shard, tag: str):
         self.gather_start(shard, tag)
         return self.gather_wait(tag)
+
+    # ------------------------------------------------------------------ stand-alone reduce-scatter
+    def partial_buffer(self, tag: str, M: int, N: int):
+        """Symmetric-memory tensor ``[M, N]`` for this rank's partial product of ``tag``; the GEMM
+        writes it, ``rs_reduce(tag)`` then returns this rank's rows of the sum over ranks."""
+        assert M == self.rows and N <= self.width and tag in self.off_split
+        slot = self.calls_split[tag] & 1
+        self.calls_split[tag] += 1
+        off = self.off_split[tag][slot]
+        self._split_pending[tag] = (slot, (self.calls_split[tag] + 1) // 2, M, N)
+        return self.buf[off:off + M * N * 2].view(torch.bfloat16).view(M, N)
+
+    def rs_reduce(self, tag: str):
+        """Runs on the current stream, which must already wait for the GEMM that filled the buffer."""
+        slot, use, M, N = self._split_pending.pop(tag)
+        out = torch.empty((M // self.world, N), dtype=torch.bfloat16, device=self.device)
+        s = torch.cuda.current_stream(self.device)
+        fn = K.proto("dh_rs_reduce", [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_uint, c_int, c_void_p])
+        off = self.off_split[tag][slot]
+        K.check(fn(self._ptr_array(off), self._mc(off), self._ptr_array(self.off_rsflag[tag][slot]), out.data_ptr(), M, N, self.rank,
+                   self.world, use, self.rs_ctas, s.cuda_stream), "dh_rs_reduce")
+        return out

@@ -106,6 +106,15 @@ def _fused_worker(rank, world, rows, h, n_out, iters):
         ref3, _ = C.reduce_scatter_along_first_dim(gemm_nn(a, w3), ps.tp_group)
         got3 = fused.gemm_rs(a, w3, transpose_w=True)
         assert _rel(got3, ref3) < 1e-2, _rel(got3, ref3)
+        # the reduce-scatter alone: a local GEMM into symmetric memory, then the in-switch
+        # (or peer-load) reduction; with and without the multicast alias
+        for mc in (fused.mc_ptr, 0):
+            keep, fused.mc_ptr = fused.mc_ptr, mc
+            part = fused.partial_buffer("attn_l", rows, h)
+            gemm_nt(a, w2, out=part)
+            got4 = fused.rs_reduce("attn_l")
+            fused.mc_ptr = keep
+            assert _rel(got4, ref) < 1e-2, (_rel(got4, ref), mc)
     torch.cuda.synchronize()
     st = K.read_status()
     assert st.code == 0, (st.code, st.where, st.extra)
@@ -117,7 +126,8 @@ def test_fused_ag_gemm_and_gemm_rs_match_nccl_composition():
     run_gpu_ranks(_fused_worker, world, 2048, 1024, 768, 3)
 
 
-def _engine_worker(rank, world, fused, out_path):
+def _engine_worker(rank, world, fused, out_path, policy="auto"):
+    os.environ["DHELLAM_FUSED_POLICY"] = policy
     from dhellam_b200 import kernels as K
     from dhellam_b200.config import ModelConfig, ParallelConfig, TrainConfig
     from dhellam_b200.data import make_microbatch, synthetic_tokens
@@ -148,12 +158,18 @@ def _engine_worker(rank, world, fused, out_path):
 
 def test_tp_engine_fused_matches_unfused(tmp_path):
     _need(2)
-    a, b = str(tmp_path / "fused.pt"), str(tmp_path / "nccl.pt")
-    run_gpu_ranks(_engine_worker, 2, True, a)
+    b = str(tmp_path / "nccl.pt")
     run_gpu_ranks(_engine_worker, 2, False, b)
-    ra, rb = torch.load(a), torch.load(b)
-    assert ra["fused"] and not rb["fused"]
-    for x, y in zip(ra["losses"], rb["losses"]):
-        assert abs(x - y) / abs(y) < 1e-2, (ra["losses"], rb["losses"])
-    assert _rel(ra["g_ln"], rb["g_ln"]) < 5e-2
-    assert _rel(ra["g_qkv"], rb["g_qkv"]) < 5e-2
+    rb = torch.load(b)
+    assert not rb["fused"]
+    # every collective inside its GEMM kernel / every collective as its own kernel on the
+    # communication stream
+    for policy in ("fused", "split"):
+        a = str(tmp_path / f"{policy}.pt")
+        run_gpu_ranks(_engine_worker, 2, True, a, policy)
+        ra = torch.load(a)
+        assert ra["fused"]
+        for x, y in zip(ra["losses"], rb["losses"]):
+            assert abs(x - y) / abs(y) < 1e-2, (policy, ra["losses"], rb["losses"])
+        assert _rel(ra["g_ln"], rb["g_ln"]) < 5e-2, policy
+        assert _rel(ra["g_qkv"], rb["g_qkv"]) < 5e-2, policy
