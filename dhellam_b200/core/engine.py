@@ -168,6 +168,8 @@ class DoubleStrandEngine:
                 saved_acts = self.acts.pop((b, b_idx))
                 hand_over(saved_acts, st.s2)
                 brun = LayerRun(b_params, saved_acts, mbs[b], self.env, {"dout": g}, b_idx)
+            if self.env.fused is not None:
+                self.env.fused.paired = frun is not None and brun is not None
             self.executor.run(frun, brun)
             if fa:
                 x = frun.v["out"]
