@@ -38,7 +38,7 @@ def parse():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="native", choices=["native", "reference"])
     ap.add_argument("--model", default="llama3.1-70b-8l")
-    ap.add_argument("--micro-batch", type=int, default=0, help="0 = 4 where it fits in 180 GB, else 2")
+    ap.add_argument("--micro-batch", type=int, default=0, help="0 = 4 on 2+ GPUs, 1 on one GPU (whose 180 GB hold ~150 GiB of weights and optimizer state)")
     ap.add_argument("--global-batch", type=int, default=32)
     ap.add_argument("--seq", type=int, default=0)
     ap.add_argument("--layers", type=int, default=0, help="override the layer count (debugging only; marks the run)")
@@ -144,7 +144,7 @@ def main():
     if args.layers:
         over["num_layers"] = args.layers
     cfg = preset(args.model, **over)
-    mbs = args.micro_batch or (4 if N >= 2 else 2)
+    mbs = args.micro_batch or (4 if N >= 2 else 1)
     train = TrainConfig(micro_batch_size=mbs, global_batch_size=args.global_batch, dtype="bf16", fused_comm=not args.no_fused_comm,
                         dhellam=not args.no_dual_strand, schedule_config=args.schedule_config,
                         compute_streams=args.compute_streams)
