@@ -327,6 +327,12 @@ struct BwdGeometry {
   int B, Hq, Hk, Sq, Sk, causal;
   float scale;
   long long dk_s, dk_b, dk_h, dv_s, dv_b, dv_h;
+  // Head split: the query heads of one KV head are divided over `hs` CTAs (grid.y = Hk * hs) when
+  // KV blocks x batch x KV heads alone would leave SMs idle (tensor parallelism leaves one KV head per
+  // GPU).  Each CTA then writes fp32 partial dV / dK to `part` ([2][hs][Sk][B][Hk][128]) and
+  // attn_dkv_reduce_kernel adds them up.
+  int hs;
+  float* part;
   DeviceStatus* status;
 };
 
@@ -345,8 +351,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
   BwdCtl* ctl = reinterpret_cast<BwdCtl*>(smem + 6 * TILE_BYTES);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int kb = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
+  const int kb = blockIdx.x, hk = blockIdx.y / g.hs, hpart = blockIdx.y % g.hs, b = blockIdx.z;
   const int group = g.Hq / g.Hk;
+  const int gpp = group / g.hs;                 // query heads handled by this CTA
+  const int hq0 = hk * group + hpart * gpp;
   const int off = g.Sk - g.Sq;
   const int nqb = (g.Sq + BQ - 1) / BQ;
   // first query block that sees any key of this block: i + off >= kb*BKV
@@ -355,7 +363,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
     const int first_q = kb * BKV - off;
     qb0 = first_q <= 0 ? 0 : first_q / BQ;
   }
-  const int n_iter = qb0 < nqb ? (nqb - qb0) * group : 0;
+  const int n_iter = qb0 < nqb ? (nqb - qb0) * gpp : 0;
 
   if (threadIdx.x == 0) {
     mbar_init(&ctl->kv_full, 1); mbar_init(&ctl->qdo_full, 1); mbar_init(&ctl->qdo_empty, 1);
@@ -380,8 +388,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
       tma_load_4d(sV, &tv, &ctl->kv_full, 0, hk, b, kb * BKV);
       tma_load_4d(sV + HALF_BYTES, &tv, &ctl->kv_full, 64, hk, b, kb * BKV);
       for (int it = 0; it < n_iter; ++it) {
-        const int hq = hk * group + it % group;
-        const int qb = qb0 + it / group;
+        const int hq = hq0 + it % gpp;
+        const int qb = qb0 + it / gpp;
         if (!mbar_wait(&ctl->qdo_empty, (it & 1) ^ 1, abort_flag, g.status, 500)) break;
         mbar_expect_tx(&ctl->qdo_full, 2 * TILE_BYTES);
         tma_load_4d(sQ, &tq, &ctl->qdo_full, 0, hq, b, qb * BQ);
@@ -429,8 +437,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
     bool ok = n_iter > 0;
     for (int it = 0; it < n_iter && ok; ++it) {
       const uint32_t ph = it & 1;
-      const int hq = hk * group + it % group;
-      const int qb = qb0 + it / group;
+      const int hq = hq0 + it % gpp;
+      const int qb = qb0 + it / gpp;
       const int qi = qb * BQ + r;
       const bool row_ok = qi < g.Sq;
       const long long stat = ((long long)b * g.Hq + hq) * g.Sq + qi;
@@ -474,7 +482,39 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
     }
     // dK (times scale) and dV of this key block
     const int kj = kb * BKV + r;
-    if (ok && n_iter > 0) {
+    // fp32 partial rows of this CTA's head part (head split only)
+    const long long part_elems = (long long)g.Sk * g.B * g.Hk * D;
+    float* pdv = g.hs > 1 ? g.part + (long long)hpart * part_elems + (((long long)kj * g.B + b) * g.Hk + hk) * D : nullptr;
+    float* pdk = g.hs > 1 ? pdv + (long long)g.hs * part_elems : nullptr;
+    if (g.hs > 1) {
+      if (ok && n_iter > 0) {
+        if (mbar_wait(&ctl->acc_full, 0, abort_flag, g.status, 523)) {
+          tc_fence_after();
+#pragma unroll 1
+          for (int c = c_lo; c < c_lo + 2; ++c) {
+            uint32_t a[32], bb[32];
+            tmem_ld32(tmem + 256 + lane_base + c * 32, a);      // warp-collective: no per-lane branch around it
+            tmem_ld32(tmem + 384 + lane_base + c * 32, bb);
+            tmem_ld_wait();
+            if (kj < g.Sk) {
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                reinterpret_cast<float4*>(pdv + c * 32)[j] = make_float4(__uint_as_float(a[4 * j]), __uint_as_float(a[4 * j + 1]),
+                                                                         __uint_as_float(a[4 * j + 2]), __uint_as_float(a[4 * j + 3]));
+                reinterpret_cast<float4*>(pdk + c * 32)[j] =
+                    make_float4(__uint_as_float(bb[4 * j]) * g.scale, __uint_as_float(bb[4 * j + 1]) * g.scale,
+                                __uint_as_float(bb[4 * j + 2]) * g.scale, __uint_as_float(bb[4 * j + 3]) * g.scale);
+              }
+            }
+          }
+        }
+      } else if (n_iter == 0 && kj < g.Sk) {
+        for (int i = c_lo * 8; i < c_lo * 8 + 16; ++i) {
+          reinterpret_cast<float4*>(pdv)[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+          reinterpret_cast<float4*>(pdk)[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+      }
+    } else if (ok && n_iter > 0) {
       if (mbar_wait(&ctl->acc_full, 0, abort_flag, g.status, 522)) {
         tc_fence_after();
         __nv_bfloat16* dvr = dv + (long long)kj * g.dv_s + (long long)b * g.dv_b + (long long)hk * g.dv_h;
@@ -516,6 +556,35 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
   tc_fence_before();
   __syncthreads();
   if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem, 512); }
+}
+
+// Sums the `hs` fp32 partials of a head-split backward and writes bf16 dK / dV.
+// One thread per 8 consecutive head-dim elements of one (key, batch, KV head) row of dV and of dK.
+__global__ void __launch_bounds__(256) attn_dkv_reduce_kernel(const float* __restrict__ part, int hs, __nv_bfloat16* __restrict__ dk,
+                                                              __nv_bfloat16* __restrict__ dv, int Sk, int B, int Hk, long long dk_s,
+                                                              long long dk_b, long long dk_h, long long dv_s, long long dv_b,
+                                                              long long dv_h) {
+  const long long nvec = (long long)Sk * B * Hk * (D / 8);
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= 2 * nvec) return;
+  const int which = i >= nvec;                  // 0: dV, 1: dK
+  const long long v = which ? i - nvec : i;
+  const int c8 = (int)(v % (D / 8));
+  const long long row = v / (D / 8);            // (kj * B + b) * Hk + hk
+  const int hk = (int)(row % Hk), b = (int)((row / Hk) % B);
+  const long long kj = row / ((long long)Hk * B);
+  const long long part_elems = (long long)Sk * B * Hk * D;
+  const float* src = part + (long long)which * hs * part_elems + row * D + c8 * 8;
+  float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  for (int h = 0; h < hs; ++h) {
+    const float4 x = *reinterpret_cast<const float4*>(src + (long long)h * part_elems);
+    const float4 y = *reinterpret_cast<const float4*>(src + (long long)h * part_elems + 4);
+    acc[0] += x.x; acc[1] += x.y; acc[2] += x.z; acc[3] += x.w;
+    acc[4] += y.x; acc[5] += y.y; acc[6] += y.z; acc[7] += y.w;
+  }
+  __nv_bfloat16* dst = which ? dk + kj * dk_s + b * dk_b + hk * dk_h : dv + kj * dv_s + b * dv_b + hk * dv_h;
+  reinterpret_cast<uint4*>(dst)[c8] = make_uint4(pack_bf16x2(acc[0], acc[1]), pack_bf16x2(acc[2], acc[3]), pack_bf16x2(acc[4], acc[5]),
+                                                 pack_bf16x2(acc[6], acc[7]));
 }
 
 // ----------------------------------------------------------------------- backward, dQ
@@ -744,8 +813,27 @@ int dh_attn_fwd(const void* q, const void* k, const void* v, void* out, void* ls
   return (int)e;
 }
 
-// Scratch: delta [B*Hq*Sq] fp32 (row dot products of dO and O), rounded up to 256 bytes.
-int64_t dh_attn_bwd_scratch_bytes(int B, int Hq, int Sq) { return ((int64_t)B * Hq * Sq * 4 + 255) / 256 * 256; }
+// Number of CTAs that share the query heads of one KV head in the dK/dV kernel: 1 while
+// KV blocks x batch x KV heads already give every SM a few CTAs, else the smallest power of
+// two (dividing the group size) that does.
+static int bwd_head_split(int B, int Hq, int Hk, int Sk) {
+  const int group = Hq / Hk;
+  const long long ctas = (long long)((Sk + BKV - 1) / BKV) * B * Hk;
+  int hs = 1;
+  while (hs < group && group % (hs * 2) == 0 && ctas * hs < 4LL * dh_sm_count()) hs *= 2;
+  return hs;
+}
+
+// Scratch: delta [B*Hq*Sq] fp32 (row dot products of dO and O), rounded up to 256 bytes, then, when
+// the dK/dV kernel splits heads, the fp32 partials [2][hs][Sk][B][Hk][128].
+int64_t dh_attn_bwd_scratch_bytes(int B, int Hq, int Hk, int Sq, int Sk) {
+  int64_t n = ((int64_t)B * Hq * Sq * 4 + 255) / 256 * 256;
+  if (Hk > 0 && Hq % Hk == 0) {
+    const int hs = bwd_head_split(B, Hq, Hk, Sk);
+    if (hs > 1) n += (int64_t)2 * hs * Sk * B * Hk * D * 4;
+  }
+  return n;
+}
 
 int dh_attn_bwd(const void* dout, const void* q, const void* k, const void* v, const void* out, const void* lse, void* dq, void* dk,
                 void* dv, void* scratch, const int64_t* strides /* 8 tensors x (s,b,h): do,q,k,v,o,dq,dk,dv */, int B, int Hq, int Hk,
@@ -777,8 +865,15 @@ int dh_attn_bwd(const void* dout, const void* q, const void* k, const void* v, c
   g.B = B; g.Hq = Hq; g.Hk = Hk; g.Sq = Sq; g.Sk = Sk; g.causal = causal; g.scale = scale;
   g.dk_s = sdk[0]; g.dk_b = sdk[1]; g.dk_h = sdk[2]; g.dv_s = sdv[0]; g.dv_b = sdv[1]; g.dv_h = sdv[2];
   g.status = st;
-  attn_bwd_kernel<<<dim3((Sk + BKV - 1) / BKV, Hk, B), BWD_THREADS, BWD_SMEM, stream>>>(*tq, *tk, *tv, *tdo, (const float*)lse, delta,
-                                                                                      (__nv_bfloat16*)dk, (__nv_bfloat16*)dv, g);
+  g.hs = bwd_head_split(B, Hq, Hk, Sk);
+  g.part = g.hs > 1 ? reinterpret_cast<float*>(reinterpret_cast<char*>(scratch) + ((int64_t)rows * 4 + 255) / 256 * 256) : nullptr;
+  attn_bwd_kernel<<<dim3((Sk + BKV - 1) / BKV, Hk * g.hs, B), BWD_THREADS, BWD_SMEM, stream>>>(*tq, *tk, *tv, *tdo, (const float*)lse, delta,
+                                                                                             (__nv_bfloat16*)dk, (__nv_bfloat16*)dv, g);
+  if (g.hs > 1) {
+    const long long n = 2LL * Sk * B * Hk * (D / 8);
+    attn_dkv_reduce_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(g.part, g.hs, (__nv_bfloat16*)dk, (__nv_bfloat16*)dv, Sk, B, Hk,
+                                                                           sdk[0], sdk[1], sdk[2], sdv[0], sdv[1], sdv[2]);
+  }
   DqGeometry gq;
   gq.B = B; gq.Hq = Hq; gq.Hk = Hk; gq.Sq = Sq; gq.Sk = Sk; gq.causal = causal; gq.scale = scale;
   gq.dq_s = sdq[0]; gq.dq_b = sdq[1]; gq.dq_h = sdq[2];
@@ -859,6 +954,8 @@ extern "C" int dh_attn_bwd_noalloc(const void* dout, const void* q, const void* 
   g.B = B; g.Hq = Hq; g.Hk = Hk; g.Sq = Sq; g.Sk = Sk; g.causal = causal; g.scale = scale;
   g.dk_s = sdk[0]; g.dk_b = sdk[1]; g.dk_h = sdk[2]; g.dv_s = sdv[0]; g.dv_b = sdv[1]; g.dv_h = sdv[2];
   g.status = nullptr;
+  g.hs = 1;              // the built-in scratch holds delta only: no head split here
+  g.part = nullptr;
   attn_bwd_kernel<<<dim3((Sk + BKV - 1) / BKV, Hk, B), BWD_THREADS, BWD_SMEM, stream>>>(tq, tk, tv, tdo, (const float*)lse, delta,
                                                                                       (__nv_bfloat16*)dk, (__nv_bfloat16*)dv, g);
   DqGeometry gq;

@@ -56,6 +56,7 @@ struct Params {
   int M, N, K;
   int tiles_m, tiles_n;
   int accumulate;
+  int stages, group_m;          // CTA-pair kernel: ring depth in use, m-tiles per L2 band
   DeviceStatus* status;
 };
 
@@ -306,13 +307,12 @@ static int launch(const CUtensorMap* ta, const CUtensorMap* tb, const Params& p,
 // can still signal it.
 // ---------------------------------------------------------------------------------------
 namespace pair {
-constexpr int STAGES2 = 6;
+constexpr int STAGES2 = 7;                        // ring slots allocated; Params.stages of them are used
 constexpr int TILE_M = 2 * BM;                     // 256 rows per CTA pair
 constexpr int BN_HALF = BN / 2;                    // B columns loaded by each CTA
 constexpr int A2_STAGE_BYTES = BM * BK * 2;        // 16 KiB
 constexpr int B2_STAGE_BYTES = BN_HALF * BK * 2;   // 16 KiB
 constexpr int STAGE2_BYTES = A2_STAGE_BYTES + B2_STAGE_BYTES;
-constexpr int GROUP_M2 = 4;
 
 struct __align__(8) Control2 {
   uint64_t full[STAGES2];
@@ -324,11 +324,11 @@ struct __align__(8) Control2 {
 };
 constexpr int SMEM2_BYTES = STAGES2 * STAGE2_BYTES + 1024 + 256;
 
-__device__ __forceinline__ void tile_coords2(int t, int tiles_m, int tiles_n, int& tm, int& tn) {
-  const int band = GROUP_M2 * tiles_n;
+__device__ __forceinline__ void tile_coords2(int t, int tiles_m, int tiles_n, int group_m, int& tm, int& tn) {
+  const int band = group_m * tiles_n;
   const int g = t / band;
-  const int first_m = g * GROUP_M2;
-  const int rows = min(GROUP_M2, tiles_m - first_m);
+  const int first_m = g * group_m;
+  const int rows = min(group_m, tiles_m - first_m);
   const int r = t - g * band;
   tm = first_m + (r % rows);
   tn = r / rows;
@@ -384,7 +384,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       bool ok = true;
       for (int t = pair_id; t < num_tiles && ok; t += num_pairs) {
         int tm, tn;
-        tile_coords2(t, p.tiles_m, p.tiles_n, tm, tn);
+        tile_coords2(t, p.tiles_m, p.tiles_n, p.group_m, tm, tn);
         const int m0 = tm * TILE_M + (int)rank * BM;
         const int n0 = tn * BN + (int)rank * BN_HALF;
         for (int kb = 0; kb < num_kb; ++kb) {
@@ -406,7 +406,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           } else {
             tma_load_2d_2sm(b_dst, &tmap_b, full_leader, k0, n0);
           }
-          if (++s == STAGES2) { s = 0; ph ^= 1; }
+          if (++s == p.stages) { s = 0; ph ^= 1; }
         }
       }
     }
@@ -440,7 +440,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           const uint32_t e = smem_u32(&ctl->empty[s]);
           umma_commit_2sm(mapa_u32(e, 0));
           umma_commit_2sm(mapa_u32(e, 1));
-          if (++s == STAGES2) { s = 0; ph ^= 1; }
+          if (++s == p.stages) { s = 0; ph ^= 1; }
         }
         if (!ok) break;
         const uint32_t f = smem_u32(&ctl->acc_full[acc]);
@@ -458,7 +458,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     bool ok = true;
     for (int t = pair_id; t < num_tiles && ok; t += num_pairs) {
       int tm, tn;
-      tile_coords2(t, p.tiles_m, p.tiles_n, tm, tn);
+      tile_coords2(t, p.tiles_m, p.tiles_n, p.group_m, tm, tn);
       if (!mbar_wait(&ctl->acc_full[acc], acc_ph, abort_flag, p.status, 310)) { ok = false; break; }
       tc_fence_after();
       const int row = tm * TILE_M + (int)rank * BM + quarter * 32 + lane;
@@ -548,6 +548,15 @@ extern "C" int dh_gemm_bf16(const void* a, int64_t lda, int a_mn_major, const vo
   const int mode = gemm_mode();
   const bool use_pair = mode != 1 && M > BM;
   const int b_rows = use_pair ? pair::BN_HALF : BN;
+  static int pair_stages = 0, pair_group = 0;
+  if (pair_stages == 0) {
+    const char* e = getenv("DHELLAM_GEMM_STAGES");
+    pair_stages = e ? atoi(e) : 6;
+    if (pair_stages < 2 || pair_stages > pair::STAGES2) pair_stages = 6;
+    e = getenv("DHELLAM_GEMM_GROUP");
+    pair_group = e ? atoi(e) : 8;        // 8 x 256 rows per L2 band measured best at the large shapes
+    if (pair_group < 1) pair_group = 8;
+  }
   // K-major operand: tensor (inner K, outer rows); MN-major operand: (inner rows, outer K).
   const CUtensorMap* ta = a_mn_major ? get_tmap_2d(a, 2, (uint64_t)M, (uint64_t)K, (uint64_t)lda * 2, 64, BK, true)
                                      : get_tmap_2d(a, 2, (uint64_t)K, (uint64_t)M, (uint64_t)lda * 2, BK, BM, true);
@@ -564,6 +573,8 @@ extern "C" int dh_gemm_bf16(const void* a, int64_t lda, int a_mn_major, const vo
   p.tiles_m = use_pair ? (M + pair::TILE_M - 1) / pair::TILE_M : (M + BM - 1) / BM;
   p.tiles_n = (N + BN - 1) / BN;
   p.accumulate = accumulate;
+  p.stages = pair_stages;
+  p.group_m = pair_group;
   p.status = reinterpret_cast<DeviceStatus*>(dh_status_device_ptr());
   const int sms = dh_sm_count();
   int budget = (sm_budget <= 0 || sm_budget > sms) ? sms : sm_budget;

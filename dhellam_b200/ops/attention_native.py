@@ -1,8 +1,10 @@
 """ctypes glue for the sm_100a attention backward (csrc/attention_sm100.cu).
 
 The backward needs scratch memory beyond its inputs and outputs: ``delta = rowsum(dO * O)``,
-one fp32 per query row and head, which both backward kernels read.  The scratch is taken
-from a small per-device cache here so that the hot path does not allocate.
+one fp32 per query row and head, which both backward kernels read, and, when the dK/dV kernel
+splits the query heads of a KV head over several CTAs (few KV heads per GPU), their fp32
+partial sums.  The scratch is taken from a small per-device cache here so that the hot path
+does not allocate.
 """
 from __future__ import annotations
 
@@ -30,8 +32,8 @@ def attn_bwd_native(dout, q, k, v, out, lse, dq, dk, dv, causal, scale, sm_budge
     Sk, Hk = k.shape[0], k.shape[2]
     for t in (dout, q, k, v, out, dq, dk, dv):
         assert t.stride(3) == 1 and t.dtype == torch.bfloat16
-    nbytes_fn = K.proto("dh_attn_bwd_scratch_bytes", [c_int, c_int, c_int], c_int64)
-    scratch = _scratch_for(q.device, nbytes_fn(B, Hq, Sq))
+    nbytes_fn = K.proto("dh_attn_bwd_scratch_bytes", [c_int, c_int, c_int, c_int, c_int], c_int64)
+    scratch = _scratch_for(q.device, nbytes_fn(B, Hq, Hk, Sq, Sk))
     strides = []
     for t in (dout, q, k, v, out, dq, dk, dv):
         strides += [t.stride(0), t.stride(1), t.stride(2)]

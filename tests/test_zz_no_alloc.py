@@ -61,11 +61,12 @@ def test_noalloc_attention_backward_matches_regular_entry_point_twice():
         rc, dq, dk, dv = _call_noalloc(lib, dout, q, k, v, out, lse, causal, scale)
         assert rc == 0, lib.dh_last_error_string().decode()
         torch.cuda.synchronize()
-        # same kernels, same inputs, no atomics anywhere: the results are bitwise equal
-        assert _rel(dq, ref_dq) < 2e-2
-        assert _rel(dk, ref_dk) < 2e-2
-        assert _rel(dv, ref_dv) < 2e-2
-        assert torch.equal(dq, ref_dq) and torch.equal(dk, ref_dk) and torch.equal(dv, ref_dv)
+        # dQ: same kernel, same inputs, no atomics: bitwise equal.  dK / dV: the regular entry
+        # point may split the query heads of a KV head over several CTAs and add their fp32
+        # partial sums afterwards (it has the scratch for that), so only the rounding can differ.
+        assert torch.equal(dq, ref_dq)
+        assert _rel(dk, ref_dk) < 5e-3
+        assert _rel(dv, ref_dv) < 5e-3
 
 
 def test_noalloc_attention_backward_rejects_oversized_problem():
