@@ -176,6 +176,7 @@ class DoubleStrandEngine:
             if fb:
                 g = brun.v["dx"]
                 if b == N - 1 and self.grad_reducer is not None:
+                    self.executor.flush_carry()       # a weight gradient handed to the next layer run belongs to this layer
                     self.grad_reducer.layer_final(b_idx, st.s2 if st.cuda else None)
         if fa and st.cuda:
             ev = torch.cuda.Event()
@@ -256,6 +257,7 @@ class DoubleStrandEngine:
             st.fork_from(torch.cuda.current_stream())
         for t in range(PP.total_ticks(self.P, N)):
             self.tick(t, mbs)
+        self.executor.flush_carry()
         if st.cuda:
             st.join_all_into(torch.cuda.current_stream())
         assert not self.acts, f"activations left over: {list(self.acts.keys())[:4]}"

@@ -21,7 +21,7 @@ from dataclasses import dataclass, field
 from typing import Dict, List, Optional, Sequence, Set, Tuple
 
 from .ir import LayerProgram
-from .strategy import Block, Strategy, split_budget
+from .strategy import CARRIED, CARRY_SUFFIX, Block, Strategy, split_budget
 
 
 class RaceError(AssertionError):
@@ -77,6 +77,7 @@ def launches_of(program: LayerProgram, blocks: Sequence[Block], compute_streams:
     listed = {split_budget(e)[0] for b in blocks for e in b.all_entries()}
     deferred = {markers[m] for m in listed if m in markers}
     pending: Dict[str, str] = {}
+    carried: List[tuple] = []
     out: List[Launch] = []
     stream_of: Dict[str, str] = {}
 
@@ -98,6 +99,11 @@ def launches_of(program: LayerProgram, blocks: Sequence[Block], compute_streams:
         for lane, lst in order:
             for e in lst:
                 name = split_budget(e)[0]
+                if name == CARRIED:
+                    continue                      # ops of the previous layer run: checked where that run hands them over
+                if name.endswith(CARRY_SUFFIX) and name[:-len(CARRY_SUFFIX)] in markers.values():
+                    carried.append((name[:-len(CARRY_SUFFIX)], lane))
+                    continue
                 if name in markers:
                     if markers[name] in pending:
                         pending.pop(markers[name])
@@ -109,6 +115,8 @@ def launches_of(program: LayerProgram, blocks: Sequence[Block], compute_streams:
                 emit(name, lane)
     for name in list(pending):
         emit(name, "S2")
+    for name, lane in carried:                    # the next layer run (or the flush) launches them after everything here
+        emit(name, lane)
     return out
 
 

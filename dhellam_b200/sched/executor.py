@@ -18,7 +18,7 @@ from typing import Dict, List, Optional
 import torch
 
 from .ir import BWD, COMM, FWD, LayerProgram, LayerRun
-from .strategy import Block, Strategy, split_budget
+from .strategy import CARRIED, CARRY_SUFFIX, Block, Strategy, split_budget
 
 
 class StreamSet:
@@ -77,12 +77,15 @@ class Executor:
         self._events: Dict[str, object] = {}
         self._lane_of: Dict[str, Dict[str, str]] = {}
         self._markers = program.marker_targets()
+        self._carry_names = {f"{n}{CARRY_SUFFIX}": n for n in self._markers.values()}
+        self._carry: List[tuple] = []            # weight-gradient ops handed to the next layer run
         for key, blocks in (("pair", self.strategy.dcblocks), ("fwd", self.strategy.fwd_only), ("bwd", self.strategy.bwd_only)):
             lanes = {}
             for blk in blocks:
                 for lane, lst in (("S3", blk.s3), ("S1", blk.s1), ("S2", blk.s2)):
                     for e in lst:
-                        lanes[split_budget(e)[0]] = lane
+                        n = split_budget(e)[0]
+                        lanes[self._carry_names.get(n, n)] = lane
             self._lane_of[key] = lanes
 
     # ------------------------------------------------------------------ public
@@ -100,8 +103,19 @@ class Executor:
         pending: Dict[str, tuple] = {}
         runs = {FWD: fwd_run, BWD: bwd_run}
 
+        has_slot = any(split_budget(e)[0] == CARRIED for blk in blocks for e in blk.s1 + blk.s2)
+        if self._carry and not has_slot:
+            self.flush_carry()
+
         def launch(entry: str, lane: str):
             name, budget = split_budget(entry)
+            if name == CARRIED:                             # slot for what the previous layer run handed over
+                self.flush_carry(lane)
+                return
+            if name in self._carry_names:                   # hand this op to the next layer run
+                op = self.program.op(self._carry_names[name])
+                self._carry.append((op, runs[op.strand], lane, dict(lanes), budget, self._snapshot(op, lane)))
+                return
             if name in self._markers:                       # placement marker of a deferred wgrad
                 target = self._markers[name]
                 if target in pending:
@@ -127,13 +141,38 @@ class Executor:
         for target, (op, run, b) in list(pending.items()):   # flush what no marker claimed
             self._exec(op, run, "S2", lanes, b)
 
+    def flush_carry(self, lane: Optional[str] = None):
+        """Runs the ops that earlier layer runs handed over (on ``lane``, else on the lane they
+        were scheduled on).  The engine calls it where their results are needed: before a
+        layer's gradients are reduced and at the end of the step."""
+        carried, self._carry = self._carry, []
+        for op, run, own_lane, lanes, budget, waits in carried:
+            self._exec(op, run, lane or own_lane, lanes, budget, waits)
+
     # ------------------------------------------------------------------ internals
-    def _exec(self, op, run: LayerRun, lane: str, lanes: Dict[str, str], budget: int):
+    def _snapshot(self, op, lane: str):
+        """Fresh events for the producers of ``op`` that ran on other streams: the per-op
+        events are re-recorded by the next layer run, which a carried op must not wait for."""
+        st = self.streams
+        if not st.cuda:
+            return []
+        stream = st.lane(lane)
+        waits = []
+        for s in {rec[1] for d in op.deps if (rec := self._events.get(d)) is not None and rec[1] is not stream}:
+            ev = torch.cuda.Event()
+            ev.record(s)
+            waits.append(ev)
+        return waits
+
+    def _exec(self, op, run: LayerRun, lane: str, lanes: Dict[str, str], budget: int, waits=None):
         st = self.streams
         stream = st.lane(lane)
         if self.trace is not None:
             self.trace.append((op.name, lane, run.layer_index, getattr(run.mb, "index", -1)))
-        if st.cuda:
+        if st.cuda and waits is not None:
+            for ev in waits:
+                stream.wait_event(ev)
+        elif st.cuda:
             for d in op.deps:
                 rec = self._events.get(d)
                 if rec is not None and rec[1] is not stream:   # produced on another stream

@@ -13,6 +13,12 @@ names, one name, or the string ``"None"``.  One extension: a name may carry an S
 as ``"name@96"`` (number of persistent CTAs for that op), which is how co-running two
 compute kernels is expressed here instead of TPC masks.
 
+Two more extensions move a weight-gradient GEMM (which nothing downstream waits for) across
+the layer boundary, where both strands otherwise wait for a collective at the same time:
+``"<wgrad op>_next"`` in place of the op hands it to the next layer run, and ``"carried"``
+marks where that next run executes what it was handed.  The reference's ``*_n`` markers
+(dhellam/core/dstb.py:1043-1059) defer a weight gradient only within its own layer.
+
 Fused names that the search writes, e.g. ``gemm_wgrad_mlp_c_reduce_scatter_mlp_c_bwd``,
 are split into the compute op (``S2``) and the collective (``S3``) as in
 search/search.py:189-228.
@@ -24,6 +30,9 @@ from dataclasses import dataclass, field
 from typing import Dict, Iterable, List, Optional, Tuple
 
 from .ir import BWD, COMM, COMPUTE, FWD, LayerProgram
+
+CARRY_SUFFIX = "_next"      # "<op>_next": run <op> in the next layer run
+CARRIED = "carried"         # slot where a layer run executes the ops handed over by the previous one
 
 FUSED_SPLIT = {
     "gemm_wgrad_mlp_c_reduce_scatter_mlp_c_bwd": ("gemm_wgrad_mlp_c", "reduce_scatter_mlp_c_bwd"),
@@ -163,7 +172,9 @@ def _dense_tp_paired(program: LayerProgram) -> Optional[List[Block]]:
     and that lasts longer than the transfer at the headline shapes: the big GEMM groups of
     the other strand, or a weight-gradient GEMM, which nothing downstream waits for.  The
     row-parallel MLP weight gradient is deferred (``gemm_wgrad_mlp_l_n``) to sit beside the
-    last reduce-scatter together with the QKV weight gradient.  The reference's built-in
+    last reduce-scatter, and the QKV weight gradient is handed to the next layer run, where it
+    covers the first all-gather of the forward strand (both strands start a layer with a
+    collective, so nothing of the new layer can).  The reference's built-in
     schedule (dhellam/core/dstb.py:1043-1059) follows the same idea with fewer fillers."""
     act_f = "swiglu_mlp" if program.has("swiglu_mlp") else "gelu_mlp"
     act_b = "swiglu_bwd" if program.has("swiglu_bwd") else "gelu_bwd"
@@ -173,7 +184,7 @@ def _dense_tp_paired(program: LayerProgram) -> Optional[List[Block]]:
         return None
     return [
         Block(s1=["ln_attn"]),
-        Block(s2=["bda_mlp_bwd"], s3=["allgather_attn"]),
+        Block(s2=["bda_mlp_bwd", CARRIED], s3=["allgather_attn"]),
         Block(s1=["gemm_attn_c", "fl_attn", "gemm_attn_l"], s3=["allgather_mlp_bwd"]),
         Block(s2=["gemm_dgrad_mlp_l", "gemm_wgrad_mlp_l", act_b, "gemm_dgrad_mlp_c"], s3=["reduce_scatter_attn"]),
         Block(s1=["bda_attn", "ln_mlp"], s3=["reduce_scatter_mlp_c_bwd"]),
@@ -181,7 +192,7 @@ def _dense_tp_paired(program: LayerProgram) -> Optional[List[Block]]:
         Block(s2=["ln_mlp_bwd", "bda_attn_bwd"]),
         Block(s1=["gemm_mlp_c", act_f, "gemm_mlp_l"], s3=["allgather_attn_bwd"]),
         Block(s2=["gemm_dgrad_attn_l", "gemm_wgrad_attn_l", "attn_bwd", "gemm_dgrad_attn_c"], s3=["reduce_scatter_mlp"]),
-        Block(s1=["bda_mlp"], s2=["gemm_wgrad_attn_c", "gemm_wgrad_mlp_l_n"], s3=["reduce_scatter_attn_c_bwd"]),
+        Block(s1=["bda_mlp"], s2=["gemm_wgrad_mlp_l_n", "gemm_wgrad_attn_c" + CARRY_SUFFIX], s3=["reduce_scatter_attn_c_bwd"]),
         Block(s2=["ln_attn_bwd"]),
     ]
 
@@ -230,6 +241,12 @@ def validate_blocks(blocks: List[Block], program: LayerProgram, need_fwd: bool, 
         for lst, lane in ((blk.s3, "S3"), (blk.s1, "S1"), (blk.s2, "S2")):
             for entry in lst:
                 name, _ = split_budget(entry)
+                if name == CARRIED:
+                    if lane == "S3":
+                        raise StrategyError(f"the slot for carried ops cannot be a collective (block {bi})")
+                    continue
+                if name.endswith(CARRY_SUFFIX) and name[:-len(CARRY_SUFFIX)] in markers.values():
+                    name = name[:-len(CARRY_SUFFIX)]          # scheduled here, executed by the next layer run
                 if name in markers:
                     if lane == "S3":
                         raise StrategyError(f"marker {name} cannot be a collective (block {bi})")

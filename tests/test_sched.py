@@ -66,6 +66,42 @@ def test_deferred_wgrad_marker_moves_the_op():
     check_schedule(prog, s)
 
 
+def test_wgrad_handed_to_the_next_layer_run_executes_there_and_is_flushed_at_the_end():
+    """``<op>_next`` hands a weight-gradient op to the next layer run, ``carried`` is where that
+    run executes it; the last layer's hand-over runs when the engine flushes."""
+    import torch
+    from dhellam_b200.config import ParallelConfig, TrainConfig
+    from dhellam_b200.data import make_microbatch, synthetic_tokens
+    from dhellam_b200.parallel import state as PS
+    from dhellam_b200.trainer import Trainer
+    cfg = preset("tiny-llama")
+    d = json.loads(json.dumps(REFERENCE_DEFAULT))
+    d["DCBlocks"][1] = ["None", ["bda_mlp_bwd", "carried"], ["allgather_attn"]]
+    d["DCBlocks"][15] = ["None", ["gemm_wgrad_attn_c_next"], ["reduce_scatter_attn_c_bwd"]]
+    strat = Strategy.from_dict(d)
+    strat.validate(_program())
+    check_schedule(_program(), strat)
+    trace = []
+    train = TrainConfig(micro_batch_size=1, global_batch_size=3, dtype="fp32")
+    tr = Trainer(cfg, ParallelConfig(), train, device=torch.device("cpu"), ps=PS.initialize_model_parallel(ParallelConfig()),
+                 strategy=strat, trace=trace)
+    mbs = [make_microbatch(cfg, tr.ps, synthetic_tokens(cfg, 1, 3 + i), i, 3 + i, tr.device) for i in range(3)]
+    tr.optimizer.zero_grad()
+    tr.engine.run_step(mbs)
+    wg = [i for i, t in enumerate(trace) if t[0] == "gemm_wgrad_attn_c"]
+    # one weight gradient per (micro-batch, layer), none lost
+    assert len(wg) == 3 * cfg.num_layers
+    # in a paired run the op of layer L, micro-batch b shows up after the NEXT run's bda_mlp_bwd
+    paired = [i for i in wg if i + 1 < len(trace) and trace[i - 1][0] == "bda_mlp_bwd" and trace[i - 1][2:] != trace[i][2:]]
+    assert paired, "no weight gradient was executed inside the following layer run"
+    # same gradients as the built-in schedule
+    ref = Trainer(cfg, ParallelConfig(), train, device=torch.device("cpu"), ps=tr.ps, strategy=Strategy.from_dict(REFERENCE_DEFAULT))
+    ref.model.flat_param.data.copy_(tr.model.flat_param.data)
+    ref.optimizer.zero_grad()
+    ref.engine.run_step(mbs)
+    assert torch.allclose(ref.model.flat_grad, tr.model.flat_grad, rtol=1e-5, atol=1e-6)
+
+
 @pytest.mark.parametrize("bad", ["dup", "missing", "order", "lane"])
 def test_invalid_strategies_are_rejected(bad):
     prog = _program()
