@@ -30,6 +30,8 @@
 #include <float.h>
 #include <stdint.h>
 
+#include <cstdlib>
+
 #include "api.h"
 #include "ptx.cuh"
 #include "tmap.h"
@@ -817,6 +819,12 @@ int dh_attn_fwd(const void* q, const void* k, const void* v, void* out, void* ls
 // KV blocks x batch x KV heads already give every SM a few CTAs, else the smallest power of
 // two (dividing the group size) that does.
 static int bwd_head_split(int B, int Hq, int Hk, int Sk) {
+  static int enabled = -1;
+  if (enabled < 0) {
+    const char* e = getenv("DHELLAM_ATTN_HEAD_SPLIT");
+    enabled = e ? atoi(e) : 1;
+  }
+  if (!enabled) return 1;
   const int group = Hq / Hk;
   const long long ctas = (long long)((Sk + BKV - 1) / BKV) * B * Hk;
   int hs = 1;

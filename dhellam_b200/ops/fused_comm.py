@@ -26,6 +26,7 @@ push stores to every peer in turn.  Peer pointers come from
 """
 from __future__ import annotations
 
+import collections
 import ctypes
 import os
 from ctypes import c_int, c_int64, c_uint, c_void_p
@@ -215,10 +216,10 @@ class FusedTP:
                 "dh_ag_push")
         ev = torch.cuda.Event()
         ev.record(s)
-        self._pending[tag] = (slot, self.total_ag[tag][slot], M, Kd, ev)
+        self._pending.setdefault(tag, collections.deque()).append((slot, self.total_ag[tag][slot], M, Kd, ev))
 
     def gather_wait(self, tag: str):
-        slot, target, M, Kd, ev = self._pending.pop(tag)
+        slot, target, M, Kd, ev = self._pending[tag].popleft()     # oldest first: a weight gradient may trail by one layer
         s = torch.cuda.current_stream(self.device)
         s.wait_event(ev)
         fn = K.proto("dh_wait_counters", [c_void_p, c_int, c_uint, c_void_p])

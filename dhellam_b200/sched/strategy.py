@@ -26,6 +26,7 @@ search/search.py:189-228.
 from __future__ import annotations
 
 import json
+import os
 from dataclasses import dataclass, field
 from typing import Dict, Iterable, List, Optional, Tuple
 
@@ -182,6 +183,10 @@ def _dense_tp_paired(program: LayerProgram) -> Optional[List[Block]]:
               "allgather_mlp", "gemm_mlp_c", act_f, "gemm_mlp_l", "reduce_scatter_mlp", "bda_mlp", "attn_bwd", act_b]
     if not all(program.has(n) for n in needed) or len(program.fwd) != 14 or len(program.bwd) != 18:
         return None
+    if os.environ.get("DHELLAM_CARRY_WGRAD", "1") != "0":
+        last_fillers = ["gemm_wgrad_mlp_l_n", "gemm_wgrad_attn_c" + CARRY_SUFFIX]
+    else:                                     # everything stays inside its own layer run
+        last_fillers = ["gemm_wgrad_attn_c", "gemm_wgrad_mlp_l_n"]
     return [
         Block(s1=["ln_attn"]),
         Block(s2=["bda_mlp_bwd", CARRIED], s3=["allgather_attn"]),
@@ -192,7 +197,7 @@ def _dense_tp_paired(program: LayerProgram) -> Optional[List[Block]]:
         Block(s2=["ln_mlp_bwd", "bda_attn_bwd"]),
         Block(s1=["gemm_mlp_c", act_f, "gemm_mlp_l"], s3=["allgather_attn_bwd"]),
         Block(s2=["gemm_dgrad_attn_l", "gemm_wgrad_attn_l", "attn_bwd", "gemm_dgrad_attn_c"], s3=["reduce_scatter_mlp"]),
-        Block(s1=["bda_mlp"], s2=["gemm_wgrad_mlp_l_n", "gemm_wgrad_attn_c" + CARRY_SUFFIX], s3=["reduce_scatter_attn_c_bwd"]),
+        Block(s1=["bda_mlp"], s2=last_fillers, s3=["reduce_scatter_attn_c_bwd"]),
         Block(s2=["ln_attn_bwd"]),
     ]
 
