@@ -1,0 +1,10 @@
+"""Process-wide blackboard with the reference's name (dhellam/common/global_variables.py:1-2).
+
+The reference passes the step's inputs, the loss and the optimizer's loss-scale function
+between its patched Megatron loop and the folded model through this dict
+(megatron.patch:764-770, 786-803; dhellam/core/dsllm.py:86-106).  The engine here passes
+them as arguments (``DoubleStrandEngine.run_step``, ``Env``); the dict is kept so that code
+written against the reference finds the same keys, and ``Trainer`` mirrors the values
+that outside code used to read: ``loss`` after every step and ``loss_scale_func``.
+"""
+GLOBAL_VARIABLES = {"inputs": None, "loss": None, "loss_scale_func": None}

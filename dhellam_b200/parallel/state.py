@@ -36,6 +36,8 @@ class ParallelState:
     dp_group: object = None
     pp_group: object = None
     ep_group: object = None
+    edp_group: object = None       # ranks that hold the same experts (across EP blocks and CP ranks)
+    edp_ranks: List[int] = field(default_factory=lambda: [0])
     dp_cp_group: object = None            # gradient reduction group (DP x CP)
     tp_ranks: List[int] = field(default_factory=lambda: [0])
     cp_ranks: List[int] = field(default_factory=lambda: [0])
@@ -139,6 +141,9 @@ def initialize_model_parallel(cfg: ParallelConfig, backend: Optional[str] = None
                     ep_groups.append([rank_of(t, c, blk * cfg.ep + e, p, cfg) for e in range(cfg.ep)])
     make(ep_groups, "ep_group", "ep_ranks")
     st.ep_rank = dp % cfg.ep
+    # expert-data-parallel: the replicas of one expert shard, whose gradients are summed
+    make([[rank_of(t, c, blk * cfg.ep + e, p, cfg) for blk in range(cfg.dp // cfg.ep) for c in range(cfg.cp)]
+          for p in range(cfg.pp) for t in range(cfg.tp) for e in range(cfg.ep)], "edp_group", "edp_ranks")
     _STATE = st
     return st
 

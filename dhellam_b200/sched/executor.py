@@ -13,6 +13,7 @@ device; on CPU tensors the same code runs synchronously without streams.
 from __future__ import annotations
 
 import contextlib
+import os
 from typing import Dict, List, Optional
 
 import torch
@@ -73,6 +74,9 @@ class Executor:
         self.streams = streams
         self.profile = profile
         self.trace = trace                       # optional list collecting (name, lane) launch records
+        # NVTX range per op ("F:" forward strand, "B:" backward strand, layer and micro-batch in the
+        # name) for timelines taken with an external tool; the reference has no ranges at all.
+        self.nvtx = streams.cuda and os.environ.get("DHELLAM_NVTX", "0") == "1"
         self.timings: Dict[str, List] = {}
         self._events: Dict[str, object] = {}
         self._lane_of: Dict[str, Dict[str, str]] = {}
@@ -180,6 +184,8 @@ class Executor:
         if budget:
             run.sm_budget[op.name] = budget
         run.env.cur_stream = stream
+        if self.nvtx:
+            torch.cuda.nvtx.range_push(f"{'F' if op.strand == FWD else 'B'}:{op.name} L{run.layer_index} mb{getattr(run.mb, 'index', -1)}")
         with st.ctx(stream):
             if self.profile and st.cuda:
                 e0 = torch.cuda.Event(enable_timing=True)
@@ -190,6 +196,8 @@ class Executor:
                 self.timings.setdefault(op.name, []).append((e0, e1))
             else:
                 op.fn(run)
+        if self.nvtx:
+            torch.cuda.nvtx.range_pop()
         if st.cuda:
             rec = self._events.get(op.name)
             ev = rec[0] if rec is not None else torch.cuda.Event()

@@ -14,6 +14,7 @@ from typing import List, Optional
 import torch
 import torch.distributed as dist
 
+from .common.global_variables import GLOBAL_VARIABLES
 from .config import ModelConfig, ParallelConfig, TrainConfig
 from .core.engine import DoubleStrandEngine, Env, MicroBatch
 from .core.modules import DSLLM
@@ -53,6 +54,7 @@ class Trainer:
             reducer = OverlappedGradReducer(self.model, self.ps, self.engine.streams)
             self.engine.grad_reducer = reducer
             self.optimizer.grad_reducer = reducer
+        GLOBAL_VARIABLES["loss_scale_func"] = self.optimizer.scale_loss
         self.iteration = 0
         self.last_grad_norm = None
 
@@ -68,6 +70,7 @@ class Trainer:
             if self.ps.dp > 1:
                 dist.all_reduce(loss, group=self.ps.dp_group)
                 loss = loss / self.ps.dp
+            GLOBAL_VARIABLES["loss"] = loss
             return loss
         return None
 

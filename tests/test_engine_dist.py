@@ -73,6 +73,8 @@ CASES = [
     ("tiny-llama", 4, dict(tp=2, pp=2), 3, 1, 32, {"num_layers": 4}),
     ("tiny-llama", 4, dict(cp=4), 2, 1, 64, {}),
     ("tiny-gpt", 4, dict(pp=2, cp=2), 3, 1, 32, {"num_layers": 4}),
+    ("tiny-moe", 4, dict(dp=4, ep=2), 2, 1, 32, {"moe_aux_loss_coeff": 0.0}),    # two replicas of every expert shard
+    ("tiny-moe", 4, dict(dp=2, ep=2, cp=2), 2, 1, 32, {"moe_aux_loss_coeff": 0.0}),   # experts replicated over CP ranks
 ]
 
 

@@ -40,7 +40,7 @@ def main(argv=None):
     from dhellam_b200.adaptor import initialize_dhellam_megatron
     from dhellam_b200.ckpt import load_checkpoint, save_checkpoint
     from dhellam_b200.common import print_rank0
-    from dhellam_b200.data import synthetic_step_batches
+    from dhellam_b200.data import TokenFileDataset, file_step_batches, synthetic_step_batches
     from dhellam_b200.runtime.metrics import MetricsLogger
     from dhellam_b200.trainer import Trainer
 
@@ -63,8 +63,15 @@ def main(argv=None):
     print_rank0(f"model {cfg.total_params() / 1e9:.2f} B parameters, parallelism {pcfg.describe()}, "
                 f"{train.num_microbatches(pcfg.dp)} micro-batches of {train.micro_batch_size} per step, "
                 f"dual-strand {'on' if train.dhellam else 'off'}, fused comm {'on' if tr.env.fused_tp else 'off'}")
+    dataset = None
+    if args.data_path and not args.mock_data:
+        # a flat token file (the payload of a Megatron .bin file); "<path>:<dtype>" selects the id type
+        path, _, dt = args.data_path[-1].partition(":")
+        dataset = TokenFileDataset(path, cfg.seq_length, dt or "int32", seed=train.seed)
+        print_rank0(f"data: {path} ({len(dataset)} samples of {cfg.seq_length + 1} tokens)")
     for it in range(start, train.train_iters):
-        mbs = synthetic_step_batches(cfg, train, tr.ps, it, device)
+        mbs = (file_step_batches(dataset, cfg, train, tr.ps, it, device) if dataset is not None
+               else synthetic_step_batches(cfg, train, tr.ps, it, device))
         if cuda:
             torch.cuda.synchronize()
         t0 = time.perf_counter()
