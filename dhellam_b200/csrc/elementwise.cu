@@ -137,6 +137,11 @@ __global__ void __launch_bounds__(NT) norm_fwd_kernel(const __nv_bfloat16* __res
   }
 }
 
+// 16-byte aligned fp32 x4 reduction into global memory (no return value).
+__device__ __forceinline__ void red_add_v4(float* p, float a, float b, float c, float d) {
+  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
+
 template <int MODE, int VPT>
 __global__ void __launch_bounds__(NT) norm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
                                                       const __nv_bfloat16* __restrict__ w, const float* __restrict__ mu_in,
@@ -203,14 +208,27 @@ __global__ void __launch_bounds__(NT) norm_bwd_kernel(const __nv_bfloat16* __res
       }
     }
   }
+  // gradient buffers are views into one flat buffer: 16-byte alignment is usual, not guaranteed
+  const bool vec_ok = ((reinterpret_cast<uintptr_t>(dw) | (MODE == 1 && db != nullptr ? reinterpret_cast<uintptr_t>(db) : 0)) & 15) == 0;
 #pragma unroll
   for (int i = 0; i < VPT; ++i) {
     const int c = threadIdx.x + i * NT;
     if (c < nvec) {
+      // every CTA adds its partial sums to the same h addresses: the 4-wide reduction
+      // quarters the number of L2 atomic operations
+      if (vec_ok) {
+        red_add_v4(dw + c * 8, accw[i][0], accw[i][1], accw[i][2], accw[i][3]);
+        red_add_v4(dw + c * 8 + 4, accw[i][4], accw[i][5], accw[i][6], accw[i][7]);
+        if (MODE == 1 && db != nullptr) {
+          red_add_v4(db + c * 8, accb[i][0], accb[i][1], accb[i][2], accb[i][3]);
+          red_add_v4(db + c * 8 + 4, accb[i][4], accb[i][5], accb[i][6], accb[i][7]);
+        }
+      } else {
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        atomicAdd(dw + c * 8 + j, accw[i][j]);
-        if (MODE == 1 && db != nullptr) atomicAdd(db + c * 8 + j, accb[i][j]);
+        for (int j = 0; j < 8; ++j) {
+          atomicAdd(dw + c * 8 + j, accw[i][j]);
+          if (MODE == 1 && db != nullptr) atomicAdd(db + c * 8 + j, accb[i][j]);
+        }
       }
     }
   }

@@ -51,8 +51,10 @@ def test_noalloc_attention_backward_matches_regular_entry_point_twice():
     torch.manual_seed(7)
     d = 128
     scale = 1.0 / math.sqrt(d)
-    # two different problems back to back: the second must not see the first one's leftovers
-    for (Sq, B, Hq, Hk, causal) in ((384, 2, 4, 2, True), (256, 1, 2, 1, False)):
+    # different problems back to back: none must see its predecessor's leftovers
+    # the third problem fills the built-in scratch exactly (4 x 16 x 4096 rows) and makes the regular
+    # entry point split the 16 query heads of its one KV head over 8 CTAs, two heads each
+    for (Sq, B, Hq, Hk, causal) in ((384, 2, 4, 2, True), (256, 1, 2, 1, False), (4096, 4, 16, 1, True)):
         qkv = torch.randn(Sq, B, Hq + 2 * Hk, d, device="cuda").to(torch.bfloat16)
         q, k, v = qkv[:, :, :Hq], qkv[:, :, Hq:Hq + Hk], qkv[:, :, Hq + Hk:]
         out, lse = attn_fwd(q, k, v, causal, scale)
