@@ -16,7 +16,9 @@
 //     warps form P = exp2(S - lse) and dS = P (dP - delta) into swizzled shared-memory images
 //     that are consumed as MN-major operands (dV += P^T dO, dK += dS^T Q), so no transposed
 //     copies exist anywhere; dK / dV accumulate in TMEM over the whole loop, which also sums
-//     the query heads of a KV group.
+//     the query heads of a KV group.  When keys x batch x KV heads gives too few CTAs for the
+//     machine (one KV head per GPU under tensor parallelism), the query heads of a group are
+//     split over up to 8 CTAs that write fp32 partials, and attn_dkv_reduce_kernel adds them.
 //   dQ: one CTA per (128 queries, batch, query head) loops over the key blocks, recomputes S
 //     and dP and accumulates dQ += dS K in TMEM.  Recomputing two products per tile pair
 //     replaces an fp32 atomic accumulation of dQ, which was bound by L2 atomic throughput.

@@ -1,28 +1,37 @@
-// Tensor-parallel collectives fused into the tcgen05 GEMM, over NVLink peer memory.
+// Tensor-parallel collectives over NVLink / NVSwitch peer memory: inside the tcgen05 GEMM kernels
+// and as stand-alone kernels that share SMs with a GEMM running on another stream.
 //
 //  ag_gemm : sequence all-gather -> GEMM            (QKV / FC1 forward, proj / FC2 dgrad)
-//    A few "copy" CTAs of the same grid push this rank's row shard into every peer's
-//    symmetric staging buffer with plain 16-byte peer stores (data is read once from HBM and
-//    stored to all peers from registers) and bump a per-row-block counter on the receiver
-//    with a system-scope release.  The GEMM CTAs walk the row blocks starting with the local
-//    shard; the TMA producer of a tile waits (bounded) on the counter of its row block and
-//    then loads A from LOCAL memory only.  The copy CTAs also copy every arrived block to a
-//    regular tensor that the caller keeps for the weight-gradient GEMM.
+//    A few "copy" CTAs of the same grid push this rank's row shard into every rank's symmetric
+//    staging buffer (one multimem.st per 16 bytes reaches all GPUs through the switch; per-peer
+//    stores without the multicast alias; data is read once from HBM) and bump a per-row-block
+//    counter on every receiver with a system-scope release.  The GEMM CTAs walk the row blocks
+//    starting with the local shard; the TMA producer of a tile waits (bounded) on the counter of
+//    its row block and then loads A from LOCAL memory only.  The gathered operand stays in the
+//    staging buffer for the weight-gradient GEMM of the same layer.
 //
 //  gemm_rs : GEMM -> sequence reduce-scatter        (proj / FC2 forward, QKV / FC1 dgrad)
-//    The epilogue stores each partial tile straight into the row OWNER's symmetric buffer
-//    (slot = source rank) and bumps a per-source arrival counter there; row blocks of remote
-//    owners are computed first, the local ones last.  After its last tile every CTA waits
-//    (bounded) for all sources and the whole grid reduces the owner's slots in fp32 to the
-//    bf16 shard.
+//    The epilogue stages each partial tile through shared memory and stores it, 256 bytes per
+//    row segment, straight into the row OWNER's symmetric buffer (slot = source rank), then bumps
+//    a per-source arrival counter there; row blocks of remote owners are computed first, the
+//    local ones last.  After its last tile every CTA waits (bounded) for all sources and the
+//    whole grid reduces the owner's slots in fp32 to the bf16 shard.
 //
-// Both kernels use double-buffered symmetric buffers with monotonically increasing counter
-// targets (no resets, no host barriers).  The host runs fused kernels one at a time and in
-// the same order on every rank, which makes the double buffering sufficient: a rank can
-// only finish call c after every peer has started call c, i.e. finished call c-1.
+//  ag_push / wait_counters : the all-gather alone (push on the communication stream, counter
+//    wait in front of the consumer), used where the schedule hides the transfer behind the other
+//    strand's kernels and to re-gather a saved shard for a weight gradient.
 //
-// No load in this file is a multi-CTA broadcast; peer memory is only ever the target of
-// plain stores / reductions or the source of plain loads.
+//  rs_reduce : the reduce-scatter alone over partial products that a plain local GEMM wrote
+//    into symmetric memory: announcement flags, then multimem.ld_reduce (the switch adds the
+//    copies in fp32) or peer loads.
+//
+// All buffers are double-buffered per call site with monotonically increasing counter targets
+// (no resets, no host barriers).  Kernels that wait for peers inside the kernel are launched one
+// at a time and in the same order on every rank, which makes the double buffering sufficient: a
+// rank can only finish call c after every peer has started call c, i.e. finished call c-1.
+//
+// No load in this file is a multi-CTA broadcast; peer memory is only ever the target of plain or
+// multimem stores / reductions or the source of plain or multimem loads.
 //
 // Role in the reference: all_gather_into_tensor / reduce_scatter_tensor around torch.matmul
 // (dhellam/operators/comm.py:13-58, dhellam/core/dstb.py:407-425) and the host-level

@@ -10,9 +10,15 @@ of ``csrc/comm_fused.cu``:
 * ``gemm_rs(a, w)`` = ``reduce_scatter(a @ op(w))``, replacing ``gemm_* + reduce_scatter``
   (dstb.py:407-410);
 * ``gather_start(shard, tag)`` / ``gather_wait(tag)``: the all-gather alone, pushed from a
-  few CTAs on the communication stream while other kernels run; used to re-gather the
-  sequence-parallel input of a column-parallel layer for its weight gradient instead of
-  keeping the gathered activation alive from the forward pass.
+  few CTAs on the communication stream while other kernels run; used by the split policy
+  (below) and to re-gather the sequence-parallel input of a column-parallel layer for its
+  weight gradient instead of keeping the gathered activation alive from the forward pass;
+* ``partial_buffer(tag, M, N)`` / ``rs_reduce(tag)``: the reduce-scatter alone: a plain local
+  GEMM writes its partial product into symmetric memory, then a small kernel on the
+  communication stream exchanges completion flags and reduces this rank's rows inside the
+  NVSwitch (``multimem.ld_reduce``) or with peer loads.
+
+``split(M, N, K)`` says per call site which form the layer ops use (``DHELLAM_FUSED_POLICY``).
 
 Every staging buffer is double-buffered per tag, with monotonically increasing arrival
 counters.  Kernels that wait for peers inside the kernel (``ag_gemm``, ``gemm_rs``) are
