@@ -36,8 +36,17 @@ class Trainer:
         fused = None
         if train.fused_comm and self.device.type == "cuda" and self.ps.tp > 1:
             from .ops.fused_comm import FusedTP
-            fused = FusedTP(self.ps, cfg, train, self.device)
-        elif self.device.type == "cuda" and self.ps.world > 1 and train.dhellam:
+            try:
+                fused = FusedTP(self.ps, cfg, train, self.device)
+            except Exception as e:       # no symmetric memory / no peer access on this machine
+                print(f"[dhellam_b200] in-kernel collectives unavailable on rank {self.ps.rank} ({type(e).__name__}: {e}); "
+                      "using NCCL collectives", flush=True)
+            # all ranks of the group take the same path
+            ok = torch.tensor([1 if fused is not None else 0], device=self.device)
+            dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=self.ps.tp_group)
+            if int(ok) == 0:
+                fused = None
+        if fused is None and self.device.type == "cuda" and self.ps.world > 1 and train.dhellam:
             # Library collectives co-run with the GEMMs and occupy one SM of many SM pairs;
             # a CTA-pair GEMM then cannot place its clusters (measured 1.6x slower step),
             # so that path keeps the single-CTA tiles.
