@@ -104,9 +104,9 @@ def reference_arm():
     # The reference cannot be installed here: its two submodules (Megatron-LM, flash-attention) are empty
     # directories in the source tree, TransformerEngine 1.4 / apex / megatron are not in the offline wheelhouse,
     # and its attention wrapper rejects sm_100.
-    print(json.dumps({"impl": "reference", "unavailable": "reference needs Megatron-LM core 0.5 + TransformerEngine 1.4 + its "
-                      "flash-attention submodule, all absent offline (empty 3rdparty/, not in wheelhouse); its attention "
-                      "wrapper also refuses sm_100"}))
+    print(json.dumps({"impl": "reference", "unavailable": "offline pip install of the reference fails in its setup.py (include_paths(cuda=True) is "
+                      "not accepted by PyTorch 2.11); it also needs Megatron-LM core 0.5, TransformerEngine 1.4 and its "
+                      "flash-attention submodule, all absent offline, and its attention wrapper refuses sm_100"}))
 
 
 def main():
