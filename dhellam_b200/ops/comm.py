@@ -97,3 +97,76 @@ def ring_exchange(send, recv, group, global_ranks, reverse: bool = False):
     if me % 2 == 1:
         ops.reverse()
     return ReqList(dist.batch_isend_irecv(ops))
+
+
+def get_distributed_world_size(group=None) -> int:
+    """Name kept from the reference (dhellam/operators/comm.py:7-11)."""
+    return group_size(group)
+
+
+# --------------------------------------------------------------------------- host-level chunked overlap
+# The reference carries two prototypes that overlap a TP collective with its GEMM from the
+# host, chunk by chunk (dhellam/operators/comm.py:89-143).  The kernels of
+# ``ops/fused_comm.py`` do the same thing inside one launch; these functions keep the
+# prototypes' contracts on any backend (they are also the only overlapped form on CPU ranks).
+def chunk_allgather_gemm(gemm_weight, comm_input, tp_size: int, tp_rank: int, tp_group, tp_ranks=None):
+    """``all_gather(comm_input) @ gemm_weight.T`` with the gather done as ``tp_size - 1`` ring
+    steps; the GEMM on the shard that has already arrived runs while the next shard is in
+    flight.  ``comm_input [m, k]``, ``gemm_weight [n, k]``.  Returns ``(out [m * tp, n],
+    gathered [m * tp, k])``, rows in rank order."""
+    from .gemm import gemm_nt
+    if tp_size == 1:
+        return gemm_nt(comm_input, gemm_weight), comm_input
+    m = comm_input.shape[0]
+    ranks = tp_ranks if tp_ranks is not None else dist.get_process_group_ranks(tp_group)
+    gathered = torch.empty((m * tp_size,) + tuple(comm_input.shape[1:]), dtype=comm_input.dtype, device=comm_input.device)
+    out = torch.empty((m * tp_size, gemm_weight.shape[0]), dtype=comm_input.dtype, device=comm_input.device)
+    gathered[tp_rank * m:(tp_rank + 1) * m].copy_(comm_input)
+    have = tp_rank                                  # index of the shard this rank holds and forwards
+    for step in range(tp_size):
+        cur = gathered[have * m:(have + 1) * m]
+        reqs = None
+        if step + 1 < tp_size:
+            nxt = (have - 1) % tp_size              # the previous rank forwards the shard it held one step ago
+            reqs = ring_exchange(cur, gathered[nxt * m:(nxt + 1) * m], tp_group, ranks)
+        gemm_nt(cur, gemm_weight, out=out[have * m:(have + 1) * m])
+        if reqs is not None:
+            reqs.wait()
+            have = nxt
+    return out, gathered
+
+
+def chunk_gemm_reduce_scatter(gemm_input, gemm_weight, tp_size: int, tp_rank: int, tp_group, chunks: int = 4):
+    """``reduce_scatter(gemm_input @ gemm_weight.T)`` along the rows, computed in ``chunks``
+    blocks of output columns: the reduce-scatter of one block runs (asynchronously) while the
+    GEMM of the next block computes.  ``gemm_input [M, k]``, ``gemm_weight [n, k]``.  Returns
+    this rank's ``[M / tp, n]`` rows of the sum."""
+    from .gemm import gemm_nt
+    if tp_size == 1:
+        return gemm_nt(gemm_input, gemm_weight)
+    M, n = gemm_input.shape[0], gemm_weight.shape[0]
+    chunks = max(1, min(chunks, n // 8))
+    bounds = [(n * i // chunks) // 8 * 8 for i in range(chunks)] + [n]
+    parts, handles = [], ReqList()
+    for i in range(chunks):
+        lo, hi = bounds[i], bounds[i + 1]
+        if hi <= lo:
+            continue
+        partial = gemm_nt(gemm_input, gemm_weight[lo:hi])
+        shard = torch.empty((M // tp_size, hi - lo), dtype=partial.dtype, device=partial.device)
+        handles.append(dist.reduce_scatter_tensor(shard, partial, group=tp_group, async_op=True))
+        parts.append(shard)
+    handles.wait()
+    return torch.cat(parts, dim=1)
+
+
+def flash_attn_p2p_communicate(rank, send_tensor, send_dst, recv_tensor, recv_src, cp_group, batch_p2p_comm: bool = True):
+    """One ring-attention exchange with the reference's signature
+    (dhellam/operators/comm.py:144-205): even ranks post the send first, odd ranks the receive
+    first; returns the list of requests to wait on."""
+    ops = [dist.P2POp(dist.isend, send_tensor, send_dst, cp_group), dist.P2POp(dist.irecv, recv_tensor, recv_src, cp_group)]
+    if rank % 2 == 1:
+        ops.reverse()
+    if batch_p2p_comm:
+        return ReqList(dist.batch_isend_irecv(ops))
+    return ReqList([op.op(op.tensor, op.peer, group=op.group) for op in ops])

@@ -70,3 +70,27 @@ def test_blackboard_and_launch_templates():
     assert out == 5 and ms >= 0.0
     out, ev = launch_with_event(lambda a: a * 2, 4)
     assert out == 8 and (ev is None or hasattr(ev, "record"))
+
+
+def _chunk_worker(rank, world):
+    import torch.distributed as dist
+    from dhellam_b200.ops import comm as C
+    from dhellam_b200.parallel import state as PS
+    ps = PS.initialize_model_parallel(ParallelConfig(tp=world))
+    g = torch.Generator().manual_seed(5)
+    shards = [torch.randn(6, 16, generator=g) for _ in range(world)]
+    w = torch.randn(24, 16, generator=g)
+    out, full = C.chunk_allgather_gemm(w, shards[rank], world, rank, ps.tp_group, ps.tp_ranks)
+    ref_full = torch.cat(shards)
+    assert torch.equal(full, ref_full)
+    assert torch.allclose(out, ref_full @ w.t(), rtol=1e-5, atol=1e-5)
+    xs = [torch.randn(4 * world, 16, generator=g) for _ in range(world)]      # each rank's partial-product input
+    total = sum(x @ w.t() for x in xs)
+    got = C.chunk_gemm_reduce_scatter(xs[rank], w, world, rank, ps.tp_group, chunks=3)
+    assert torch.allclose(got, total[rank * 4:(rank + 1) * 4], rtol=1e-5, atol=1e-5)
+    assert C.get_distributed_world_size(ps.tp_group) == world
+
+
+def test_host_level_chunked_overlap_prototypes_match_plain_composition():
+    run_ranks(_chunk_worker, 2)
+    run_ranks(_chunk_worker, 4)
