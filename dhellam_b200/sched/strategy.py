@@ -122,7 +122,7 @@ class Strategy:
         """Fills missing parts with built-in schedules (the reference falls back the same
         way, dhellam/core/dstb.py:1042-1129; unlike the reference, a missing file is fine)."""
         return Strategy(self.dcblocks or default_paired(program), self.fwd_only or default_single(program, FWD),
-                        self.bwd_only or default_single(program, BWD))
+                        self.bwd_only or _dense_tp_bwd_only(program) or default_single(program, BWD))
 
     def validate(self, program: LayerProgram):
         """Checks every part that is present (absent parts are filled by ``completed``)."""
@@ -198,6 +198,32 @@ def _dense_tp_paired(program: LayerProgram) -> Optional[List[Block]]:
         Block(s1=["gemm_mlp_c", act_f, "gemm_mlp_l"], s3=["allgather_attn_bwd"]),
         Block(s2=["gemm_dgrad_attn_l", "gemm_wgrad_attn_l", "attn_bwd", "gemm_dgrad_attn_c"], s3=["reduce_scatter_mlp"]),
         Block(s1=["bda_mlp"], s2=last_fillers, s3=["reduce_scatter_attn_c_bwd"]),
+        Block(s2=["ln_attn_bwd"]),
+    ]
+
+
+def _dense_tp_bwd_only(program: LayerProgram) -> Optional[List[Block]]:
+    """Built-in backward-only schedule of the dense layer (cool-down rounds, where no forward
+    strand is left to cover the collectives): the weight-gradient GEMMs, which wait for no
+    collective, are placed beside the four collectives of the backward strand, and the QKV
+    weight gradient is handed to the next layer run to cover its first all-gather."""
+    act_b = "swiglu_bwd" if program.has("swiglu_bwd") else "gelu_bwd"
+    needed = ["bda_mlp_bwd", "allgather_mlp_bwd", "gemm_dgrad_mlp_l", "gemm_wgrad_mlp_l", act_b, "gemm_dgrad_mlp_c", "gemm_wgrad_mlp_c",
+              "reduce_scatter_mlp_c_bwd", "ln_mlp_bwd", "bda_attn_bwd", "allgather_attn_bwd", "gemm_dgrad_attn_l", "gemm_wgrad_attn_l",
+              "attn_bwd", "gemm_dgrad_attn_c", "gemm_wgrad_attn_c", "reduce_scatter_attn_c_bwd", "ln_attn_bwd"]
+    if not all(program.has(n) for n in needed) or len(program.bwd) != 18:
+        return None
+    carry = os.environ.get("DHELLAM_CARRY_WGRAD", "1") != "0"
+    return [
+        Block(s2=["bda_mlp_bwd"]),
+        Block(s2=[CARRIED], s3=["allgather_mlp_bwd"]),
+        Block(s2=["gemm_dgrad_mlp_l", "gemm_wgrad_mlp_l", act_b, "gemm_dgrad_mlp_c"]),       # wgrad_mlp_l waits for its marker
+        Block(s2=["gemm_wgrad_mlp_c"], s3=["reduce_scatter_mlp_c_bwd"]),
+        Block(s2=["ln_mlp_bwd", "bda_attn_bwd"]),
+        Block(s2=["gemm_wgrad_mlp_l_n"], s3=["allgather_attn_bwd"]),
+        Block(s2=["gemm_dgrad_attn_l", "gemm_wgrad_attn_l", "attn_bwd", "gemm_dgrad_attn_c"]),    # wgrad_attn_l waits for its marker
+        Block(s2=["gemm_wgrad_attn_l_n", "gemm_wgrad_attn_c" + CARRY_SUFFIX if carry else "gemm_wgrad_attn_c"],
+              s3=["reduce_scatter_attn_c_bwd"]),
         Block(s2=["ln_attn_bwd"]),
     ]
 
