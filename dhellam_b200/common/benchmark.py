@@ -93,3 +93,45 @@ def benchmark_ms_ops(repeat: int, s1, s2, ops1: Sequence[Callable], ops2: Sequen
                     op()
     streams = [s for s in (s1, s2, comm_stream) if s is not None] if cuda else []
     return device_time_ms(bundle, repeat=repeat, warmup=2, group=group, streams=streams)
+
+
+def benchmark_ms_ops_cp(repeat: int, s1, s2, ops1: Sequence[Callable], ops2: Sequence[Callable], comms: Sequence[Callable] = (),
+                        comm_stream=None, group=None, wait_fwd: bool = False, wait_bwd: bool = False) -> float:
+    """As ``benchmark_ms_ops`` with several collectives (the ring steps of context-parallel
+    attention): all of ``comms`` are launched first on ``comm_stream``; with ``wait_fwd`` /
+    ``wait_bwd`` the stream-1 / stream-2 list starts only after them (the consumer of a ring
+    step cannot start before its KV block arrived).  Reference: benchmark.py:82-149."""
+    cuda = torch.cuda.is_available()
+
+    def bundle():
+        for c in comms:
+            if cuda and comm_stream is not None:
+                with torch.cuda.stream(comm_stream):
+                    c()
+            else:
+                c()
+        done = None
+        if cuda and comm_stream is not None and comms and (wait_fwd or wait_bwd):
+            done = torch.cuda.Event()
+            done.record(comm_stream)
+        for lst, s, wait in ((ops1, s1, wait_fwd), (ops2, s2, wait_bwd)):
+            if cuda and s is not None and wait and done is not None:
+                s.wait_event(done)
+            for op in lst:
+                if cuda and s is not None:
+                    with torch.cuda.stream(s):
+                        op()
+                else:
+                    op()
+    streams = [s for s in (s1, s2, comm_stream) if s is not None] if cuda else []
+    return device_time_ms(bundle, repeat=repeat, warmup=2, group=group, streams=streams)
+
+
+def benchmark_dhellam(repeat: int, sequential: Callable[[], None], paired: Callable[[], None], group=None, streams: Sequence = ()):
+    """Times a sequential execution (forward-only then backward-only schedule) against the
+    paired schedule of the same work and returns ``(sequential_ms, paired_ms, speedup)``, the
+    three figures the reference's strategy validator prints (benchmark.py:151-195,
+    search/execute.py:107-113)."""
+    seq = device_time_ms(sequential, repeat=repeat, warmup=2, group=group, streams=streams)
+    par = device_time_ms(paired, repeat=repeat, warmup=2, group=group, streams=streams)
+    return seq, par, (seq / par if par > 0 else float("nan"))

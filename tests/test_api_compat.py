@@ -66,3 +66,18 @@ def test_adaptor_parses_megatron_flags_and_builds_configs():
     assert (cfg.num_layers, cfg.num_query_groups, cfg.activation, cfg.norm) == (4, 2, "swiglu", "rmsnorm")
     assert args.train_config.dtype == "bf16" and args.parallel_config.dp == 1
     PS.set_state(None)
+
+
+def test_benchmark_harness_has_the_reference_entry_points():
+    """benchmark, benchmark_ms, benchmark_ms_ops, benchmark_ms_ops_cp, benchmark_dhellam
+    (dhellam/common/benchmark.py) exist and time plain callables on CPU."""
+    import time
+
+    import torch
+    from dhellam_b200.common import benchmark, benchmark_dhellam, benchmark_ms_ops, benchmark_ms_ops_cp
+    x = torch.randn(32, 32)
+    assert benchmark(3, lambda a: a @ a, x) >= 0.0
+    assert benchmark_ms_ops(3, None, None, [lambda: x @ x], [lambda: x + x], comm=lambda: x.sum()) >= 0.0
+    assert benchmark_ms_ops_cp(3, None, None, [lambda: x @ x], [lambda: x + x], [lambda: x.sum(), lambda: x.mean()], wait_fwd=True) >= 0.0
+    seq, par, sp = benchmark_dhellam(3, lambda: time.sleep(0.004), lambda: time.sleep(0.002))
+    assert seq > par and sp > 1.2
