@@ -17,6 +17,7 @@ N+1-round schedule) and nothing is routed through autograd or a global dictionar
 from __future__ import annotations
 
 import math
+import time
 from dataclasses import dataclass, field
 from typing import Dict, List, Optional
 
@@ -99,6 +100,11 @@ class DoubleStrandEngine:
         self._carry = (None, None)
         self._inbox = {"next": [None, None], "prev": [None, None]}
         self.grad_reducer = None          # set by the trainer when data parallelism is on
+        # "pp-bubble": time the communication stream spends in the pipeline exchanges of a step
+        # (waiting for the neighbour stage included), measured with events on that stream instead
+        # of the reference's extra 1-element exchange + device synchronisation (megatron.patch:82-96)
+        self.time_pp = False
+        self._pp_spans: List[tuple] = []
 
     # ------------------------------------------------------------------ helpers
     @property
@@ -230,16 +236,40 @@ class DoubleStrandEngine:
             st.s3.wait_stream(st.s1)
             st.s3.wait_stream(st.s2)
         self._set_stream("S3")
+        t0 = None
+        if self.time_pp:
+            if st.cuda:
+                t0 = torch.cuda.Event(enable_timing=True)
+                t0.record(st.s3)
+            else:
+                t0 = time.perf_counter()
         with self._on("S3"):
             for tns in list(send_next) + list(send_prev):
                 if tns is not None and tns.is_cuda:
                     tns.record_stream(st.s3)
             from_next, from_prev = PP.exchange(ps, send_next, send_prev, recv_next, recv_prev, shape, self.env.dtype,
                                                self.env.device)
+        if t0 is not None:
+            if st.cuda:
+                t1 = torch.cuda.Event(enable_timing=True)
+                t1.record(st.s3)
+                self._pp_spans.append((t0, t1))
+            else:
+                self._pp_spans.append((t0, time.perf_counter()))
         if st.cuda:
             st.s1.wait_stream(st.s3)
             st.s2.wait_stream(st.s3)
         self._inbox = {"next": from_next, "prev": from_prev}
+
+    def pp_bubble_ms(self) -> float:
+        """Sum of the exchange spans recorded since the last call (synchronises on GPUs)."""
+        spans, self._pp_spans = self._pp_spans, []
+        if not spans:
+            return 0.0
+        if self.streams.cuda:
+            torch.cuda.synchronize()
+            return float(sum(a.elapsed_time(b) for a, b in spans))
+        return float(sum(b - a for a, b in spans) * 1e3)
 
     # ------------------------------------------------------------------ whole step
     def run_step(self, mbs: List[MicroBatch]) -> List[torch.Tensor]:

@@ -81,3 +81,24 @@ CASES = [
 @pytest.mark.parametrize("name,world,par,n_mb,B,seq,ov", CASES, ids=[f"{c[0]}-{'x'.join(f'{k}{v}' for k, v in c[2].items())}" for c in CASES])
 def test_parallel_engine_matches_autograd(name, world, par, n_mb, B, seq, ov):
     run_ranks(_worker, world, name, par, n_mb, B, seq, ov)
+
+
+def _pp_bubble_worker(rank, world):
+    from dhellam_b200.config import ParallelConfig, TrainConfig, preset
+    from dhellam_b200.data import make_microbatch, synthetic_tokens
+    from dhellam_b200.trainer import Trainer
+    cfg = preset("tiny-llama", num_layers=4, seq_length=32)
+    pcfg = ParallelConfig(pp=2)
+    train = TrainConfig(micro_batch_size=1, global_batch_size=3, dtype="fp32")
+    tr = Trainer(cfg, pcfg, train, device="cpu")
+    tr.engine.time_pp = True
+    mbs = [make_microbatch(cfg, tr.ps, synthetic_tokens(cfg, 1, 9 + i), i, 9 + i, "cpu") for i in range(3)]
+    tr.optimizer.zero_grad()
+    tr.engine.run_step(mbs)
+    ms = tr.engine.pp_bubble_ms()
+    assert ms > 0.0                       # every tick but the last exchanges with the neighbour stage
+    assert tr.engine.pp_bubble_ms() == 0.0  # reading clears the record
+
+
+def test_pipeline_exchange_time_is_recorded():
+    run_ranks(_pp_bubble_worker, 2)

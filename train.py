@@ -69,6 +69,7 @@ def main(argv=None):
         path, _, dt = args.data_path[-1].partition(":")
         dataset = TokenFileDataset(path, cfg.seq_length, dt or "int32", seed=train.seed)
         print_rank0(f"data: {path} ({len(dataset)} samples of {cfg.seq_length + 1} tokens)")
+    tr.engine.time_pp = pcfg.pp > 1 and args.timing_log_level >= 2
     for it in range(start, train.train_iters):
         mbs = (file_step_batches(dataset, cfg, train, tr.ps, it, device) if dataset is not None
                else synthetic_step_batches(cfg, train, tr.ps, it, device))
@@ -84,7 +85,8 @@ def main(argv=None):
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             ms = float(t)
         lv = float(loss) if loss is not None else None
-        rec = ml.log(it + 1, ms, lv, float(tr.last_grad_norm) if tr.last_grad_norm is not None else None)
+        extra = {"pp_bubble_ms": tr.engine.pp_bubble_ms()} if tr.engine.time_pp else None
+        rec = ml.log(it + 1, ms, lv, float(tr.last_grad_norm) if tr.last_grad_norm is not None else None, extra)
         if (it + 1) % train.log_interval == 0:
             print_rank0(f" iteration {it + 1:6d}/{train.train_iters} | elapsed time per iteration (ms): {ms:.1f} | lm loss: "
                         f"{lv if lv is not None else float('nan'):.6E} | grad norm: {rec['grad_norm']} | throughput per GPU "
