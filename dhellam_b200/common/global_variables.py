@@ -7,4 +7,16 @@ them as arguments (``DoubleStrandEngine.run_step``, ``Env``); the dict is kept s
 written against the reference finds the same keys, and ``Trainer`` mirrors the values
 that outside code used to read: ``loss`` after every step and ``loss_scale_func``.
 """
-GLOBAL_VARIABLES = {"inputs": None, "loss": None, "loss_scale_func": None}
+
+
+class _Blackboard(dict):
+    """A key that was never written reads as an empty dict that is kept under that key
+    (what the reference's blackboard does), so ``GLOBAL_VARIABLES["x"]["y"] = 1`` works
+    without set-up."""
+
+    def __missing__(self, key):
+        value = self[key] = {}
+        return value
+
+
+GLOBAL_VARIABLES = _Blackboard(inputs=None, loss=None, loss_scale_func=None)
