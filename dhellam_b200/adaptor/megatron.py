@@ -87,7 +87,11 @@ def _add_megatron_args(parser):
     t.add_argument("--clip-grad", type=float, default=1.0)
     t.add_argument("--fp16", action="store_true")
     t.add_argument("--bf16", action="store_true")
-    t.add_argument("--initial-loss-scale", type=float, default=1.0)
+    t.add_argument("--initial-loss-scale", type=float, default=2.0 ** 32)
+    t.add_argument("--loss-scale", type=float, default=None, help="constant loss scale (else dynamic under --fp16)")
+    t.add_argument("--loss-scale-window", type=int, default=1000)
+    t.add_argument("--hysteresis", type=int, default=2)
+    t.add_argument("--min-loss-scale", type=float, default=1.0)
     t.add_argument("--use-distributed-optimizer", action="store_true")
     t.add_argument("--seed", type=int, default=1234)
     t.add_argument("--no-fused-comm", action="store_true", help="library collectives instead of in-kernel ones")
@@ -150,7 +154,11 @@ def configs_from_args(args, world_size: int):
         dtype="bf16" if (args.bf16 or args.fp16) else "fp32", seed=args.seed, fused_comm=not args.no_fused_comm,
         schedule_config=args.schedule_config, dhellam=bool(args.dhellam), compute_streams=args.compute_streams,
         train_iters=args.train_iters, log_interval=args.log_interval, save=args.save, load=args.load,
-        save_interval=args.save_interval, distributed_timeout_minutes=args.distributed_timeout_minutes)
+        save_interval=args.save_interval, distributed_timeout_minutes=args.distributed_timeout_minutes,
+        # Megatron semantics: --loss-scale fixes the factor; --fp16 without it turns the dynamic scaler on
+        loss_scale=args.loss_scale if args.loss_scale is not None else 1.0,
+        dynamic_loss_scale=bool(args.fp16) and args.loss_scale is None, initial_loss_scale=args.initial_loss_scale,
+        loss_scale_window=args.loss_scale_window, hysteresis=args.hysteresis, min_loss_scale=args.min_loss_scale)
     return cfg, pcfg, train
 
 

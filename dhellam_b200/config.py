@@ -120,6 +120,15 @@ class TrainConfig:
     load: Optional[str] = None
     save_interval: int = 10000
     distributed_timeout_minutes: float = 2.0
+    # loss scaling (Megatron's --loss-scale / --initial-loss-scale / --loss-scale-window / --hysteresis /
+    # --min-loss-scale): a constant factor, or the dynamic scaler that halves on overflow and doubles after a
+    # window of good steps.  bf16 needs neither; it is there for 16-bit runs configured the reference's way.
+    loss_scale: float = 1.0
+    dynamic_loss_scale: bool = False
+    initial_loss_scale: float = 65536.0
+    loss_scale_window: int = 1000
+    hysteresis: int = 2
+    min_loss_scale: float = 1.0
 
     def num_microbatches(self, dp: int) -> int:
         assert self.global_batch_size % (self.micro_batch_size * dp) == 0, "global batch must divide by micro-batch x dp"

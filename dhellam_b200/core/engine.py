@@ -104,6 +104,7 @@ class DoubleStrandEngine:
         # (waiting for the neighbour stage included), measured with events on that stream instead
         # of the reference's extra 1-element exchange + device synchronisation (megatron.patch:82-96)
         self.time_pp = False
+        self.loss_scale = 1.0             # factor on the loss gradient; the trainer copies the optimizer's value in
         self._pp_spans: List[tuple] = []
 
     # ------------------------------------------------------------------ helpers
@@ -278,7 +279,7 @@ class DoubleStrandEngine:
         N = len(mbs)
         self.losses = []
         self.env.moe_aux = []
-        self.grad_scale = 1.0 / N
+        self.grad_scale = self.loss_scale / N
         self.env.grad_scale = self.grad_scale
         st = self.streams
         if self.grad_reducer is not None:

@@ -53,6 +53,37 @@ def sum_squares(t, stream=None):
     return out
 
 
+class DynamicLossScaler:
+    """Loss scale that backs off on overflow and grows after a window of good steps (the
+    behaviour of Megatron's dynamic grad scaler, which the reference's fp16 run relies on:
+    script/run.sh:117 ``--initial-loss-scale 65536``).  ``hysteresis`` overflows in a row are
+    tolerated before the scale is halved."""
+
+    def __init__(self, initial: float = 65536.0, min_scale: float = 1.0, growth: float = 2.0, backoff: float = 0.5,
+                 window: int = 1000, hysteresis: int = 2):
+        self.scale, self.min_scale = float(initial), float(min_scale)
+        self.growth, self.backoff, self.window, self.hysteresis = growth, backoff, window, hysteresis
+        self._good, self._left = 0, hysteresis
+
+    def update(self, overflow: bool):
+        if overflow:
+            self._good = 0
+            self._left -= 1
+            if self._left <= 0:
+                self.scale = max(self.scale * self.backoff, self.min_scale)
+        else:
+            self._good += 1
+            if self._good >= self.window:
+                self._good, self._left = 0, self.hysteresis
+                self.scale *= self.growth
+
+    def state_dict(self):
+        return {"scale": self.scale, "good": self._good, "left": self._left}
+
+    def load_state_dict(self, sd):
+        self.scale, self._good, self._left = float(sd["scale"]), int(sd["good"]), int(sd["left"])
+
+
 class MixedPrecisionAdam:
     """Adam with fp32 master weights over ``model.flat_param`` / ``model.flat_grad``.
 
@@ -61,10 +92,13 @@ class MixedPrecisionAdam:
     is updated, and the updated parameters are all-gathered (ZeRO-1).
     """
 
-    def __init__(self, model, train: TrainConfig, ps, distributed: bool = False, loss_scale: float = 1.0):
+    def __init__(self, model, train: TrainConfig, ps, distributed: bool = False, loss_scale: Optional[float] = None):
         self.model, self.train, self.ps = model, train, ps
         self.step_count = 0
-        self.loss_scale = loss_scale
+        self.skipped_steps = 0
+        self.scaler = DynamicLossScaler(train.initial_loss_scale, train.min_loss_scale, window=train.loss_scale_window,
+                                        hysteresis=train.hysteresis) if train.dynamic_loss_scale else None
+        self._static_scale = float(loss_scale if loss_scale is not None else train.loss_scale)
         self.distributed = distributed and ps.dp * ps.cp > 1 and not model.cfg.is_moe
         flat = model.flat_param
         n = flat.numel()
@@ -96,6 +130,17 @@ class MixedPrecisionAdam:
                 self.segments[-1] = (self.segments[-1][0], hi, wd)
             else:
                 self.segments.append((lo, hi, wd))
+
+    @property
+    def loss_scale(self) -> float:
+        return self.scaler.scale if self.scaler is not None else self._static_scale
+
+    @loss_scale.setter
+    def loss_scale(self, value: float):
+        if self.scaler is not None:
+            self.scaler.scale = float(value)
+        else:
+            self._static_scale = float(value)
 
     # ---- hooks kept from the Megatron optimizer API
     def scale_loss(self, loss):
@@ -183,6 +228,16 @@ class MixedPrecisionAdam:
         self.reduce_gradients()
         norm = self.grad_norm()
         scale = 1.0 / self.loss_scale
+        scale_of_norm = scale              # the scaler may change the scale below; the norm was taken with this one
+        if self.scaler is not None:
+            # the norm is already summed over every model-parallel group, so all ranks see the same
+            # overflow; one host read per step, as in Megatron's fp16 optimizer
+            overflow = not bool(torch.isfinite(norm))
+            used = self.loss_scale
+            self.scaler.update(overflow)
+            if overflow:
+                self.skipped_steps += 1
+                return norm * (1.0 / used)
         if tr.clip_grad and tr.clip_grad > 0:
             clip = torch.clamp(tr.clip_grad / (norm * scale + 1e-6), max=1.0)
             scale = float(clip) * scale     # host read: one scalar per step, after the last backward
@@ -203,12 +258,13 @@ class MixedPrecisionAdam:
                 mine[: self.hi - self.lo] = flat_p[self.lo:self.hi]
                 dist.all_gather(parts, mine, group=self.group)
                 flat_p.copy_(torch.cat(parts)[:n])
-        return norm * (1.0 / self.loss_scale)
+        return norm * scale_of_norm
 
     # ---- checkpoint support
     def state_dict(self):
         return {"step": self.step_count, "lo": self.lo, "hi": self.hi, "master": self.master, "exp_avg": self.exp_avg,
-                "exp_avg_sq": self.exp_avg_sq, "loss_scale": self.loss_scale}
+                "exp_avg_sq": self.exp_avg_sq, "loss_scale": self.loss_scale,
+                "scaler": self.scaler.state_dict() if self.scaler is not None else None}
 
     def load_state_dict(self, sd):
         self.step_count = int(sd["step"])
@@ -217,3 +273,5 @@ class MixedPrecisionAdam:
         self.exp_avg.copy_(sd["exp_avg"])
         self.exp_avg_sq.copy_(sd["exp_avg_sq"])
         self.loss_scale = sd.get("loss_scale", 1.0)
+        if self.scaler is not None and sd.get("scaler"):
+            self.scaler.load_state_dict(sd["scaler"])

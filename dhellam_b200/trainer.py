@@ -71,6 +71,7 @@ class Trainer:
         """One optimizer step over ``mbs``.  Returns the mean loss as a tensor on the first
         pipeline stage (``None`` elsewhere); nothing here synchronises the host."""
         self.optimizer.zero_grad()
+        self.engine.loss_scale = self.optimizer.loss_scale
         losses = self.engine.run_step(mbs)
         self.last_grad_norm = self.optimizer.step(lr)
         self.iteration += 1
