@@ -105,8 +105,7 @@ class MixedPrecisionAdam:
         self.group = ps.dp_cp_group
         self.gsize = ps.dp * ps.cp
         if self.distributed:
-            pad = (-n) % self.gsize
-            assert pad == 0 or True
+            # the last rank's shard may be shorter when n does not divide by the group size
             self.shard = (n + self.gsize - 1) // self.gsize
             grank = dist.get_rank(self.group)
             self.lo = min(grank * self.shard, n)
