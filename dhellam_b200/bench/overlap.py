@@ -114,6 +114,7 @@ def main(argv=None):
             print_rank0(f"{fn_name:7s} || {bn_name:7s}: alone {a:.3f} + {b:.3f} ms, together {c:.3f} ms, "
                         f"speedup {speed[(fn_name, bn_name)]:.3f}, efficiency {eff[(fn_name, bn_name)]:.3f}")
     if not dist.is_initialized() or dist.get_rank() == 0:
+        os.makedirs(args.out_dir, exist_ok=True)
         for fname, table in (("speedup.csv", speed), ("efficiency.csv", eff)):
             with open(os.path.join(args.out_dir, fname), "w", newline="") as fp:
                 wr = csv.writer(fp)

@@ -91,3 +91,18 @@ def test_search_pipeline_end_to_end_on_cpu(tmp_path):
     lines = (tmp_path / "op_profile_num.txt").read_text().strip().splitlines()
     assert len(lines) > 300
     PS.set_state(None)
+
+
+def test_overlap_micro_benchmark_writes_both_tables_on_cpu(tmp_path):
+    """The pairwise overlap benchmark (reference: micro_benchmark/overlap.py) runs on CPU tensors
+    and writes speedup.csv and efficiency.csv into a directory it creates."""
+    import csv
+
+    from dhellam_b200.bench import overlap
+    out = tmp_path / "new_dir"
+    rc = overlap.main(["--rows", "64", "--hidden", "128", "--ffn", "256", "--heads", "2", "--kv-heads", "1", "--seq", "32",
+                       "--repeat", "1", "--out-dir", str(out)])
+    assert rc in (0, None)
+    for name in ("speedup.csv", "efficiency.csv"):
+        rows = list(csv.reader(open(out / name)))
+        assert rows[0][0] == "fwd\\bwd" and len(rows) > 3 and len(rows[1]) == len(rows[0])
