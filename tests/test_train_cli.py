@@ -33,3 +33,27 @@ def test_train_cli_with_schedule_metrics_and_resume(tmp_path):
     assert (tmp_path / "ck" / "latest_checkpointed_iteration.txt").read_text() == "3"
     out2 = _run(["--train-iters", "4", "--load", str(tmp_path / "ck")], str(tmp_path))
     assert "resumed from" in out2 and "iteration      4/" in out2.replace("  ", " ") or "resumed from" in out2
+
+
+def test_train_cli_reads_a_token_file_and_runs_fp16_style_loss_scaling(tmp_path):
+    import numpy as np
+    path = tmp_path / "tokens.bin"
+    (np.arange(4000) % 128).astype(np.int32).tofile(str(path))
+    out = _run(["--train-iters", "2", "--data-path", str(path), "--fp16", "--initial-loss-scale", "1024",
+                "--metrics-jsonl", str(tmp_path / "m.jsonl")], str(tmp_path))
+    assert "data:" in out and "tokens.bin" in out
+    recs = [json.loads(l) for l in open(tmp_path / "m.jsonl")]
+    assert len(recs) == 2 and all(r["loss"] == r["loss"] for r in recs)       # finite losses
+
+
+def test_train_cli_two_ranks_tensor_and_sequence_parallel(tmp_path):
+    """The launcher path of the one-click script on CPU ranks (gloo): torch.distributed.run + train.py."""
+    env = dict(os.environ, PYTHONPATH=ROOT)
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr", "127.0.0.1",
+           "--master-port", "29537", os.path.join(ROOT, "train.py")] + ARGS + [
+               "--tensor-model-parallel-size", "2", "--sequence-parallel", "--train-iters", "2", "--timing-log-level", "2",
+               "--metrics-jsonl", str(tmp_path / "m.jsonl")]
+    p = subprocess.run(cmd, cwd=str(tmp_path), env=env, capture_output=True, text=True, timeout=600)
+    assert p.returncode == 0, p.stdout[-2000:] + p.stderr[-4000:]
+    recs = [json.loads(l) for l in open(tmp_path / "m.jsonl")]
+    assert len(recs) == 2 and recs[0]["tokens_per_s"] > 0
