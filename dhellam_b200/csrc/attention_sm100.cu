@@ -562,6 +562,280 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
   if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem, 512); }
 }
 
+// ----------------------------------------------------------------------- backward, dK/dV, pipelined form
+// Same work split as attn_bwd_kernel (one CTA per 128 keys, loop over the query heads of its
+// part of the KV group and over the query blocks that see these keys), rearranged so that the
+// tensor cores, the TMA and the math warps overlap:
+//   * the scores are formed transposed, S^T = K Q^T and dP^T = V dO^T (keys on the TMEM lanes,
+//     64 queries per iteration on the columns), double-buffered in TMEM (4 x 64 columns), so the
+//     products of iteration i+1 run while the math warps work on iteration i;
+//   * a math thread owns one key row: it forms P^T = exp2(S^T - lse[q]) and dS^T = P^T (dP^T -
+//     delta[q]) with the per-query statistics taken from registers of its warp (shuffles), and
+//     writes its 64-byte piece of the row into a K-major [128 keys][64 queries] shared-memory
+//     tile, which is the A operand of dV += P^T dO and dK += dS^T Q as it stands;
+//   * Q / dO tiles are 64 rows (16 KiB each) in a 2-stage ring, P^T / dS^T tiles likewise, which
+//     fits 192 KiB; the TMA for iteration i+1 is in flight during iteration i.
+// dV / dK accumulate in TMEM columns [256, 512) exactly as in attn_bwd_kernel, so the epilogue
+// (bf16 rows, or fp32 partials under the head split) is the same.
+constexpr int BQT = 64;                          // queries per iteration
+constexpr int QT_HALF = BQT * 128;               // one [64 rows][64 elems] swizzled box
+constexpr int QT_TILE = 2 * QT_HALF;             // [64][128] bf16
+constexpr int PT_TILE = BKV * 128;               // [128 keys][64 queries] bf16, one 128-byte row per key
+struct BwdTCtl {
+  uint64_t kv_full, qdo_full[2], stage_free[2], sdp_full[2], sdp_empty[2], pds_ready[2], acc_full;
+  uint32_t tmem_base;
+  int abort_flag;
+};
+constexpr int BWDT_SMEM = 2 * TILE_BYTES + 4 * QT_TILE + 4 * PT_TILE + 1024 + 256;
+
+__global__ void __launch_bounds__(BWD_THREADS, 1)
+attn_bwd_t_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ CUtensorMap tk, const __grid_constant__ CUtensorMap tv,
+                  const __grid_constant__ CUtensorMap tdo, const float* __restrict__ lse, const float* __restrict__ delta,
+                  __nv_bfloat16* __restrict__ dk, __nv_bfloat16* __restrict__ dv, const BwdGeometry g) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sK = smem;
+  uint8_t* sV = smem + TILE_BYTES;
+  uint8_t* sQ = smem + 2 * TILE_BYTES;                     // 2 stages
+  uint8_t* sDO = sQ + 2 * QT_TILE;                         // 2 stages
+  uint8_t* sP = sDO + 2 * QT_TILE;                         // 2 stages
+  uint8_t* sDS = sP + 2 * PT_TILE;                         // 2 stages
+  BwdTCtl* ctl = reinterpret_cast<BwdTCtl*>(sDS + 2 * PT_TILE);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int kb = blockIdx.x, hk = blockIdx.y / g.hs, hpart = blockIdx.y % g.hs, b = blockIdx.z;
+  const int group = g.Hq / g.Hk;
+  const int gpp = group / g.hs;
+  const int hq0 = hk * group + hpart * gpp;
+  const int off = g.Sk - g.Sq;
+  const int nqb = (g.Sq + BQT - 1) / BQT;
+  int qb0 = 0;
+  if (g.causal) {
+    const int first_q = kb * BKV - off;
+    qb0 = first_q <= 0 ? 0 : first_q / BQT;
+  }
+  const int n_iter = qb0 < nqb ? (nqb - qb0) * gpp : 0;
+
+  if (threadIdx.x == 0) {
+    mbar_init(&ctl->kv_full, 1);
+    mbar_init(&ctl->acc_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&ctl->qdo_full[i], 1);
+      mbar_init(&ctl->stage_free[i], 1);
+      mbar_init(&ctl->sdp_full[i], 1);
+      mbar_init(&ctl->sdp_empty[i], 8);
+      mbar_init(&ctl->pds_ready[i], 8);
+    }
+    ctl->abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) { tmem_alloc(&ctl->tmem_base, 512); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = ctl->tmem_base;
+  volatile int* abort_flag = &ctl->abort_flag;
+  // TMEM columns: S^T buffers [0,64) [64,128); dP^T buffers [128,192) [192,256); dV [256,384); dK [384,512)
+
+  if (warp == 0) {
+    if (lane == 0 && n_iter > 0) {
+      tma_prefetch_desc(&tq); tma_prefetch_desc(&tk); tma_prefetch_desc(&tv); tma_prefetch_desc(&tdo);
+      mbar_expect_tx(&ctl->kv_full, 2 * TILE_BYTES);
+      tma_load_4d(sK, &tk, &ctl->kv_full, 0, hk, b, kb * BKV);
+      tma_load_4d(sK + HALF_BYTES, &tk, &ctl->kv_full, 64, hk, b, kb * BKV);
+      tma_load_4d(sV, &tv, &ctl->kv_full, 0, hk, b, kb * BKV);
+      tma_load_4d(sV + HALF_BYTES, &tv, &ctl->kv_full, 64, hk, b, kb * BKV);
+      for (int it = 0; it < n_iter; ++it) {
+        const int st = it & 1;
+        const uint32_t ph = (it >> 1) & 1;
+        const int hq = hq0 + it % gpp;
+        const int qb = qb0 + it / gpp;
+        if (!mbar_wait(&ctl->stage_free[st], ph ^ 1, abort_flag, g.status, 530)) break;
+        mbar_expect_tx(&ctl->qdo_full[st], 2 * QT_TILE);
+        uint8_t* q_dst = sQ + st * QT_TILE;
+        uint8_t* do_dst = sDO + st * QT_TILE;
+        tma_load_4d(q_dst, &tq, &ctl->qdo_full[st], 0, hq, b, qb * BQT);
+        tma_load_4d(q_dst + QT_HALF, &tq, &ctl->qdo_full[st], 64, hq, b, qb * BQT);
+        tma_load_4d(do_dst, &tdo, &ctl->qdo_full[st], 0, hq, b, qb * BQT);
+        tma_load_4d(do_dst + QT_HALF, &tdo, &ctl->qdo_full[st], 64, hq, b, qb * BQT);
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    if (lane == 0 && n_iter > 0) {
+      constexpr uint32_t id_st = umma_idesc_bf16(128, BQT, 0, 0);    // S^T, dP^T: A = K / V (K-major), B = Q / dO (K-major), N = 64
+      constexpr uint32_t id_acc = umma_idesc_bf16(128, 128, 0, 1);   // dV, dK: A = P^T / dS^T (K-major), B = dO / Q (MN-major)
+      const uint32_t k_base = smem_u32(sK), v_base = smem_u32(sV);
+      bool ok = mbar_wait(&ctl->kv_full, 0, abort_flag, g.status, 540);
+      // S^T and dP^T of iteration j into TMEM buffer j & 1
+      auto issue_scores = [&](int j) -> bool {
+        const int st = j & 1;
+        const uint32_t ph = (j >> 1) & 1;
+        if (!mbar_wait(&ctl->qdo_full[st], ph, abort_flag, g.status, 541)) return false;
+        if (!mbar_wait(&ctl->sdp_empty[st], ph ^ 1, abort_flag, g.status, 542)) return false;
+        tc_fence_after();
+        const uint32_t q_base = smem_u32(sQ + st * QT_TILE), do_base = smem_u32(sDO + st * QT_TILE);
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk)
+          umma_bf16(tmem + 64 * st, desc_kmajor(k_base, kk), umma_smem_desc(q_base + (kk >> 2) * QT_HALF + (kk & 3) * 32, 16, 1024), id_st,
+                    kk > 0);
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk)
+          umma_bf16(tmem + 128 + 64 * st, desc_kmajor(v_base, kk), umma_smem_desc(do_base + (kk >> 2) * QT_HALF + (kk & 3) * 32, 16, 1024),
+                    id_st, kk > 0);
+        umma_commit(&ctl->sdp_full[st]);
+        return true;
+      };
+      if (ok) ok = issue_scores(0);
+      for (int it = 0; it < n_iter && ok; ++it) {
+        const int st = it & 1;
+        const uint32_t ph = (it >> 1) & 1;
+        if (it + 1 < n_iter && !issue_scores(it + 1)) { ok = false; break; }
+        if (!mbar_wait(&ctl->pds_ready[st], ph, abort_flag, g.status, 543)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t p_base = smem_u32(sP + st * PT_TILE), ds_base = smem_u32(sDS + st * PT_TILE);
+        const uint32_t q_base = smem_u32(sQ + st * QT_TILE), do_base = smem_u32(sDO + st * QT_TILE);
+#pragma unroll
+        for (int kk = 0; kk < BQT / 16; ++kk)
+          umma_bf16(tmem + 256, umma_smem_desc(p_base + kk * 32, 16, 1024), umma_smem_desc(do_base + kk * 2048, QT_HALF, 1024), id_acc,
+                    (it | kk) != 0);
+#pragma unroll
+        for (int kk = 0; kk < BQT / 16; ++kk)
+          umma_bf16(tmem + 384, umma_smem_desc(ds_base + kk * 32, 16, 1024), umma_smem_desc(q_base + kk * 2048, QT_HALF, 1024), id_acc,
+                    (it | kk) != 0);
+        umma_commit(&ctl->stage_free[st]);      // Q, dO, P^T, dS^T of this stage are free once dV and dK have read them
+      }
+      if (ok) umma_commit(&ctl->acc_full);
+    }
+    __syncwarp();
+  } else {
+    // warps 2..5 take query columns [0, 32) of the 64-column buffers, warps 6..9 take [32, 64);
+    // each warp covers the TMEM lane quarter (key rows) it is allowed to read
+    const int quarter = warp & 3;
+    const int c_half = (warp - 2) >> 2;
+    const int r = quarter * 32 + lane;                 // key row inside the block
+    const int kv_g = kb * BKV + r;
+    const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
+    const float sl2 = g.scale * LOG2E;
+    bool ok = n_iter > 0;
+    for (int it = 0; it < n_iter && ok; ++it) {
+      const int st = it & 1;
+      const uint32_t ph = (it >> 1) & 1;
+      const int hq = hq0 + it % gpp;
+      const int qb = qb0 + it / gpp;
+      // lane j holds the statistics of query column j of this warp's 32 columns
+      const int q_mine = qb * BQT + c_half * 32 + lane;
+      const bool q_ok = q_mine < g.Sq;
+      const long long stat = ((long long)b * g.Hq + hq) * g.Sq + q_mine;
+      const float L_mine = q_ok ? lse[stat] * LOG2E : INFINITY;     // +inf: exp2(x - inf) = 0 for rows past the end
+      const float d_mine = q_ok ? delta[stat] : 0.f;
+      if (!mbar_wait(&ctl->sdp_full[st], ph, abort_flag, g.status, 550)) { ok = false; break; }
+      tc_fence_after();
+      uint32_t sv[32], dpv[32];
+      tmem_ld32(tmem + 64 * st + lane_base + c_half * 32, sv);
+      tmem_ld32(tmem + 128 + 64 * st + lane_base + c_half * 32, dpv);
+      tmem_ld_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&ctl->sdp_empty[st]);              // this TMEM buffer may take iteration it + 2
+      uint32_t pk[16], dsk[16];
+      const int q0 = qb * BQT + c_half * 32;
+#pragma unroll
+      for (int j = 0; j < 32; j += 2) {
+        float pe[2], de[2];
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const float Lq = __shfl_sync(0xffffffffu, L_mine, j + e);
+          const float dq_ = __shfl_sync(0xffffffffu, d_mine, j + e);
+          const bool valid = kv_g < g.Sk && (!g.causal || kv_g <= q0 + j + e + off);
+          const float p = valid ? exp2f(__uint_as_float(sv[j + e]) * sl2 - Lq) : 0.f;
+          pe[e] = p;
+          de[e] = p * (__uint_as_float(dpv[j + e]) - dq_);
+        }
+        pk[j >> 1] = pack_bf16x2(pe[0], pe[1]);
+        dsk[j >> 1] = pack_bf16x2(de[0], de[1]);
+      }
+      if (!mbar_wait(&ctl->stage_free[st], ph ^ 1, abort_flag, g.status, 551)) { ok = false; break; }
+      uint8_t* prow = sP + st * PT_TILE + r * 128;
+      uint8_t* drow = sDS + st * PT_TILE + r * 128;
+#pragma unroll
+      for (int t = 0; t < 4; ++t) {
+        const uint32_t o = (uint32_t)(((c_half * 4 + t) ^ (r & 7)) << 4);
+        *reinterpret_cast<uint4*>(prow + o) = make_uint4(pk[4 * t], pk[4 * t + 1], pk[4 * t + 2], pk[4 * t + 3]);
+        *reinterpret_cast<uint4*>(drow + o) = make_uint4(dsk[4 * t], dsk[4 * t + 1], dsk[4 * t + 2], dsk[4 * t + 3]);
+      }
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&ctl->pds_ready[st]);
+    }
+    // epilogue: this thread's key row of dV and dK, columns [64 * c_half, 64 * c_half + 64)
+    const int c_lo = c_half * 2;
+    const int kj = kv_g;
+    const long long part_elems = (long long)g.Sk * g.B * g.Hk * D;
+    float* pdv = g.hs > 1 ? g.part + (long long)hpart * part_elems + (((long long)kj * g.B + b) * g.Hk + hk) * D : nullptr;
+    float* pdk = g.hs > 1 ? pdv + (long long)g.hs * part_elems : nullptr;
+    if (ok && n_iter > 0) {
+      if (mbar_wait(&ctl->acc_full, 0, abort_flag, g.status, 552)) {
+        tc_fence_after();
+        __nv_bfloat16* dvr = dv + (long long)kj * g.dv_s + (long long)b * g.dv_b + (long long)hk * g.dv_h;
+        __nv_bfloat16* dkr = dk + (long long)kj * g.dk_s + (long long)b * g.dk_b + (long long)hk * g.dk_h;
+#pragma unroll 1
+        for (int c = c_lo; c < c_lo + 2; ++c) {
+          uint32_t a[32], bb[32];
+          tmem_ld32(tmem + 256 + lane_base + c * 32, a);
+          tmem_ld32(tmem + 384 + lane_base + c * 32, bb);
+          tmem_ld_wait();
+          if (kj >= g.Sk) continue;
+          if (g.hs > 1) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              reinterpret_cast<float4*>(pdv + c * 32)[j] = make_float4(__uint_as_float(a[4 * j]), __uint_as_float(a[4 * j + 1]),
+                                                                       __uint_as_float(a[4 * j + 2]), __uint_as_float(a[4 * j + 3]));
+              reinterpret_cast<float4*>(pdk + c * 32)[j] =
+                  make_float4(__uint_as_float(bb[4 * j]) * g.scale, __uint_as_float(bb[4 * j + 1]) * g.scale,
+                              __uint_as_float(bb[4 * j + 2]) * g.scale, __uint_as_float(bb[4 * j + 3]) * g.scale);
+            }
+          } else {
+#pragma unroll
+            for (int q4 = 0; q4 < 4; ++q4) {
+              uint4 u, w;
+              const int i0 = q4 * 8;
+              u.x = pack_bf16x2(__uint_as_float(a[i0]), __uint_as_float(a[i0 + 1]));
+              u.y = pack_bf16x2(__uint_as_float(a[i0 + 2]), __uint_as_float(a[i0 + 3]));
+              u.z = pack_bf16x2(__uint_as_float(a[i0 + 4]), __uint_as_float(a[i0 + 5]));
+              u.w = pack_bf16x2(__uint_as_float(a[i0 + 6]), __uint_as_float(a[i0 + 7]));
+              w.x = pack_bf16x2(__uint_as_float(bb[i0]) * g.scale, __uint_as_float(bb[i0 + 1]) * g.scale);
+              w.y = pack_bf16x2(__uint_as_float(bb[i0 + 2]) * g.scale, __uint_as_float(bb[i0 + 3]) * g.scale);
+              w.z = pack_bf16x2(__uint_as_float(bb[i0 + 4]) * g.scale, __uint_as_float(bb[i0 + 5]) * g.scale);
+              w.w = pack_bf16x2(__uint_as_float(bb[i0 + 6]) * g.scale, __uint_as_float(bb[i0 + 7]) * g.scale);
+              reinterpret_cast<uint4*>(dvr + c * 32)[q4] = u;
+              reinterpret_cast<uint4*>(dkr + c * 32)[q4] = w;
+            }
+          }
+        }
+      }
+    } else if (n_iter == 0 && kj < g.Sk) {
+      // no query sees these keys: zero gradients (each warp half clears its own 64 columns)
+      if (g.hs > 1) {
+        for (int i = c_lo * 8; i < c_lo * 8 + 16; ++i) {
+          reinterpret_cast<float4*>(pdv)[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+          reinterpret_cast<float4*>(pdk)[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+      } else {
+        __nv_bfloat16* dvr = dv + (long long)kj * g.dv_s + (long long)b * g.dv_b + (long long)hk * g.dv_h;
+        __nv_bfloat16* dkr = dk + (long long)kj * g.dk_s + (long long)b * g.dk_b + (long long)hk * g.dk_h;
+        for (int i = c_lo * 4; i < c_lo * 4 + 8; ++i) {
+          reinterpret_cast<uint4*>(dvr)[i] = make_uint4(0, 0, 0, 0);
+          reinterpret_cast<uint4*>(dkr)[i] = make_uint4(0, 0, 0, 0);
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem, 512); }
+}
+
 // Sums the `hs` fp32 partials of a head-split backward and writes bf16 dK / dV.
 // One thread per 8 consecutive head-dim elements of one (key, batch, KV head) row of dV and of dK.
 __global__ void __launch_bounds__(256) attn_dkv_reduce_kernel(const float* __restrict__ part, int hs, __nv_bfloat16* __restrict__ dk,
@@ -774,10 +1048,11 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant
 }
 
 
-static const CUtensorMap* tensor_map_sbhd(const void* p, int S, int B, int H, long long s_s, long long s_b, long long s_h) {
+static const CUtensorMap* tensor_map_sbhd(const void* p, int S, int B, int H, long long s_s, long long s_b, long long s_h,
+                                          uint32_t box_rows = 128) {
   const uint64_t dims[4] = {(uint64_t)D, (uint64_t)H, (uint64_t)B, (uint64_t)S};
   const uint64_t st[3] = {(uint64_t)s_h * 2, (uint64_t)s_b * 2, (uint64_t)s_s * 2};
-  const uint32_t box[4] = {64, 1, 1, 128};
+  const uint32_t box[4] = {64, 1, 1, box_rows};
   return get_tmap_4d(p, 2, dims, st, box, true);
 }
 
@@ -877,8 +1152,29 @@ int dh_attn_bwd(const void* dout, const void* q, const void* k, const void* v, c
   g.status = st;
   g.hs = bwd_head_split(B, Hq, Hk, Sk);
   g.part = g.hs > 1 ? reinterpret_cast<float*>(reinterpret_cast<char*>(scratch) + ((int64_t)rows * 4 + 255) / 256 * 256) : nullptr;
-  attn_bwd_kernel<<<dim3((Sk + BKV - 1) / BKV, Hk * g.hs, B), BWD_THREADS, BWD_SMEM, stream>>>(*tq, *tk, *tv, *tdo, (const float*)lse, delta,
-                                                                                             (__nv_bfloat16*)dk, (__nv_bfloat16*)dv, g);
+  // DHELLAM_ATTN_BWD_T=1 selects the pipelined (transposed-score) form of the dK/dV kernel
+  static int use_t = -1;
+  if (use_t < 0) {
+    const char* ev = getenv("DHELLAM_ATTN_BWD_T");
+    use_t = ev ? atoi(ev) : 0;
+  }
+  if (use_t) {
+    const CUtensorMap* tq64 = tensor_map_sbhd(q, Sq, B, Hq, sq[0], sq[1], sq[2], BQT);
+    const CUtensorMap* tdo64 = tensor_map_sbhd(dout, Sq, B, Hq, sdo[0], sdo[1], sdo[2], BQT);
+    if (!tq64 || !tdo64) return (int)cudaErrorInvalidValue;
+    static bool configured_t = false;
+    if (!configured_t) {
+      cudaError_t e2 = cudaFuncSetAttribute(attn_bwd_t_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, BWDT_SMEM);
+      if (e2 != cudaSuccess) { set_last_error("dh_attn_bwd: shared memory opt-in failed: %s", cudaGetErrorString(e2)); return (int)e2; }
+      configured_t = true;
+    }
+    attn_bwd_t_kernel<<<dim3((Sk + BKV - 1) / BKV, Hk * g.hs, B), BWD_THREADS, BWDT_SMEM, stream>>>(*tq64, *tk, *tv, *tdo64, (const float*)lse,
+                                                                                                  delta, (__nv_bfloat16*)dk,
+                                                                                                  (__nv_bfloat16*)dv, g);
+  } else {
+    attn_bwd_kernel<<<dim3((Sk + BKV - 1) / BKV, Hk * g.hs, B), BWD_THREADS, BWD_SMEM, stream>>>(*tq, *tk, *tv, *tdo, (const float*)lse, delta,
+                                                                                               (__nv_bfloat16*)dk, (__nv_bfloat16*)dv, g);
+  }
   if (g.hs > 1) {
     const long long n = 2LL * Sk * B * Hk * (D / 8);
     attn_dkv_reduce_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(g.part, g.hs, (__nv_bfloat16*)dk, (__nv_bfloat16*)dv, Sk, B, Hk,
