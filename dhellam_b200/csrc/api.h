@@ -36,6 +36,9 @@ int dh_sm_count();
 int dh_gemm_bf16(const void* a, int64_t lda, int a_mn_major, const void* b, int64_t ldb, int b_mn_major, void* d,
                  int64_t ldd, int d_fp32, int accumulate, int M, int N, int K, int epilogue, int sm_budget,
                  cudaStream_t stream);
+// dK/dV kernel of dh_attn_bwd: 0 = one 128-query tile per iteration (default), 1 = pipelined transposed-score form
+// (64 queries per iteration, double-buffered); -1 = take DHELLAM_ATTN_BWD_T from the environment at the next call.
+void dh_attn_set_bwd_mode(int mode);
 // Kernel choice for dh_gemm_bf16: 0 = per problem (default; also DHELLAM_GEMM_MODE), 1 = single-CTA tiles
 // (128 x 256) only, 2 = CTA-pair tiles (256 x 256, tcgen05 cta_group::2) whenever M > 128.
 void dh_gemm_set_mode(int mode);

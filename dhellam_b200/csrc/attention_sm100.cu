@@ -1062,7 +1062,12 @@ static const CUtensorMap* tensor_map_sbhd(const void* p, int S, int B, int H, lo
 using namespace dh;
 using namespace dh::attn;
 
+// dK/dV kernel choice of dh_attn_bwd: -1 = read DHELLAM_ATTN_BWD_T on first use, 0 = attn_bwd_kernel, 1 = attn_bwd_t_kernel
+static int g_bwd_mode = -1;
+
 extern "C" {
+
+void dh_attn_set_bwd_mode(int mode) { g_bwd_mode = mode; }
 
 int dh_attn_fwd(const void* q, const void* k, const void* v, void* out, void* lse, int64_t q_s, int64_t q_b, int64_t q_h, int64_t k_s,
                 int64_t k_b, int64_t k_h, int64_t v_s, int64_t v_b, int64_t v_h, int B, int Hq, int Hk, int Sq, int Sk, int d, int causal,
@@ -1152,13 +1157,12 @@ int dh_attn_bwd(const void* dout, const void* q, const void* k, const void* v, c
   g.status = st;
   g.hs = bwd_head_split(B, Hq, Hk, Sk);
   g.part = g.hs > 1 ? reinterpret_cast<float*>(reinterpret_cast<char*>(scratch) + ((int64_t)rows * 4 + 255) / 256 * 256) : nullptr;
-  // DHELLAM_ATTN_BWD_T=1 selects the pipelined (transposed-score) form of the dK/dV kernel
-  static int use_t = -1;
-  if (use_t < 0) {
+  // DHELLAM_ATTN_BWD_T=1 (or dh_attn_set_bwd_mode(1)) selects the pipelined (transposed-score) form of the dK/dV kernel
+  if (g_bwd_mode < 0) {
     const char* ev = getenv("DHELLAM_ATTN_BWD_T");
-    use_t = ev ? atoi(ev) : 0;
+    g_bwd_mode = ev ? atoi(ev) : 0;
   }
-  if (use_t) {
+  if (g_bwd_mode == 1) {
     const CUtensorMap* tq64 = tensor_map_sbhd(q, Sq, B, Hq, sq[0], sq[1], sq[2], BQT);
     const CUtensorMap* tdo64 = tensor_map_sbhd(dout, Sq, B, Hq, sdo[0], sdo[1], sdo[2], BQT);
     if (!tq64 || !tdo64) return (int)cudaErrorInvalidValue;

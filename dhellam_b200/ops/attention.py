@@ -121,6 +121,12 @@ def merge_attention_partials(o_a, lse_a, o_b, lse_b):
 
 
 # ----------------------------------------------------------------------------- variable-length API
+def set_attn_bwd_mode(mode: int):
+    """dK/dV kernel on the GPU: 0 = one 128-query tile per iteration (default), 1 = the pipelined
+    transposed-score form, -1 = re-read ``DHELLAM_ATTN_BWD_T`` at the next call."""
+    K.proto("dh_attn_set_bwd_mode", [c_int], None)(int(mode))
+
+
 def pymha_varlen_fwd(q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k, p_dropout: float = 0.0,
                      softmax_scale: float | None = None, is_causal: bool = True, return_softmax: bool = False,
                      math_sm_count: int = 0, profiling: bool = False):

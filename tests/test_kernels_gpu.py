@@ -174,9 +174,18 @@ def test_router_topk():
     assert rel(gates.cpu()[same], gr[same]) < 1e-3
 
 
+@pytest.fixture(params=[0, 1], ids=["tile128", "pipelined64"])
+def attn_bwd_mode(request):
+    """Both dK/dV kernels: the default and the pipelined transposed-score form."""
+    from dhellam_b200.ops.attention import set_attn_bwd_mode
+    set_attn_bwd_mode(request.param)
+    yield request.param
+    set_attn_bwd_mode(0)
+
+
 @pytest.mark.parametrize("Sq,Sk,B,Hq,Hk,causal", [(128, 128, 1, 1, 1, True), (256, 256, 2, 4, 2, True), (384, 384, 1, 2, 1, False),
                                                      (200, 200, 2, 2, 2, True), (128, 256, 1, 2, 1, False), (256, 128, 1, 2, 2, False)])
-def test_attention_forward_backward(Sq, Sk, B, Hq, Hk, causal):
+def test_attention_forward_backward(Sq, Sk, B, Hq, Hk, causal, attn_bwd_mode):
     from dhellam_b200.ops.attention import attn_bwd, attn_fwd
     d = 128
     # strided views into packed buffers, as the engine uses them
