@@ -104,6 +104,10 @@ def _add_megatron_args(parser):
     p.add_argument("--sequence-parallel", action="store_true")
     p.add_argument("--distributed-backend", default=None, choices=[None, "nccl", "gloo"])
     p.add_argument("--distributed-timeout-minutes", type=float, default=2.0)
+    p.add_argument("--step-gate-timeout", type=float, default=120.0,
+                   help="seconds a rank waits for the others to announce a step before raising RankFailure (0: no gate, no heartbeat)")
+    p.add_argument("--heartbeat-interval", type=float, default=0.5)
+    p.add_argument("--heartbeat-timeout", type=float, default=15.0)
     l = parser.add_argument_group(title="logging and checkpoints")
     l.add_argument("--log-interval", type=int, default=1)
     l.add_argument("--log-throughput", action="store_true")
@@ -147,7 +151,7 @@ def configs_from_args(args, world_size: int):
     tp, pp, cp = args.tensor_model_parallel_size, args.pipeline_model_parallel_size, args.context_parallel_size
     assert world_size % (tp * pp * cp) == 0, "world size must divide by tp x pp x cp"
     pcfg = ParallelConfig(tp=tp, pp=pp, cp=cp, ep=args.expert_model_parallel_size, dp=world_size // (tp * pp * cp),
-                          sequence_parallel=True)
+                          sequence_parallel=bool(args.sequence_parallel) or tp == 1)
     train = TrainConfig(
         micro_batch_size=args.micro_batch_size, global_batch_size=args.global_batch_size, lr=args.lr, min_lr=args.min_lr,
         weight_decay=args.weight_decay, adam_beta1=args.adam_beta1, adam_beta2=args.adam_beta2, clip_grad=args.clip_grad,

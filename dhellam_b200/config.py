@@ -83,6 +83,15 @@ class ParallelConfig:
     dp: int = 1
     sequence_parallel: bool = True
 
+    def __post_init__(self):
+        # Like the reference (its layer graph is LN -> all-gather -> GEMM ... GEMM -> reduce-scatter,
+        # dhellam/core/dstb.py:700-757), this engine always shards the activations between
+        # tensor-parallel regions along the sequence.  Tensor parallelism without it is not built,
+        # so asking for it is an error rather than a silently different run.
+        if self.tp > 1 and not self.sequence_parallel:
+            raise ValueError("tensor parallelism here always uses sequence parallelism: pass --sequence-parallel "
+                             "(ParallelConfig(sequence_parallel=True)) when tp > 1")
+
     @property
     def world(self) -> int:
         return self.tp * self.cp * self.pp * self.dp

@@ -472,6 +472,36 @@ def b_ln_attn_bwd(run):
     run.v["dx"] = dx
 
 
+# --------------------------------------------------------------------------- symmetric-buffer effects
+# What each op of the dense layer does to the double-buffered symmetric-memory sites of
+# ``FusedTP`` when the collectives run as their own kernels (the default).  The schedule checker
+# (``sched.checker.check_buffer_reuse``) uses it to prove that no rank can overwrite a slot that
+# another rank still reads; keep it next to the op functions above, which are the ground truth.
+FUSED_BUFFER_EFFECTS = {
+    "allgather_attn": [("push", "attn_c")],
+    "gemm_attn_c": [("wait_read", "attn_c")],
+    "allgather_mlp": [("push", "mlp_c")],
+    "gemm_mlp_c": [("wait_read", "mlp_c")],
+    "gemm_attn_l": [("write", "attn_l")],
+    "reduce_scatter_attn": [("reduce", "attn_l")],
+    "gemm_mlp_l": [("write", "mlp_l")],
+    "reduce_scatter_mlp": [("reduce", "mlp_l")],
+    "bda_mlp_bwd": [("push_s3", "regather_mlp"), ("push_s3", "regather_attn")],
+    "allgather_mlp_bwd": [("push", "mlp_l_bwd")],
+    "gemm_dgrad_mlp_l": [("wait_read", "mlp_l_bwd")],
+    "gemm_wgrad_mlp_l": [("read", "mlp_l_bwd")],
+    "gemm_dgrad_mlp_c": [("write", "mlp_c_bwd")],
+    "gemm_wgrad_mlp_c": [("wait_read", "regather_mlp")],
+    "reduce_scatter_mlp_c_bwd": [("reduce", "mlp_c_bwd")],
+    "allgather_attn_bwd": [("push", "attn_l_bwd")],
+    "gemm_dgrad_attn_l": [("wait_read", "attn_l_bwd")],
+    "gemm_wgrad_attn_l": [("read", "attn_l_bwd")],
+    "gemm_dgrad_attn_c": [("write", "attn_c_bwd")],
+    "gemm_wgrad_attn_c": [("wait_read", "regather_attn")],
+    "reduce_scatter_attn_c_bwd": [("reduce", "attn_c_bwd")],
+}
+
+
 # --------------------------------------------------------------------------- program builder
 def _id(name: str) -> int:
     return OP_TABLE_IDX.get(name, -1)

@@ -237,9 +237,16 @@ class MixedPrecisionAdam:
             if overflow:
                 self.skipped_steps += 1
                 return norm * (1.0 / used)
+        # host read: one scalar per step, after the last backward.  A non-finite norm (an overflow or a
+        # NaN somewhere in the gradients) must not reach the update: inf gives clip = 0 and inf * 0 = NaN
+        # would be written into the master weights and both moments for good.  The step is skipped and
+        # counted, whichever scaler is in use (the dynamic scaler above has already returned).
+        norm_val = float(norm) * scale
+        if not math.isfinite(norm_val):
+            self.skipped_steps += 1
+            return norm * scale_of_norm
         if tr.clip_grad and tr.clip_grad > 0:
-            clip = torch.clamp(tr.clip_grad / (norm * scale + 1e-6), max=1.0)
-            scale = float(clip) * scale     # host read: one scalar per step, after the last backward
+            scale = min(tr.clip_grad / (norm_val + 1e-6), 1.0) * scale
         self.step_count += 1
         lr = tr.lr if lr is None else lr
         flat_p, flat_g = self.model.flat_param, self.model.flat_grad

@@ -77,7 +77,11 @@ class Heartbeat:
         self._paused.clear()
 
     def stop(self):
+        """Ends the beating thread and waits for it, so that no store call is in flight when the
+        caller tears the process group (and with it the store) down."""
         self._stop.set()
+        if self._thread.is_alive() and threading.current_thread() is not self._thread:
+            self._thread.join(timeout=5.0)
 
     def dead_ranks(self) -> List[int]:
         now = time.time()

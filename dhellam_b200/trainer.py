@@ -57,6 +57,14 @@ class Trainer:
             strategy = Strategy.load(train.schedule_config)
         self.engine = DoubleStrandEngine(self.model, self.env, strategy, single_stream=single_stream or not train.dhellam,
                                          profile=profile, trace=trace, compute_streams=train.compute_streams)
+        if self.env.fused_tp and not cfg.is_moe and self.ps.cp == 1:
+            # The symmetric staging slots are reused every second call; prove for THIS strategy (built in,
+            # searched or user-written) and stream count that no rank can overwrite a slot another rank
+            # still reads.  A strategy that fails is refused instead of producing silently wrong gradients.
+            from .models.transformer import FUSED_BUFFER_EFFECTS
+            from .sched.checker import check_buffer_reuse
+            check_buffer_reuse(self.engine.program, self.engine.executor.strategy, FUSED_BUFFER_EFFECTS,
+                               compute_streams=1 if (single_stream or not train.dhellam) else train.compute_streams)
         self.optimizer = MixedPrecisionAdam(self.model, train, self.ps, distributed=distributed_optimizer)
         if self.ps.dp * self.ps.cp > 1 and not distributed_optimizer:
             from .parallel.dp import OverlappedGradReducer
@@ -66,6 +74,12 @@ class Trainer:
         GLOBAL_VARIABLES["loss_scale_func"] = self.optimizer.scale_loss
         self.iteration = 0
         self.last_grad_norm = None
+        # True: synchronise after the forward-backward pass and read the device status word, so that
+        # a bounded device-side wait that gave up (its kernel returned early and left an output
+        # unwritten) raises ``CommTimeout`` BEFORE the optimizer folds that garbage into the master
+        # weights.  Costs one device synchronisation per step; train.py turns it on (it synchronises
+        # every step anyway), the benchmark leaves it off.
+        self.check_status = False
 
     def train_step(self, mbs: List[MicroBatch], lr: Optional[float] = None):
         """One optimizer step over ``mbs``.  Returns the mean loss as a tensor on the first
@@ -73,6 +87,9 @@ class Trainer:
         self.optimizer.zero_grad()
         self.engine.loss_scale = self.optimizer.loss_scale
         losses = self.engine.run_step(mbs)
+        if self.check_status and self.device.type == "cuda":
+            from .runtime.signals import check_device_status
+            check_device_status()
         self.last_grad_norm = self.optimizer.step(lr)
         self.iteration += 1
         if losses:

@@ -21,6 +21,7 @@ def _dead_rank(rank, world):
         time.sleep(2.0)
         hb.resume()
         gate.announce(10**6)                 # let the survivors' final barrier in the harness pass
+        hb.stop()
         return
     t0 = time.time()
     with pytest.raises(RankFailure) as ei:
@@ -28,6 +29,7 @@ def _dead_rank(rank, world):
     assert ei.value.ranks == [world - 1]
     assert time.time() - t0 < 2.5
     time.sleep(1.5)
+    hb.stop()
 
 
 def test_rank_that_stops_between_steps_is_detected_before_the_next_launch():
@@ -41,11 +43,13 @@ def _late_rank(rank, world):
     if rank == 1:
         time.sleep(1.2)                      # alive (heartbeat runs) but far too late
         gate.announce(0)
+        hb.stop()
         return
     with pytest.raises(RankFailure) as ei:
         gate.agree(0)
     assert ei.value.ranks == [1] and "within" in str(ei.value)
     time.sleep(1.0)
+    hb.stop()
 
 
 def test_delayed_rank_times_out_with_a_typed_error():
@@ -104,6 +108,7 @@ def _exception_rank(rank, world, path):
         torch.save(losses, path + "/losses.pt")
     time.sleep(1.5)
     hb.resume()
+    hb.stop()
 
 
 def _resume_rank(rank, world, path):
@@ -139,3 +144,29 @@ def _never_joins(rank, world):
 
 def test_rank_that_never_joins_is_reported():
     run_ranks(_never_joins, 2)
+
+
+def test_train_loop_stops_before_the_next_launch_and_saves_nothing_after_a_host_failure(tmp_path):
+    """``train.py`` on two CPU ranks: rank 1 stops beating and hangs on the host at step 1 (a
+    host-made failure, no GPU involved).  Rank 0 must raise ``RankFailure`` from the step gate
+    before launching step 1, and no checkpoint newer than step 1's predecessor may exist."""
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, PYTHONPATH=root, DHELLAM_INJECT_HOST_FAILURE="1:1:6")
+    save = tmp_path / "ck"
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr", "127.0.0.1",
+           "--master-port", "29541", os.path.join(root, "train.py"),
+           "--num-layers", "2", "--hidden-size", "64", "--ffn-hidden-size", "128", "--num-attention-heads", "4",
+           "--group-query-attention", "--num-query-groups", "2", "--seq-length", "32", "--vocab-size", "128", "--swiglu",
+           "--micro-batch-size", "1", "--global-batch-size", "2", "--lr", "1e-3", "--dhellam",
+           "--tensor-model-parallel-size", "2", "--sequence-parallel", "--train-iters", "3",
+           "--save", str(save), "--save-interval", "1",
+           "--step-gate-timeout", "3", "--heartbeat-interval", "0.1", "--heartbeat-timeout", "1.0"]
+    p = subprocess.run(cmd, cwd=str(tmp_path), env=env, capture_output=True, text=True, timeout=600)
+    assert p.returncode != 0
+    assert "RankFailure" in p.stderr and "[1]" in p.stderr, p.stderr[-3000:]
+    assert (save / "iter_0000001").exists()
+    assert not (save / "iter_0000002").exists() and not (save / "iter_0000003").exists()
+    assert (save / "latest_checkpointed_iteration.txt").read_text() == "1"

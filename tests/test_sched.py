@@ -141,3 +141,35 @@ def test_checker_catches_missing_wait_and_accepts_the_fix():
     bad = [Launch("ln", "S1"), Launch("ag", "S3", ("ln",), ("ln",)), Launch("wgrad", "S2", (), ("ag",))]
     with pytest.raises(RaceError):
         check_trace(bad)
+
+
+def test_buffer_reuse_checker_accepts_builtin_and_rejects_single_slot():
+    """Cross-rank write-after-read on the double-buffered symmetric slots: the built-in schedules
+    are safe with two slots for one and two compute streams; with one slot the carried QKV weight
+    gradient (which reads its re-gathered operand one layer run late) is caught."""
+    from dhellam_b200.config import preset
+    from dhellam_b200.models.transformer import FUSED_BUFFER_EFFECTS, build_layer_program
+    from dhellam_b200.sched.checker import RaceError, check_buffer_reuse
+    from dhellam_b200.sched.strategy import Strategy
+    P = build_layer_program(preset("tiny-llama"))
+    for cs in (1, 2):
+        assert check_buffer_reuse(P, Strategy(), FUSED_BUFFER_EFFECTS, compute_streams=cs)
+    with pytest.raises(RaceError) as ei:
+        check_buffer_reuse(P, Strategy(), FUSED_BUFFER_EFFECTS, compute_streams=1, slots=1)
+    assert "regather_attn" in str(ei.value) and "gemm_wgrad_attn_c" in str(ei.value)
+
+
+def test_buffer_reuse_checker_replays_carried_ops_in_the_run_that_executes_them():
+    from dhellam_b200.config import preset
+    from dhellam_b200.models.transformer import FUSED_BUFFER_EFFECTS, build_layer_program
+    from dhellam_b200.sched.checker import launches_of_runs
+    from dhellam_b200.sched.strategy import Strategy
+    P = build_layer_program(preset("tiny-llama"))
+    strat = Strategy().completed(P)
+    launches, notes = launches_of_runs(P, strat, ("pair", "pair"), 1, FUSED_BUFFER_EFFECTS)
+    names = [l.op for l in launches]
+    # the QKV weight gradient of run 0 executes inside run 1, after run 1 started and before run 1's own
+    i = names.index("gemm_wgrad_attn_c#0")
+    assert names.index("bda_mlp_bwd#1") < i < names.index("gemm_wgrad_attn_c#1")
+    # and it waits on events of run 0's producers, not run 1's
+    assert all(w.endswith("#0") for w in launches[i].waits)

@@ -70,7 +70,56 @@ def main(argv=None):
         dataset = TokenFileDataset(path, cfg.seq_length, dt or "int32", seed=train.seed)
         print_rank0(f"data: {path} ({len(dataset)} samples of {cfg.seq_length + 1} tokens)")
     tr.engine.time_pp = pcfg.pp > 1 and args.timing_log_level >= 2
+    # Failure detection between steps: every rank beats on the rendezvous store and announces the
+    # step it is about to launch; a rank that stopped is noticed on the host BEFORE the next launch.
+    # After the step (the loop synchronises anyway) the device status word is read: a bounded wait
+    # that gave up inside a kernel raises here, before the optimizer touched the master weights
+    # (Trainer.check_status) and before any checkpoint is written.
+    hb = gate = None
+    if dist.is_initialized() and dist.get_world_size() > 1 and args.step_gate_timeout > 0:
+        from dhellam_b200.runtime.watchdog import Heartbeat, StepGate
+        hb = Heartbeat(interval=args.heartbeat_interval, timeout=args.heartbeat_timeout)
+        gate = StepGate(timeout=args.step_gate_timeout, heartbeat=hb)
+    tr.check_status = cuda
+    inject = _parse_injection(os.environ.get("DHELLAM_INJECT_HOST_FAILURE"))
+    try:
+        _loop(args, tr, train, cfg, pcfg, dataset, device, cuda, start, ml, hb, gate, inject)
+    finally:
+        if hb is not None:
+            hb.stop()
+    if train.save:
+        save_checkpoint(train.save, train.train_iters, tr.model, tr.optimizer)
+    ml.close()
+    if dist.is_initialized():
+        dist.barrier()
+        dist.destroy_process_group()
+    return 0
+
+
+def _parse_injection(spec):
+    """``DHELLAM_INJECT_HOST_FAILURE=<rank>:<step>:<seconds>`` makes that rank stop beating and
+    sleep on the host at that step, then exit with an error (a test hook; nothing on a GPU is
+    faulted)."""
+    if not spec:
+        return None
+    r, s, sec = spec.split(":")
+    return int(r), int(s), float(sec)
+
+
+def _loop(args, tr, train, cfg, pcfg, dataset, device, cuda, start, ml, hb, gate, inject):
+    import torch
+    import torch.distributed as dist
+    from dhellam_b200.ckpt import save_checkpoint
+    from dhellam_b200.common import print_rank0
+    from dhellam_b200.data import file_step_batches, synthetic_step_batches
     for it in range(start, train.train_iters):
+        if inject is not None and inject[0] == args.rank and inject[1] == it:
+            if hb is not None:
+                hb.pause()
+            time.sleep(inject[2])
+            raise RuntimeError(f"injected host failure on rank {args.rank} at step {it}")
+        if gate is not None:
+            gate.agree(it)                 # raises RankFailure: nothing of step `it` is launched, nothing is saved
         mbs = (file_step_batches(dataset, cfg, train, tr.ps, it, device) if dataset is not None
                else synthetic_step_batches(cfg, train, tr.ps, it, device))
         if cuda:
@@ -93,16 +142,6 @@ def main(argv=None):
                         f"(TFLOP/s/GPU): {rec['model_tflops_per_gpu']:.1f} | tokens/s/GPU: {rec['tokens_per_s_per_gpu']:.0f}")
         if train.save and (it + 1) % train.save_interval == 0:
             save_checkpoint(train.save, it + 1, tr.model, tr.optimizer, {k: v for k, v in vars(args).items() if isinstance(v, (int, float, str, bool, type(None)))})
-    if train.save:
-        save_checkpoint(train.save, train.train_iters, tr.model, tr.optimizer)
-    if cuda:
-        from dhellam_b200.runtime.signals import check_device_status
-        check_device_status()
-    ml.close()
-    if dist.is_initialized():
-        dist.barrier()
-        dist.destroy_process_group()
-    return 0
 
 
 if __name__ == "__main__":
