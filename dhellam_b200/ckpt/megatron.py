@@ -1,13 +1,21 @@
 """Checkpoints in the Megatron distributed-checkpoint layout, with the fold map.
 
-Directory layout (Megatron-core ``dist_checkpointing``)::
+Directory layout (Megatron-core ``dist_checkpointing`` with the ``torch_dist`` backend)::
 
     <save>/latest_checkpointed_iteration.txt
     <save>/iter_0000010/metadata.json      sharded_backend / common_backend descriptors
-    <save>/iter_0000010/common.pt          iteration, arguments, RNG, optimizer step
-    <save>/iter_0000010/.metadata          index: key -> global shape and the pieces that tile it
-    <save>/iter_0000010/__{rank}_0.distcp  the pieces written by one rank
-    <save>/iter_0000010/optim_{rank}.pt    this rank's optimizer shard (same parallel layout on resume)
+    <save>/iter_0000010/common.pt          iteration, arguments, RNG of rank 0, optimizer step
+    <save>/iter_0000010/.metadata          ``torch.distributed.checkpoint`` metadata (pickled ``Metadata``:
+                                           key -> global size, dtype and the chunks that tile it)
+    <save>/iter_0000010/__{rank}_0.distcp  the chunks written by one rank, in the format of
+                                           ``torch.distributed.checkpoint.FileSystemWriter``
+    <save>/iter_0000010/optim_{rank}.pt    this rank's optimizer shard + its CPU / CUDA RNG state
+                                           (a ``torch.save`` file; same parallel layout on resume)
+
+The weight files are genuine ``torch.distributed.checkpoint`` (DCP) files: they are written by
+``dcp.save`` through a planner that emits one write item per tensor-parallel piece, so
+``dcp.load`` (and therefore Megatron-core's ``torch_dist`` reader, which is built on it) can
+open them under the canonical keys below.
 
 Tensors are stored under Megatron-core's canonical GPT keys
 (``decoder.layers.{i}.self_attention.linear_qkv.weight`` ...), indexed by the *model* layer,
@@ -145,6 +153,37 @@ def _iter_dir(root: str, iteration: int) -> str:
     return os.path.join(root, f"iter_{iteration:07d}")
 
 
+def _dcp_save(d: str, pieces):
+    """Writes ``pieces`` = ``[(key, global shape, offsets, cpu tensor)]`` of this rank as
+    ``torch.distributed.checkpoint`` files.  Every rank of the job calls it (ranks without
+    pieces take part in the planning collectives with an empty plan); the coordinator writes
+    ``.metadata`` with, per key, the global size and all ranks' chunks."""
+    import torch.distributed.checkpoint as dcp
+    from torch.distributed.checkpoint import DefaultSavePlanner, FileSystemWriter
+    from torch.distributed.checkpoint.metadata import ChunkStorageMetadata, MetadataIndex, TensorProperties
+    from torch.distributed.checkpoint.planner import SavePlan, TensorWriteData, WriteItem, WriteItemType
+
+    table = {(k, offs): t for k, _, offs, t in pieces}
+
+    class PiecePlanner(DefaultSavePlanner):
+        def create_local_plan(self):
+            items = []
+            for k, gshape, offs, t in pieces:
+                chunk = ChunkStorageMetadata(offsets=torch.Size(offs), sizes=t.size())
+                items.append(WriteItem(index=MetadataIndex(k, torch.Size(offs)), type=WriteItemType.SHARD,
+                                       tensor_data=TensorWriteData(chunk=chunk, properties=TensorProperties.create_from_tensor(t),
+                                                                   size=torch.Size(gshape))))
+            self.plan = SavePlan(items, planner_data=dict(getattr(self, "mappings", None) or {}))
+            return self.plan
+
+        def resolve_data(self, write_item):
+            return table[(write_item.index.fqn, tuple(write_item.index.offset))]
+
+    no_dist = not (dist.is_initialized() and dist.get_world_size() > 1)
+    dcp.save({}, storage_writer=FileSystemWriter(d, single_file_per_rank=True, sync_files=False),
+             planner=PiecePlanner(), no_dist=no_dist)
+
+
 def save_checkpoint(save_dir: str, iteration: int, model, optimizer=None, args: Optional[dict] = None):
     """Writes one checkpoint.  Every rank calls this; ranks that hold a data-parallel or
     context-parallel replica of the weights write nothing but their optimizer shard."""
@@ -155,44 +194,25 @@ def save_checkpoint(save_dir: str, iteration: int, model, optimizer=None, args: 
     os.makedirs(d, exist_ok=True)
     # data-parallel rank 0 writes the dense weights; the first `ep` data-parallel ranks each write their experts
     weight_writer = ps.dp_rank < max(ps.ep, 1) and ps.cp_rank == 0
-    index = {}
-    blob = {}
+    pieces = []                        # (key, global shape, offsets, tensor)
     if weight_writer:
         dense_writer = ps.dp_rank == 0
-        n = 0
-        for key, gshape, pieces, writer in canonical_items(model):
+        for key, gshape, pcs, writer in canonical_items(model):
             is_expert = ".experts.local_experts." in key
             if not writer or (not is_expert and not dense_writer):
                 continue
-            for offs, t in pieces:
-                name = f"{key}#{n}"
-                n += 1
-                blob[name] = t.detach().to("cpu").clone()
-                index.setdefault(key, {"shape": gshape, "dtype": str(t.dtype), "pieces": []})["pieces"].append(
-                    {"file": f"__{rank}_0.distcp", "entry": name, "offsets": list(offs), "lengths": list(t.shape)})
-    torch.save(blob, os.path.join(d, f"__{rank}_0.distcp"))
+            for offs, t in pcs:
+                pieces.append((key, tuple(gshape), tuple(offs), t.detach().to("cpu").contiguous()))
+    _dcp_save(d, pieces)
     if optimizer is not None:
-        torch.save({k: (v.cpu() if torch.is_tensor(v) else v) for k, v in optimizer.state_dict().items()},
-                   os.path.join(d, f"optim_{rank}.pt"))
-    # merge the per-rank indices on rank 0
-    if dist.is_initialized() and world > 1:
-        gathered = [None] * world
-        dist.all_gather_object(gathered, index)
-    else:
-        gathered = [index]
+        osd = {k: (v.cpu() if torch.is_tensor(v) else v) for k, v in optimizer.state_dict().items()}
+        osd["rng_state"] = {"cpu": torch.get_rng_state(),
+                            "cuda": torch.cuda.get_rng_state() if torch.cuda.is_available() else None}
+        torch.save(osd, os.path.join(d, f"optim_{rank}.pt"))
     if rank == 0:
-        merged: Dict[str, dict] = {}
-        for part in gathered:
-            for key, ent in part.items():
-                if key in merged:
-                    merged[key]["pieces"].extend(ent["pieces"])
-                else:
-                    merged[key] = ent
-        with open(os.path.join(d, ".metadata"), "w") as fp:
-            json.dump({"tensors": merged}, fp)
         with open(os.path.join(d, "metadata.json"), "w") as fp:
             json.dump({"sharded_backend": "torch_dist", "sharded_backend_version": 1, "common_backend": "torch",
-                       "common_backend_version": 1, "writer": "dhellam_b200", "piece_format": "torch.save per rank"}, fp)
+                       "common_backend_version": 1, "writer": "dhellam_b200"}, fp)
         common = {"iteration": iteration, "args": args or {}, "model_config": to_dict(model.cfg),
                   "parallel": {"tp": ps.tp, "pp": ps.pp, "cp": ps.cp, "dp": ps.dp, "ep": ps.ep},
                   "fold_map": {f"{p}.{j}.{w}": l for (p, j, w), l in fold_map(model.cfg.num_layers, ps.pp).items()},
@@ -215,30 +235,28 @@ def read_latest_iteration(load_dir: str) -> Optional[int]:
 
 
 class _Reader:
-    def __init__(self, d: str):
-        self.d = d
-        with open(os.path.join(d, ".metadata")) as fp:
-            self.index = json.load(fp)["tensors"]
-        self._files = {}
+    """Reads whole tensors out of a DCP checkpoint directory (each rank reads for itself)."""
 
-    def _file(self, name):
-        if name not in self._files:
-            self._files[name] = torch.load(os.path.join(self.d, name), map_location="cpu")
-        return self._files[name]
+    def __init__(self, d: str):
+        from torch.distributed.checkpoint import FileSystemReader
+        self.d = d
+        self.meta = FileSystemReader(d).read_metadata()
+        self.index = {k: v for k, v in self.meta.state_dict_metadata.items() if hasattr(v, "chunks")}
+
+    def shape(self, key: str):
+        return list(self.index[key].size)
 
     def full(self, key: str) -> torch.Tensor:
-        """Assembles the whole tensor of ``key`` from its pieces."""
-        ent = self.index[key]
-        first = self._file(ent["pieces"][0]["file"])[ent["pieces"][0]["entry"]]
-        out = torch.zeros(ent["shape"], dtype=first.dtype)
-        covered = 0
-        for pc in ent["pieces"]:
-            t = self._file(pc["file"])[pc["entry"]]
-            sl = tuple(slice(o, o + l) for o, l in zip(pc["offsets"], pc["lengths"]))
-            out[sl] = t
-            covered += t.numel()
-        assert covered == out.numel(), f"pieces of {key} do not tile its shape {ent['shape']}"
-        return out
+        """Assembles the whole tensor of ``key`` from its chunks."""
+        return self.full_many([key])[key]
+
+    def full_many(self, keys) -> Dict[str, torch.Tensor]:
+        import torch.distributed.checkpoint as dcp
+        from torch.distributed.checkpoint import FileSystemReader
+        sd = {k: torch.empty(tuple(self.index[k].size), dtype=self.index[k].properties.dtype) for k in keys}
+        if sd:
+            dcp.load(sd, storage_reader=FileSystemReader(self.d), no_dist=True)
+        return sd
 
 
 def load_checkpoint(load_dir: str, model, optimizer=None, iteration: Optional[int] = None, strict: bool = True) -> int:
@@ -254,21 +272,22 @@ def load_checkpoint(load_dir: str, model, optimizer=None, iteration: Optional[in
     cfg, ps = model.cfg, model.ps
     # canonical (Megatron) full tensors -> this framework's full layout -> this rank's shards
     def full_layer(idx):
+        want = {base: f"decoder.layers.{idx}.{sub}" for base, sub in LAYER_KEYS.items() if f"decoder.layers.{idx}.{sub}" in rd.index}
+        ekeys = []
+        if cfg.is_moe:
+            for e in range(cfg.num_experts):
+                ekeys += [f"decoder.layers.{idx}.mlp.experts.local_experts.{e}.linear_fc1.weight",
+                          f"decoder.layers.{idx}.mlp.experts.local_experts.{e}.linear_fc2.weight"]
+        got = rd.full_many(list(want.values()) + ekeys)
         full = {}
-        for base, sub in LAYER_KEYS.items():
-            key = f"decoder.layers.{idx}.{sub}"
-            if key not in rd.index:
-                continue
-            t = rd.full(key)
+        for base, key in want.items():
+            t = got[key]
             if base == "column_attn_weight":
                 t = qkv_megatron_to_shard(t, cfg, 1)
             full[base] = t
         if cfg.is_moe:
-            c, l = [], []
-            for e in range(cfg.num_experts):
-                c.append(rd.full(f"decoder.layers.{idx}.mlp.experts.local_experts.{e}.linear_fc1.weight"))
-                l.append(rd.full(f"decoder.layers.{idx}.mlp.experts.local_experts.{e}.linear_fc2.weight"))
-            full["expert_column_weight"], full["expert_linear_weight"] = torch.stack(c), torch.stack(l)
+            full["expert_column_weight"] = torch.stack([got[k] for k in ekeys[0::2]])
+            full["expert_linear_weight"] = torch.stack([got[k] for k in ekeys[1::2]])
         return full
     for m in model.dctb:
         for which, idx in (("first", m.first_index), ("second", m.second_index)):
@@ -281,8 +300,9 @@ def load_checkpoint(load_dir: str, model, optimizer=None, iteration: Optional[in
                         continue
                     getattr(m, f"{base}_{which}").copy_(shards[base].to(model.dtype))
     if model.dchb is not None:
-        full = {base: rd.full(key) for base, key in HEAD_KEYS.items() if key in rd.index}
-        shards = shard_head(full, cfg, ps.tp, ps.tp_rank)
+        want = {base: key for base, key in HEAD_KEYS.items() if key in rd.index}
+        got = rd.full_many(list(want.values()))
+        shards = shard_head({base: got[key] for base, key in want.items()}, cfg, ps.tp, ps.tp_rank)
         with torch.no_grad():
             for base in model.dchb.shapes:
                 getattr(model.dchb, base).copy_(shards[base].to(model.dtype))
@@ -293,9 +313,18 @@ def load_checkpoint(load_dir: str, model, optimizer=None, iteration: Optional[in
         p = os.path.join(d, f"optim_{rank}.pt")
         if same and os.path.exists(p):
             sd = torch.load(p, map_location="cpu", weights_only=False)
+            rng = sd.pop("rng_state", None)
             optimizer.load_state_dict({k: (v.to(optimizer.master.device) if torch.is_tensor(v) else v) for k, v in sd.items()})
+            if rng is not None:                   # every rank continues its own random streams
+                torch.set_rng_state(rng["cpu"])
+                if rng.get("cuda") is not None and torch.cuda.is_available():
+                    torch.cuda.set_rng_state(rng["cuda"])
         else:
             # different layout: moments restart, master weights follow the loaded parameters
+            import warnings
+            warnings.warn(f"checkpoint {d} was written with parallel layout {common['parallel']}, this run uses "
+                          f"tp={ps.tp} pp={ps.pp} cp={ps.cp} dp={ps.dp} ep={ps.ep}: weights were re-sharded, but the Adam "
+                          "moments restart from zero (the optimizer shards are only reloadable in the layout that wrote them)")
             optimizer.master.copy_(model.flat_param[optimizer.lo:optimizer.hi].float())
             optimizer.step_count = int(common.get("optimizer_step", 0))
     return int(common["iteration"])

@@ -60,6 +60,12 @@ def run_execute(h: LayerHarness, config_dir: str, out_path: str = "config/best.j
     for name, strat in candidates:
         try:
             strat = strat if strat is not None else Strategy.load(name)
+            if h.env.fused is not None and not h.cfg.is_moe and h.ps.cp == 1:
+                # a candidate whose launch order lets a rank overwrite a symmetric slot that another
+                # rank still reads is illegal however fast it is
+                from ..models.transformer import FUSED_BUFFER_EFFECTS
+                from ..sched.checker import check_buffer_reuse
+                check_buffer_reuse(h.program, strat, FUSED_BUFFER_EFFECTS, compute_streams=1 if h.streams.s2 is h.streams.s1 else 2)
             seq, par = time_strategy(h, strat, repeat)
         except Exception as e:                      # an illegal candidate is skipped, not fatal
             print_rank0(f"skip {name}: {e}")

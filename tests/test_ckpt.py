@@ -59,13 +59,22 @@ def test_save_tp2_pp2_load_single_rank_reshards(tmp_path):
         assert os.path.exists(os.path.join(d, f)), f
     meta = json.load(open(os.path.join(d, "metadata.json")))
     assert meta["sharded_backend"] == "torch_dist"
-    idx = json.load(open(os.path.join(d, ".metadata")))["tensors"]
+    # the weight files are real torch.distributed.checkpoint files: any DCP reader opens them
+    import torch.distributed.checkpoint as dcp
+    from torch.distributed.checkpoint import FileSystemReader
+    idx = FileSystemReader(d).read_metadata().state_dict_metadata
     for key in ("embedding.word_embeddings.weight", "decoder.final_layernorm.weight",
                 "decoder.layers.0.self_attention.linear_qkv.weight", "decoder.layers.3.mlp.linear_fc2.weight",
                 "decoder.layers.2.self_attention.linear_qkv.layer_norm_weight"):
         assert key in idx, key
     cfg = preset("tiny-llama", num_layers=4, seq_length=32)
-    assert idx["decoder.layers.1.mlp.linear_fc1.weight"]["shape"] == [2 * cfg.ffn_hidden_size, cfg.hidden_size]
+    assert list(idx["decoder.layers.1.mlp.linear_fc1.weight"].size) == [2 * cfg.ffn_hidden_size, cfg.hidden_size]
+    assert len(idx["decoder.layers.1.mlp.linear_fc1.weight"].chunks) == 4          # gate and up halves of two TP ranks
+    sd = {"decoder.layers.3.mlp.linear_fc2.weight": torch.empty(cfg.hidden_size, cfg.ffn_hidden_size),
+          "decoder.final_layernorm.weight": torch.empty(cfg.hidden_size)}
+    dcp.load(sd, checkpoint_id=d, no_dist=True)
+    assert torch.equal(sd["decoder.layers.3.mlp.linear_fc2.weight"], random_full_layer(cfg, 3, 21)["linear_mlp_weight"])
+    assert torch.equal(sd["decoder.final_layernorm.weight"], random_full_head(cfg, 21)["final_ln_weight"])
     PS.set_state(None)
     tr = Trainer(cfg, ParallelConfig(), TrainConfig(micro_batch_size=1, global_batch_size=2, dtype="fp32"), device="cpu")
     it = load_checkpoint(path, tr.model, tr.optimizer)
