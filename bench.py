@@ -242,8 +242,11 @@ def main():
                        "heads": cfg.num_attention_heads, "kv_heads": cfg.num_query_groups, "vocab": cfg.vocab_size,
                        "global_batch": args.global_batch, "micro_batch": mbs, "seq_len": cfg.seq_length,
                        "parallelism": f"tp{N}+sp" if N > 1 else "single", "optimizer": "adam, fp32 master + fp32 main_grad",
-                       "fused_comm": bool(tr.env.fused_tp),
-                       "fused_policy": (tr.env.fused.policy if tr.env.fused_tp else None), "dual_strand": train.dhellam, "compute_streams": train.compute_streams,
+                       # how the tensor-parallel collectives run: "fused" = inside the GEMM kernels, "split" = own
+                       # peer-memory kernels on the communication stream beside plain GEMMs, "nccl" = library calls
+                       "tp_collectives": (None if N == 1 else (("fused" if tr.env.fused.policy == "fused" else
+                                                                tr.env.fused.policy) if tr.env.fused_tp else "nccl")),
+                       "dual_strand": train.dhellam, "compute_streams": train.compute_streams,
                        "l2": "working set per step (weights + activations, tens of GB) is far larger than the 126 MB L2"},
             "clocks": clocks, "e2e": e2e, "gpu_launches": launches,
             "peak_mem_gib": round(torch.cuda.max_memory_allocated() / 2**30, 1),

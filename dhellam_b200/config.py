@@ -138,6 +138,7 @@ class TrainConfig:
     loss_scale_window: int = 1000
     hysteresis: int = 2
     min_loss_scale: float = 1.0
+    label_smoothing: float = 0.0         # Megatron's --label-smoothing-factor
 
     def num_microbatches(self, dp: int) -> int:
         assert self.global_batch_size % (self.micro_batch_size * dp) == 0, "global batch must divide by micro-batch x dp"

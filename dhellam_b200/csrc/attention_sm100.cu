@@ -33,6 +33,7 @@
 #include <stdint.h>
 
 #include <cstdlib>
+#include <mutex>
 
 #include "api.h"
 #include "ptx.cuh"
@@ -1080,7 +1081,8 @@ int dh_attn_fwd(const void* q, const void* k, const void* v, void* out, void* ls
   const CUtensorMap* tk = tensor_map_sbhd(k, Sk, B, Hk, k_s, k_b, k_h);
   const CUtensorMap* tv = tensor_map_sbhd(v, Sk, B, Hk, v_s, v_b, v_h);
   if (!tq || !tk || !tv) return (int)cudaErrorInvalidValue;
-  static bool configured = false;
+  static PerDeviceFlags configured_on;
+  bool& configured = device_flag(configured_on);
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, FWD_SMEM);
     if (e != cudaSuccess) { set_last_error("dh_attn_fwd: shared memory opt-in failed: %s", cudaGetErrorString(e)); return (int)e; }
@@ -1139,7 +1141,8 @@ int dh_attn_bwd(const void* dout, const void* q, const void* k, const void* v, c
   const CUtensorMap* tv = tensor_map_sbhd(v, Sk, B, Hk, sv[0], sv[1], sv[2]);
   const CUtensorMap* tdo = tensor_map_sbhd(dout, Sq, B, Hq, sdo[0], sdo[1], sdo[2]);
   if (!tq || !tk || !tv || !tdo) return (int)cudaErrorInvalidValue;
-  static bool configured = false;
+  static PerDeviceFlags configured_on;
+  bool& configured = device_flag(configured_on);
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(attn_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, BWD_SMEM);
     if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_bwd_dq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, DQ_SMEM);
@@ -1147,8 +1150,13 @@ int dh_attn_bwd(const void* dout, const void* q, const void* k, const void* v, c
     configured = true;
   }
   float* delta = reinterpret_cast<float*>(scratch);
-  const int rows = B * Hq * Sq;
-  attn_delta_kernel<<<(rows * 32 + 255) / 256, 256, 0, stream>>>((const __nv_bfloat16*)dout, (const __nv_bfloat16*)out, delta, B, Hq, Sq,
+  const long long rows_ll = (long long)B * Hq * Sq;
+  if (rows_ll > (1ll << 26)) {     // the delta grid (one warp per row) and the int row index stay well inside 32 bits
+    set_last_error("dh_attn_bwd: B*Hq*Sq = %lld rows exceed the supported 2^26", rows_ll);
+    return (int)cudaErrorInvalidValue;
+  }
+  const int rows = (int)rows_ll;
+  attn_delta_kernel<<<(unsigned)((rows_ll * 32 + 255) / 256), 256, 0, stream>>>((const __nv_bfloat16*)dout, (const __nv_bfloat16*)out, delta, B, Hq, Sq,
                                                                  sdo[0], sdo[1], sdo[2], so[0], so[1], so[2]);
   DeviceStatus* st = reinterpret_cast<DeviceStatus*>(dh_status_device_ptr());
   BwdGeometry g;
@@ -1166,7 +1174,8 @@ int dh_attn_bwd(const void* dout, const void* q, const void* k, const void* v, c
     const CUtensorMap* tq64 = tensor_map_sbhd(q, Sq, B, Hq, sq[0], sq[1], sq[2], BQT);
     const CUtensorMap* tdo64 = tensor_map_sbhd(dout, Sq, B, Hq, sdo[0], sdo[1], sdo[2], BQT);
     if (!tq64 || !tdo64) return (int)cudaErrorInvalidValue;
-    static bool configured_t = false;
+    static PerDeviceFlags configured_t_on;
+    bool& configured_t = device_flag(configured_t_on);
     if (!configured_t) {
       cudaError_t e2 = cudaFuncSetAttribute(attn_bwd_t_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, BWDT_SMEM);
       if (e2 != cudaSuccess) { set_last_error("dh_attn_bwd: shared memory opt-in failed: %s", cudaGetErrorString(e2)); return (int)e2; }
@@ -1212,6 +1221,7 @@ static __device__ __align__(256) unsigned char g_noalloc_scratch[DH_ATTN_NOALLOC
 constexpr int kNoallocMaxDev = 32;
 static void* g_noalloc_addr[kNoallocMaxDev] = {nullptr};
 static bool g_noalloc_ready[kNoallocMaxDev] = {false};
+static std::mutex g_noalloc_mutex;     // two host threads may make the first call on one device at the same time
 
 static bool map_sbhd_into(CUtensorMap* m, const void* p, int S, int B, int H, const int64_t* st) {
   const uint64_t dims[4] = {(uint64_t)D, (uint64_t)H, (uint64_t)B, (uint64_t)S};
@@ -1239,6 +1249,8 @@ extern "C" int dh_attn_bwd_noalloc(const void* dout, const void* q, const void* 
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess || dev < 0 || dev >= kNoallocMaxDev) { set_last_error("dh_attn_bwd_noalloc: no usable current device"); return (int)cudaErrorInvalidDevice; }
+  {
+    std::lock_guard<std::mutex> lock(g_noalloc_mutex);
   if (!g_noalloc_ready[dev]) {
     // once per device, with that device current: resolve the array's device address
     void* ptr = nullptr;
@@ -1249,6 +1261,7 @@ extern "C" int dh_attn_bwd_noalloc(const void* dout, const void* q, const void* 
     if (e != cudaSuccess) { set_last_error("dh_attn_bwd_noalloc: shared memory opt-in failed: %s", cudaGetErrorString(e)); return (int)e; }
     g_noalloc_addr[dev] = ptr;
     g_noalloc_ready[dev] = true;
+  }
   }
   const int64_t* sdo = strides; const int64_t* sq = strides + 3; const int64_t* sk = strides + 6; const int64_t* sv = strides + 9;
   const int64_t* so = strides + 12; const int64_t* sdq = strides + 15; const int64_t* sdk = strides + 18; const int64_t* sdv = strides + 21;

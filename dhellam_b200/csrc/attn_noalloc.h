@@ -24,7 +24,9 @@
 //     dh_last_error_string().  1 MiB covers 262144 rows, for example Sq = 4096, B = 8, Hq = 8.
 //   * The first call on each device resolves the scratch's device address
 //     (cudaGetSymbolAddress, with that device current) and opts the kernels into their
-//     shared-memory size.  Make that first call before any stream capture begins.
+//     shared-memory size.  Make that first call before any stream capture begins.  The set-up
+//     is done under a host mutex, so threads that make their first calls on one device at the
+//     same time are safe; the calls themselves still share the scratch (next rule).
 //   * The function calls no cudaMalloc / cudaFree and no allocating library routine; the TMA
 //     descriptors are built on the caller's stack.
 //   * All calls on a device share the one array and it keeps the last call's contents.

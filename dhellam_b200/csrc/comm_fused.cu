@@ -656,8 +656,8 @@ int dh_ag_gemm_bf16(const void* shard, void* const* stage_ptrs, void* const* cou
   if (copy_ctas <= 0) copy_ctas = 8;
   if (copy_ctas > budget / 2) copy_ctas = budget / 2;
   p.copy_ctas = copy_ctas;
-  static bool c0 = false, c1 = false;
-  rc = b_mn_major ? configure(ag_gemm_kernel<true>, c1) : configure(ag_gemm_kernel<false>, c0);
+  static PerDeviceFlags f0, f1;
+  rc = b_mn_major ? configure(ag_gemm_kernel<true>, device_flag(f1)) : configure(ag_gemm_kernel<false>, device_flag(f0));
   if (rc) return rc;
   if (b_mn_major) ag_gemm_kernel<true><<<budget, THREADS, SMEM_BYTES, stream>>>(*ta, *tb, p);
   else ag_gemm_kernel<false><<<budget, THREADS, SMEM_BYTES, stream>>>(*ta, *tb, p);
@@ -716,8 +716,8 @@ int dh_gemm_rs_bf16(const void* a, int64_t lda, const void* b, int64_t ldb, int 
   int budget = (sm_budget <= 0 || sm_budget > sms) ? sms : sm_budget;
   const int num_tiles = p.tiles_m * p.tiles_n;
   const int grid = num_tiles < budget ? num_tiles : budget;
-  static bool c0 = false, c1 = false;
-  int rc = b_mn_major ? configure(gemm_rs_kernel<true>, c1, RS_SMEM_BYTES) : configure(gemm_rs_kernel<false>, c0, RS_SMEM_BYTES);
+  static PerDeviceFlags f0, f1;
+  int rc = b_mn_major ? configure(gemm_rs_kernel<true>, device_flag(f1), RS_SMEM_BYTES) : configure(gemm_rs_kernel<false>, device_flag(f0), RS_SMEM_BYTES);
   if (rc) return rc;
   if (b_mn_major) gemm_rs_kernel<true><<<grid, THREADS, RS_SMEM_BYTES, stream>>>(*ta, *tb, p);
   else gemm_rs_kernel<false><<<grid, THREADS, RS_SMEM_BYTES, stream>>>(*ta, *tb, p);

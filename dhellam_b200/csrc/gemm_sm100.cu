@@ -271,7 +271,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
 template <bool A_MN, bool B_MN, bool OUT_F32>
 static int launch(const CUtensorMap* ta, const CUtensorMap* tb, const Params& p, int grid, cudaStream_t stream) {
   auto kern = gemm_kernel<A_MN, B_MN, OUT_F32>;
-  static bool configured = false;
+  static PerDeviceFlags configured_on;
+  bool& configured = device_flag(configured_on);
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
     if (e != cudaSuccess) {
@@ -484,7 +485,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 template <bool A_MN, bool B_MN, bool OUT_F32>
 static int launch_pair(const CUtensorMap* ta, const CUtensorMap* tb, const Params& p, int pairs, cudaStream_t stream) {
   auto kern = gemm_pair_kernel<A_MN, B_MN, OUT_F32>;
-  static bool configured = false;
+  static PerDeviceFlags configured_on;
+  bool& configured = device_flag(configured_on);
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM2_BYTES);
     if (e != cudaSuccess) {

@@ -90,13 +90,14 @@ __global__ void __launch_bounds__(HT) embedding_bwd_kernel(const __nv_bfloat16* 
 template <bool F32>
 __global__ void __launch_bounds__(HT) ce_stats_kernel(const void* __restrict__ logits, const int* __restrict__ labels,
                                                       float* __restrict__ stats, int T, int Vl, long long ld, int v0) {
-  __shared__ float sm[32], ss[32];
+  __shared__ float sm[32], ss[32], st[32];
   for (int t = blockIdx.x; t < T; t += gridDim.x) {
-    float m = -FLT_MAX, s = 0.f;
+    float m = -FLT_MAX, s = 0.f, tot = 0.f;      // tot: plain sum of the logits (label smoothing)
     if (F32) {
       const float* row = reinterpret_cast<const float*>(logits) + (size_t)t * ld;
       for (int c = threadIdx.x; c < Vl; c += HT) {
         const float v = row[c];
+        tot += v;
         const float nm = fmaxf(m, v);
         s = s * __expf(m - nm) + __expf(v - nm);
         m = nm;
@@ -113,27 +114,30 @@ __global__ void __launch_bounds__(HT) ce_stats_kernel(const void* __restrict__ l
         const float nm = fmaxf(m, lm);
         float add = 0.f;
 #pragma unroll
-        for (int j = 0; j < 8; ++j) add += __expf(v[j] - nm);
+        for (int j = 0; j < 8; ++j) { add += __expf(v[j] - nm); tot += v[j]; }
         s = s * __expf(m - nm) + add;
         m = nm;
       }
       for (int c = (nvec << 3) + threadIdx.x; c < Vl; c += HT) {
         const float v = __bfloat162float(row[c]);
+        tot += v;
         const float nm = fmaxf(m, v);
         s = s * __expf(m - nm) + __expf(v - nm);
         m = nm;
       }
     }
-    // combine (m, s) over the CTA
+    // combine (m, s, tot) over the CTA
     const float wm = hwarp_max(m);
     s = hwarp_sum(s * __expf(m - wm));
+    tot = hwarp_sum(tot);
     const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
     __syncthreads();
-    if (l == 0) { sm[w] = wm; ss[w] = s; }
+    if (l == 0) { sm[w] = wm; ss[w] = s; st[w] = tot; }
     __syncthreads();
     if (w == 0) {
       float pm = l < (HT >> 5) ? sm[l] : -FLT_MAX;
       float ps = l < (HT >> 5) ? ss[l] : 0.f;
+      const float pt = hwarp_sum(l < (HT >> 5) ? st[l] : 0.f);
       const float gm = hwarp_max(pm);
       ps = hwarp_sum(ps * __expf(pm - gm));
       if (l == 0) {
@@ -143,9 +147,10 @@ __global__ void __launch_bounds__(HT) ce_stats_kernel(const void* __restrict__ l
           tgt = F32 ? reinterpret_cast<const float*>(logits)[(size_t)t * ld + loc]
                     : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(logits)[(size_t)t * ld + loc]);
         }
-        stats[t * 3 + 0] = gm;
-        stats[t * 3 + 1] = ps;
-        stats[t * 3 + 2] = tgt;
+        stats[t * 4 + 0] = gm;
+        stats[t * 4 + 1] = ps;
+        stats[t * 4 + 2] = tgt;
+        stats[t * 4 + 3] = pt;
       }
     }
   }
@@ -153,13 +158,16 @@ __global__ void __launch_bounds__(HT) ce_stats_kernel(const void* __restrict__ l
 
 template <bool F32>
 __global__ void __launch_bounds__(HT) ce_grad_kernel(void* __restrict__ logits, const int* __restrict__ labels, const float* __restrict__ lse,
-                                                     const float* __restrict__ gtok, int T, int Vl, long long ld, int v0) {
+                                                     const float* __restrict__ gtok, int T, int Vl, long long ld, int v0,
+                                                     float tcoef, float ucoef) {
+  // d loss / d logit = softmax - tcoef * onehot(target) - ucoef; plain cross-entropy has tcoef = 1, ucoef = 0,
+  // label smoothing s over V classes has tcoef = 1 - s', ucoef = s' / V with s' = s V / (V - 1).
   for (int t = blockIdx.x; t < T; t += gridDim.x) {
     const float L = lse[t], g = gtok[t];
     const int loc = labels[t] - v0;
     if (F32) {
       float* row = reinterpret_cast<float*>(logits) + (size_t)t * ld;
-      for (int c = threadIdx.x; c < Vl; c += HT) row[c] = (__expf(row[c] - L) - (c == loc ? 1.f : 0.f)) * g;
+      for (int c = threadIdx.x; c < Vl; c += HT) row[c] = (__expf(row[c] - L) - (c == loc ? tcoef : 0.f) - ucoef) * g;
     } else {
       __nv_bfloat16* row = reinterpret_cast<__nv_bfloat16*>(logits) + (size_t)t * ld;
       const int nvec = Vl >> 3;
@@ -168,11 +176,11 @@ __global__ void __launch_bounds__(HT) ce_grad_kernel(void* __restrict__ logits, 
         uint4* p = reinterpret_cast<uint4*>(row) + c;
         h_unpack8(*p, v);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) v[j] = (__expf(v[j] - L) - ((c * 8 + j) == loc ? 1.f : 0.f)) * g;
+        for (int j = 0; j < 8; ++j) v[j] = (__expf(v[j] - L) - ((c * 8 + j) == loc ? tcoef : 0.f) - ucoef) * g;
         *p = h_pack8(v);
       }
       for (int c = (nvec << 3) + threadIdx.x; c < Vl; c += HT)
-        row[c] = __float2bfloat16((__expf(__bfloat162float(row[c]) - L) - (c == loc ? 1.f : 0.f)) * g);
+        row[c] = __float2bfloat16((__expf(__bfloat162float(row[c]) - L) - (c == loc ? tcoef : 0.f) - ucoef) * g);
     }
   }
 }
@@ -349,11 +357,12 @@ int dh_ce_stats(const void* logits, const void* labels, void* stats, int T, int 
   return h_rc("dh_ce_stats");
 }
 int dh_ce_grad_inplace(void* logits, const void* labels, const void* lse, const void* gtok, int T, int Vl, int64_t ld, int v0, int is_f32,
+                       float tcoef, float ucoef,
                        int sm_budget, cudaStream_t s) {
   DH_REQ(is_f32 || ld % 8 == 0, "bf16 logits need a row stride that is a multiple of 8");
   if (T <= 0) return 0;
-  if (is_f32) ce_grad_kernel<true><<<h_grid(T, 8, sm_budget), HT, 0, s>>>(logits, (const int*)labels, (const float*)lse, (const float*)gtok, T, Vl, ld, v0);
-  else ce_grad_kernel<false><<<h_grid(T, 8, sm_budget), HT, 0, s>>>(logits, (const int*)labels, (const float*)lse, (const float*)gtok, T, Vl, ld, v0);
+  if (is_f32) ce_grad_kernel<true><<<h_grid(T, 8, sm_budget), HT, 0, s>>>(logits, (const int*)labels, (const float*)lse, (const float*)gtok, T, Vl, ld, v0, tcoef, ucoef);
+  else ce_grad_kernel<false><<<h_grid(T, 8, sm_budget), HT, 0, s>>>(logits, (const int*)labels, (const float*)lse, (const float*)gtok, T, Vl, ld, v0, tcoef, ucoef);
   return h_rc("dh_ce_grad_inplace");
 }
 int dh_router_topk(const void* x, const void* w, void* probs, void* topi, void* gates, int T, int h, int E, int k, cudaStream_t s) {

@@ -25,6 +25,19 @@ const CUtensorMap* get_tmap_4d(const void* base, int elem_bytes, const uint64_t 
 
 void set_last_error(const char* fmt, ...);
 
+// cudaFuncSetAttribute applies to the function on the CURRENT device only, so "already
+// configured" has to be remembered per device: a process that drives a second GPU would
+// otherwise launch there without the shared-memory opt-in and fail.  A zero-initialised static
+// of this type plus device_flag() replaces the usual `static bool configured`.
+struct PerDeviceFlags {
+  bool done[64];
+};
+inline bool& device_flag(PerDeviceFlags& f) {
+  int dev = 0;
+  cudaGetDevice(&dev);
+  return f.done[dev & 63];
+}
+
 }  // namespace dh
 
 inline void set_last_error_c(const char* what, const char* msg) { dh::set_last_error("%s: %s", what, msg); }

@@ -83,7 +83,7 @@ def loss_fwd(env, hp: HeadParams, mb, x):
     y_full, _ = C.gather_along_first_dim(y, env.ps.tp_group)
     logits = G.gemm_nt(y_full, hp.lm_weight)
     v0, _ = vocab_range(env)
-    loss_tok, lse = L.vocab_parallel_ce_fwd(logits, mb.labels, v0, env.ps.tp_group)
+    loss_tok, lse = L.vocab_parallel_ce_fwd(logits, mb.labels, v0, env.ps.tp_group, label_smoothing=env.train.label_smoothing)
     mask = mb.loss_mask.reshape(-1).float()
     sums = torch.stack([(loss_tok * mask).sum(), mask.sum()])
     if env.ps.cp > 1:
@@ -98,7 +98,8 @@ def loss_bwd(env, hp: HeadParams, mb, saved, grad_scale: float):
     v0, _ = vocab_range(env)
     g_tok = L.mask_scale_loss_bwd(mb.loss_mask, saved["count"], grad_scale)
     logits = _use(env, saved.pop("logits"))
-    dlogits = L.vocab_parallel_ce_bwd_(logits, mb.labels, _use(env, saved.pop("lse")), g_tok, v0)
+    dlogits = L.vocab_parallel_ce_bwd_(logits, mb.labels, _use(env, saved.pop("lse")), g_tok, v0,
+                                       label_smoothing=env.train.label_smoothing, vocab=env.cfg.vocab_size)
     if dlogits.dtype != hp.lm_weight.dtype:
         dlogits = dlogits.to(hp.lm_weight.dtype)
     y_full = _use(env, saved.pop("y_full"))

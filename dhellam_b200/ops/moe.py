@@ -1,7 +1,7 @@
 """Mixture-of-experts primitives: router, dispatch plan, row permutations, combine.
 
 New relative to the reference (it has no MoE ops; see ``models/moe.py``).  The router runs
-as one sm_100a kernel on CUDA tensors (csrc/moe.cu: logits, softmax, top-k and gate
+as one sm_100a kernel on CUDA tensors (csrc/head_optim.cu, ``router_kernel``: logits, softmax, top-k and gate
 normalisation in one pass over the token row); the plan and the permutations use index
 arithmetic on the device, and the only host read is the per-expert row count that sizes
 the expert GEMMs (dropless routing has data-dependent shapes).

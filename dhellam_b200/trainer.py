@@ -8,6 +8,7 @@ schedule, gradient finalisation, the optimizer step, and loss / throughput repor
 """
 from __future__ import annotations
 
+import os
 import time
 from typing import List, Optional
 
@@ -39,8 +40,15 @@ class Trainer:
             try:
                 fused = FusedTP(self.ps, cfg, train, self.device)
             except Exception as e:       # no symmetric memory / no peer access on this machine
+                # Falling back silently would turn a broken symmetric-memory set-up into a different
+                # (NCCL) run that looks like a slow one.  It is an error unless explicitly allowed.
+                if os.environ.get("DHELLAM_ALLOW_NCCL_FALLBACK", "0") != "1":
+                    raise RuntimeError(
+                        f"in-kernel tensor-parallel collectives could not be set up on rank {self.ps.rank} "
+                        f"({type(e).__name__}: {e}); run with --no-fused-comm (TrainConfig.fused_comm=False) for library "
+                        "collectives, or set DHELLAM_ALLOW_NCCL_FALLBACK=1 to fall back automatically") from e
                 print(f"[dhellam_b200] in-kernel collectives unavailable on rank {self.ps.rank} ({type(e).__name__}: {e}); "
-                      "using NCCL collectives", flush=True)
+                      "DHELLAM_ALLOW_NCCL_FALLBACK=1: using NCCL collectives", flush=True)
             # all ranks of the group take the same path
             ok = torch.tensor([1 if fused is not None else 0], device=self.device)
             dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=self.ps.tp_group)

@@ -81,3 +81,42 @@ def test_benchmark_harness_has_the_reference_entry_points():
     assert benchmark_ms_ops_cp(3, None, None, [lambda: x @ x], [lambda: x + x], [lambda: x.sum(), lambda: x.mean()], wait_fwd=True) >= 0.0
     seq, par, sp = benchmark_dhellam(3, lambda: time.sleep(0.004), lambda: time.sleep(0.002))
     assert seq > par and sp > 1.2
+
+
+def test_launch_templates_keep_the_reference_context_protocol():
+    """``template_fwd_new`` returns ``[[inputs that require grad], outputs]`` and
+    ``template_bwd_new`` differentiates that context (dhellam/common/template_launch.py:38-70)."""
+    from dhellam_b200.common import template_bwd, template_bwd_new, template_fwd, template_fwd_new
+    x = torch.randn(4, 3, requires_grad=True)
+    w = torch.randn(3, 2, requires_grad=True)
+    c = torch.randn(4, 2)                         # no grad: must not appear in the context
+    ctx, ms = template_fwd_new(lambda a, b, k: a @ b + k, x, w, c)
+    assert len(ctx[0]) == 2 and ctx[0][0] is x and ctx[0][1] is w and ms == 0
+    g = torch.randn(4, 2)
+    grads, _ = template_bwd_new(ctx, g)
+    assert torch.allclose(grads[0], g @ w.t().detach(), atol=1e-6) and torch.allclose(grads[1], x.t().detach() @ g, atol=1e-6)
+    ctx2, _ = template_fwd(lambda d: {"y": d["x"] * 2}, {"x": c})
+    assert ctx2[0]["x"] is c and torch.equal(ctx2[1]["y"], c * 2)
+    out, _ = template_bwd(lambda cx, go: go * 2, ctx2, g)
+    assert torch.equal(out, g * 2)
+
+
+def test_cross_entropy_wrappers_with_label_smoothing():
+    """Dictionary protocol of the reference's loss op, with label smoothing, against a float64
+    restatement of its formula taken over the whole vocabulary."""
+    import torch.nn.functional as F
+    from dhellam_b200.ops.loss import cross_entropy_bwd, cross_entropy_fwd
+    torch.manual_seed(1)
+    S, B, V, a = 5, 2, 32, 0.1
+    logits = torch.randn(S, B, V)
+    target = torch.randint(0, V, (S, B))
+    ctx = cross_entropy_fwd({"vocab_parallel_logits": logits.clone(), "target": target}, label_smoothing=a)
+    s = a * V / (V - 1)
+    ref_in = logits.double().requires_grad_(True)
+    logp = F.log_softmax(ref_in, -1)
+    ref = (1 - s) * (-logp.gather(-1, target[..., None]).squeeze(-1)) - s * logp.mean(-1)
+    assert torch.allclose(ctx["loss"].double(), ref, atol=1e-5)
+    dout = torch.randn(S, B)
+    (ref * dout.double()).sum().backward()
+    g = cross_entropy_bwd(ctx, dout)
+    assert torch.allclose(g.double(), ref_in.grad, atol=1e-5)
