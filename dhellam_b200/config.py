@@ -139,6 +139,10 @@ class TrainConfig:
     hysteresis: int = 2
     min_loss_scale: float = 1.0
     label_smoothing: float = 0.0         # Megatron's --label-smoothing-factor
+    # the two switches of the benchmark's composition arm: the reference's built-in 17-block schedule
+    # (dhellam/core/dstb.py:1043-1059) and its device-wide synchronisation after every block (:1266)
+    reference_schedule: bool = False
+    sync_per_block: bool = False
 
     def num_microbatches(self, dp: int) -> int:
         assert self.global_batch_size % (self.micro_batch_size * dp) == 0, "global batch must divide by micro-batch x dp"

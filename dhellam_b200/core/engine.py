@@ -56,6 +56,7 @@ class Env:
         self.fused = fused
         self.fused_tp = fused is not None and ps.tp > 1
         self.cur_stream = None
+        self.exposed = None           # ExposedTimer of the engine's executor (set by the engine)
         self.softmax_scale = 1.0 / math.sqrt(cfg.head_dim)
         self.rope_cos = self.rope_sin = None
         if cfg.position == "rope":
@@ -84,14 +85,16 @@ def hand_over(obj, stream):
 
 class DoubleStrandEngine:
     def __init__(self, model, env: Env, strategy: Optional[Strategy] = None, single_stream: bool = False,
-                 profile: bool = False, trace=None, compute_streams: int = 2):
+                 profile: bool = False, trace=None, compute_streams: int = 2, sync_per_block: bool = False):
         self.model, self.env = model, env
         self.cfg, self.ps = env.cfg, env.ps
         self.program = build_layer_program(env.cfg, cp=env.ps.cp)
         self.streams = StreamSet(env.device if env.device.type == "cuda" else None, single_stream=single_stream,
                                  compute_streams=compute_streams)
-        self.executor = Executor(self.program, strategy or Strategy(), self.streams, profile=profile, trace=trace)
+        self.executor = Executor(self.program, strategy or Strategy(), self.streams, profile=profile, trace=trace,
+                                 sync_per_block=sync_per_block)
         env.streams = self.streams
+        env.exposed = self.executor.exposed      # shared with the head block and the in-kernel collectives
         self.acts: Dict[tuple, dict] = {}
         self.head_saved: Dict[int, dict] = {}
         self.fwd_done: Dict[int, object] = {}
@@ -261,6 +264,16 @@ class DoubleStrandEngine:
             st.s1.wait_stream(st.s3)
             st.s2.wait_stream(st.s3)
         self._inbox = {"next": from_next, "prev": from_prev}
+
+    def measure_exposed(self, on: bool):
+        """Switches the exposed-communication measurement on or off (see ``ExposedTimer``)."""
+        self.executor.exposed.enabled = bool(on) and self.streams.cuda
+        self.executor.exposed.spans = []
+
+    def exposed_ms(self) -> float:
+        """Time, summed over the spans recorded since ``measure_exposed(True)``, that compute streams
+        spent waiting for communication (synchronises)."""
+        return self.executor.exposed.total_ms() if self.streams.cuda else 0.0
 
     def pp_bubble_ms(self) -> float:
         """Sum of the exchange spans recorded since the last call (synchronises on GPUs)."""

@@ -33,12 +33,42 @@ def available() -> bool:
     return torch.cuda.is_available()
 
 
+# Which implementation the ops layer uses for CUDA tensors: "native" = this library's sm_100a
+# kernels (the product); "library" = PyTorch / cuBLAS / flash-attn calls only, never touching
+# libdhellam_b200.so.  The second exists for one purpose: the labelled composition arm of the
+# benchmark, which times the reference's recipe (torch.matmul, flash-attn, NCCL, eager PyTorch
+# elementwise ops; dhellam/operators/*.py) on the same box.
+_BACKEND = os.environ.get("DHELLAM_OPS_BACKEND", "native")
+
+
+def set_backend(name: str):
+    global _BACKEND
+    assert name in ("native", "library"), name
+    _BACKEND = name
+
+
+def backend() -> str:
+    return _BACKEND
+
+
+def use_native(t) -> bool:
+    """True when an op on tensor ``t`` should run this library's kernel."""
+    return t.is_cuda and _BACKEND == "native"
+
+
+def use_library(t) -> bool:
+    """True when an op on CUDA tensor ``t`` should run the PyTorch / vendor-library composition."""
+    return t.is_cuda and _BACKEND == "library"
+
+
 def lib_path() -> Path:
     return _LIB_PATH
 
 
 def lib():
     global _LIB
+    if _BACKEND == "library":
+        raise KernelError("the ops backend is 'library' (composition arm): the sm_100a kernel library must not be used")
     if _LIB is not None:
         return _LIB
     if not _LIB_PATH.exists():

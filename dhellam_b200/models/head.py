@@ -47,6 +47,33 @@ def _use(env, t):
     return t
 
 
+def _span(env):
+    """Timing bracket for a collective that the current (compute) stream has to sit through."""
+    t = getattr(env, "exposed", None)
+    if t is None or not t.enabled:
+        import contextlib
+        return contextlib.nullcontext()
+    return t.span(getattr(env, "cur_stream", None))
+
+
+def _symmetric(env, rows_full: int, width: int) -> bool:
+    """True when the head block's collective of this shape can use the symmetric-memory kernels
+    (same row count and width as the layers' collectives)."""
+    return bool(getattr(env, "fused_tp", False)) and rows_full == env.fused.rows and width == env.fused.width
+
+
+def tp_gather_rows(env, shard, tag: str):
+    """Sequence all-gather of ``shard [T/t, h]`` inside the tensor-parallel group: multimem / peer
+    push + arrival counters when the symmetric buffers fit the shape, else the library collective."""
+    if env.ps.tp <= 1:
+        return shard
+    with _span(env):
+        if _symmetric(env, shard.shape[0] * env.ps.tp, shard.shape[1]) and shard.dtype == torch.bfloat16:
+            return env.fused.all_gather(shard.contiguous(), tag)
+        full, _ = C.gather_along_first_dim(shard, env.ps.tp_group)
+        return full
+
+
 def vocab_range(env):
     vl = env.cfg.vocab_size // env.ps.tp
     return env.ps.tp_rank * vl, vl
@@ -55,11 +82,19 @@ def vocab_range(env):
 def embed_fwd(env, hp: HeadParams, mb):
     """tokens -> hidden ``[T/t, h]`` (sequence-parallel rows)."""
     v0, _ = vocab_range(env)
-    partial = E.embedding_fwd(mb.tokens, hp.word_embeddings, v0)
-    if env.ps.tp > 1:
-        x, _ = C.reduce_scatter_along_first_dim(partial, env.ps.tp_group)
+    T, h = mb.tokens.numel(), hp.word_embeddings.shape[1]
+    if env.ps.tp > 1 and _symmetric(env, T, h) and hp.word_embeddings.dtype == torch.bfloat16:
+        # partial rows straight into symmetric memory, summed inside the switch (no library collective)
+        E.embedding_fwd(mb.tokens, hp.word_embeddings, v0, out=env.fused.partial_buffer("embed", T, h))
+        with _span(env):
+            x = env.fused.rs_reduce("embed")
     else:
-        x = partial
+        partial = E.embedding_fwd(mb.tokens, hp.word_embeddings, v0)
+        if env.ps.tp > 1:
+            with _span(env):
+                x, _ = C.reduce_scatter_along_first_dim(partial, env.ps.tp_group)
+        else:
+            x = partial
     if env.cfg.position == "learned":
         pos = hp.position_embeddings[mb.positions_local.long()]
         x = x + pos
@@ -71,7 +106,7 @@ def embed_bwd(env, hp: HeadParams, mb, dx):
     dx = _use(env, dx)
     if env.cfg.position == "learned":
         hp.position_embeddings.main_grad.index_add_(0, mb.positions_local.long(), dx.float())
-    full, _ = C.gather_along_first_dim(dx, env.ps.tp_group)
+    full = tp_gather_rows(env, dx, "embed_bwd")
     E.embedding_bwd(full, mb.tokens, hp.word_embeddings.main_grad, v0)
 
 
@@ -80,7 +115,7 @@ def loss_fwd(env, hp: HeadParams, mb, x):
     Returns ``(loss scalar tensor, saved)``."""
     x = _use(env, x)
     y, stat = _norm_fwd(env, x, hp.final_ln_weight, hp.get("final_ln_bias"), 0)
-    y_full, _ = C.gather_along_first_dim(y, env.ps.tp_group)
+    y_full = tp_gather_rows(env, y, "head")        # a staging-buffer view: valid until the second next head gather
     logits = G.gemm_nt(y_full, hp.lm_weight)
     v0, _ = vocab_range(env)
     loss_tok, lse = L.vocab_parallel_ce_fwd(logits, mb.labels, v0, env.ps.tp_group, label_smoothing=env.train.label_smoothing)
@@ -103,8 +138,19 @@ def loss_bwd(env, hp: HeadParams, mb, saved, grad_scale: float):
     if dlogits.dtype != hp.lm_weight.dtype:
         dlogits = dlogits.to(hp.lm_weight.dtype)
     y_full = _use(env, saved.pop("y_full"))
-    d_y_full = G.gemm_nn(dlogits, hp.lm_weight)
-    G.gemm_tn_acc(dlogits, y_full, hp.lm_weight.main_grad)
-    d_y, _ = C.reduce_scatter_along_first_dim(d_y_full, env.ps.tp_group)
+    T, h = dlogits.shape[0], hp.lm_weight.shape[1]
+    if env.ps.tp > 1 and _symmetric(env, T, h) and dlogits.dtype == torch.bfloat16:
+        G.gemm_nn(dlogits, hp.lm_weight, out=env.fused.partial_buffer("head_bwd", T, h))
+        G.gemm_tn_acc(dlogits, y_full, hp.lm_weight.main_grad)      # runs while the peers finish their partial products
+        with _span(env):
+            d_y = env.fused.rs_reduce("head_bwd")
+    else:
+        d_y_full = G.gemm_nn(dlogits, hp.lm_weight)
+        G.gemm_tn_acc(dlogits, y_full, hp.lm_weight.main_grad)
+        if env.ps.tp > 1:
+            with _span(env):
+                d_y, _ = C.reduce_scatter_along_first_dim(d_y_full, env.ps.tp_group)
+        else:
+            d_y = d_y_full
     dx = _norm_bwd(env, d_y, _use(env, saved.pop("x")), hp.final_ln_weight, hp.get("final_ln_bias"), saved.pop("stat"), None, 0)
     return dx

@@ -19,7 +19,7 @@ _K1 = 0.044715
 
 def swiglu_fwd(y, sm_budget: int = 0, stream=None):
     f = y.shape[-1] // 2
-    if not y.is_cuda:
+    if not K.use_native(y):
         g, u = y[..., :f].float(), y[..., f:].float()
         return (torch.nn.functional.silu(g) * u).to(y.dtype)
     out = torch.empty(y.shape[:-1] + (f,), dtype=y.dtype, device=y.device)
@@ -30,7 +30,7 @@ def swiglu_fwd(y, sm_budget: int = 0, stream=None):
 
 def swiglu_bwd(dout, y, sm_budget: int = 0, stream=None):
     f = y.shape[-1] // 2
-    if not y.is_cuda:
+    if not K.use_native(y):
         g, u, d = y[..., :f].float(), y[..., f:].float(), dout.float()
         s = torch.sigmoid(g)
         dg = d * u * s * (1 + g * (1 - s))
@@ -44,7 +44,7 @@ def swiglu_bwd(dout, y, sm_budget: int = 0, stream=None):
 
 
 def gelu_fwd(x, sm_budget: int = 0, stream=None):
-    if not x.is_cuda:
+    if not K.use_native(x):
         xf = x.float()
         return (0.5 * xf * (1 + torch.tanh(_K0 * (xf + _K1 * xf ** 3)))).to(x.dtype)
     out = torch.empty_like(x)
@@ -54,7 +54,7 @@ def gelu_fwd(x, sm_budget: int = 0, stream=None):
 
 
 def gelu_bwd(dout, x, sm_budget: int = 0, stream=None):
-    if not x.is_cuda:
+    if not K.use_native(x):
         xf, d = x.float(), dout.float()
         t = torch.tanh(_K0 * (xf + _K1 * xf ** 3))
         dt = (1 - t * t) * _K0 * (1 + 3 * _K1 * xf * xf)

@@ -42,6 +42,9 @@ def attn_fwd(q, k, v, causal: bool = True, scale: float | None = None, sm_budget
     """Returns ``(out [Sq,B,Hq,d], lse [B,Hq,Sq] fp32)``."""
     d = q.shape[-1]
     scale = scale if scale is not None else 1.0 / math.sqrt(d)
+    if K.use_library(q):
+        from . import library as LIB
+        return LIB.attn_fwd(q, k, v, causal, scale)
     if not q.is_cuda:
         o, lse, _ = _ref_fwd(q, k, v, causal, scale)
         return o.to(q.dtype), lse
@@ -67,6 +70,11 @@ def attn_bwd(dout, q, k, v, out, lse, causal: bool = True, scale: float | None =
     removes the reference's ``cat(dq, dk, dv)`` (dhellam/core/dstb.py:379-384)."""
     d = q.shape[-1]
     scale = scale if scale is not None else 1.0 / math.sqrt(d)
+    if K.use_library(q):
+        from . import library as LIB
+        if dq is None:
+            dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+        return LIB.attn_bwd(dout, q, k, v, out, lse, dq, dk, dv, causal, scale)
     if not q.is_cuda:
         Sq, B, Hq, _ = q.shape
         Sk, Hk = k.shape[0], k.shape[2]

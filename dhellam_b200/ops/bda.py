@@ -34,7 +34,7 @@ def keep_mask_reference(numel: int, seed: int, p: float, device="cpu"):
 def bda_fwd(x, residual, bias=None, p: float = 0.0, seed: int = 0, training: bool = True, sm_budget: int = 0, stream=None):
     """``out = residual + dropout(x + bias)``."""
     p_eff = p if training else 0.0
-    if not x.is_cuda:
+    if not K.use_native(x):
         v = x.float()
         if bias is not None:
             v = v + bias.float()
@@ -54,7 +54,7 @@ def bda_bwd(dout, p: float = 0.0, seed: int = 0, training: bool = True, sm_budge
     p_eff = p if training else 0.0
     if p_eff == 0.0:
         return dout
-    if not dout.is_cuda:
+    if not K.use_native(dout):
         keep = keep_mask_reference(dout.numel(), seed, p_eff, dout.device).view(dout.shape)
         return (dout.float() * keep * (1.0 / (1.0 - p_eff))).to(dout.dtype)
     dx = torch.empty_like(dout)

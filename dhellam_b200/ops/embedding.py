@@ -15,16 +15,21 @@ import torch
 from .. import kernels as K
 
 
-def embedding_fwd(tokens, weight, vocab_start: int = 0, sm_budget: int = 0, stream=None):
-    """``tokens [T]`` integer -> ``[T, h]``; rows of foreign tokens are zero."""
+def embedding_fwd(tokens, weight, vocab_start: int = 0, sm_budget: int = 0, stream=None, out=None):
+    """``tokens [T]`` integer -> ``[T, h]``; rows of foreign tokens are zero.  ``out`` may name
+    the destination (for example a symmetric-memory buffer that a reduce-scatter reads next)."""
     T = tokens.numel()
     Vl, h = weight.shape
-    if not weight.is_cuda:
+    if not K.use_native(weight):
         loc = tokens.reshape(-1).long() - vocab_start
         own = (loc >= 0) & (loc < Vl)
-        out = weight[loc.clamp(0, Vl - 1)] * own[:, None].to(weight.dtype)
-        return out
-    out = torch.empty((T, h), dtype=weight.dtype, device=weight.device)
+        res = weight[loc.clamp(0, Vl - 1)] * own[:, None].to(weight.dtype)
+        if out is not None:
+            out.copy_(res)
+            return out
+        return res
+    if out is None:
+        out = torch.empty((T, h), dtype=weight.dtype, device=weight.device)
     fn = K.proto("dh_embedding_fwd", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p])
     K.check(fn(tokens.data_ptr(), weight.data_ptr(), out.data_ptr(), T, h, Vl, vocab_start, sm_budget,
                K.stream_ptr(stream)), "dh_embedding_fwd")
@@ -35,7 +40,7 @@ def embedding_bwd(dout, tokens, main_grad, vocab_start: int = 0, sm_budget: int 
     """``main_grad[token - vocab_start] += dout[row]`` for owned tokens (fp32 accumulate)."""
     T = tokens.numel()
     Vl, h = main_grad.shape
-    if not main_grad.is_cuda:
+    if not K.use_native(main_grad):
         loc = tokens.reshape(-1).long() - vocab_start
         own = (loc >= 0) & (loc < Vl)
         rows = torch.nonzero(own).squeeze(1)

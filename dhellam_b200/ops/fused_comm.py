@@ -33,6 +33,7 @@ push stores to every peer in turn.  Peer pointers come from
 from __future__ import annotations
 
 import collections
+import contextlib
 import ctypes
 import os
 from ctypes import c_int, c_int64, c_uint, c_void_p
@@ -42,8 +43,8 @@ import torch.distributed as dist
 
 from .. import kernels as K
 
-AG_TAGS = ("attn_c", "mlp_c", "attn_l_bwd", "mlp_l_bwd", "regather_attn", "regather_mlp", "head")
-RS_TAGS = ("attn_l", "mlp_l", "mlp_c_bwd", "attn_c_bwd")
+AG_TAGS = ("attn_c", "mlp_c", "attn_l_bwd", "mlp_l_bwd", "regather_attn", "regather_mlp", "head", "embed_bwd")
+RS_TAGS = ("attn_l", "mlp_l", "mlp_c_bwd", "attn_c_bwd", "head_bwd", "embed")
 
 
 def _align(n, a=1024):
@@ -123,6 +124,7 @@ class FusedTP:
         self.policy = os.environ.get("DHELLAM_FUSED_POLICY", "split")
         self.paired = True                # set by the engine before every layer run
         self.rs_ctas = int(os.environ.get("DHELLAM_RS_CTAS", "0")) or max(16, 128 // self.world)
+        self.exposed = None               # the engine's ExposedTimer (set by the trainer); None = no measurement
 
     def split(self, M: int, N: int, Kd: int) -> bool:
         """Whether the collective beside the GEMM ``[M, Kd] x [Kd, N]`` runs as its own kernel."""
@@ -227,9 +229,11 @@ class FusedTP:
     def gather_wait(self, tag: str):
         slot, target, M, Kd, ev = self._pending[tag].popleft()     # oldest first: a weight gradient may trail by one layer
         s = torch.cuda.current_stream(self.device)
-        s.wait_event(ev)
-        fn = K.proto("dh_wait_counters", [c_void_p, c_int, c_uint, c_void_p])
-        K.check(fn(self.ptrs[self.rank] + self.off_agc[tag][slot], M // 128, target, s.cuda_stream), "dh_wait_counters")
+        ctx = self.exposed.span(s) if (self.exposed is not None and self.exposed.enabled) else contextlib.nullcontext()
+        with ctx:                        # the consumer's stream stands still until every rank's rows have arrived
+            s.wait_event(ev)
+            fn = K.proto("dh_wait_counters", [c_void_p, c_int, c_uint, c_void_p])
+            K.check(fn(self.ptrs[self.rank] + self.off_agc[tag][slot], M // 128, target, s.cuda_stream), "dh_wait_counters")
         return self._stage_view(tag, slot, M, Kd)
 
     def all_gather(self, shard, tag: str):

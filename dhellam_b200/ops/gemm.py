@@ -25,7 +25,11 @@ _GEMM_ARGS = [c_void_p, c_int64, c_int, c_void_p, c_int64, c_int, c_void_p, c_in
 
 
 def _native(*ts) -> bool:
-    return all(t.is_cuda for t in ts)
+    return all(K.use_native(t) for t in ts)
+
+
+def _library(*ts) -> bool:
+    return all(K.use_library(t) for t in ts)
 
 
 def _check2d(t, name):
@@ -53,6 +57,9 @@ def gemm_nt(x, w, out=None, sm_budget: int = 0, stream=None, out_dtype=None):
     M, Kd = x.shape
     N = w.shape[0]
     assert w.shape[1] == Kd, (x.shape, w.shape)
+    if _library(x, w):
+        from . import library as LIB
+        return LIB.gemm_nt(x, w, out, out_dtype)
     if not _native(x, w):
         y = (x.float() @ w.float().t()).to(out_dtype or x.dtype)
         if out is not None:
@@ -71,6 +78,9 @@ def gemm_nn(dy, w, out=None, sm_budget: int = 0, stream=None):
     M, N = dy.shape
     Kd = w.shape[1]
     assert w.shape[0] == N, (dy.shape, w.shape)
+    if _library(dy, w):
+        from . import library as LIB
+        return LIB.gemm_nn(dy, w, out)
     if not _native(dy, w):
         y = (dy.float() @ w.float()).to(dy.dtype)
         if out is not None:
@@ -90,6 +100,9 @@ def gemm_tn_acc(dy, x, main_grad, accumulate: bool = True, sm_budget: int = 0, s
     M, N = dy.shape
     Kd = x.shape[1]
     assert x.shape[0] == M and tuple(main_grad.shape) == (N, Kd), (dy.shape, x.shape, main_grad.shape)
+    if _library(dy, x, main_grad):
+        from . import library as LIB
+        return LIB.gemm_tn_acc(dy, x, main_grad, accumulate)
     if not _native(dy, x, main_grad):
         g = dy.float().t() @ x.float()
         if accumulate:

@@ -28,7 +28,7 @@ from .comm import group_size
 def ce_local_stats(logits, labels, vocab_start: int, sm_budget: int = 0, stream=None):
     """``stats [T,4] fp32 = (max, sumexp relative to max, target logit if owned else 0, sum of logits)``."""
     T, Vl = logits.shape
-    if not logits.is_cuda:
+    if not K.use_native(logits):
         lf = logits.float()
         m = lf.max(dim=-1).values
         se = torch.exp(lf - m[:, None]).sum(-1)
@@ -87,7 +87,7 @@ def vocab_parallel_ce_bwd_(logits, labels, lse, grad_per_token, vocab_start: int
     T, Vl = logits.shape
     s = _smoothing(label_smoothing, vocab)
     tcoef, ucoef = 1.0 - s, (s / vocab if s else 0.0)
-    if not logits.is_cuda:
+    if not K.use_native(logits):
         p = torch.exp(logits.float() - lse[:, None])
         loc = labels.long() - vocab_start
         own = (loc >= 0) & (loc < Vl)

@@ -61,7 +61,7 @@ def _ln_bwd_ref(dy, x, w, mu, rstd):
 # ----------------------------------------------------------------------------- public
 def rmsnorm_fwd(x, weight, eps: float = 1e-5, sm_budget: int = 0, stream=None):
     """Returns ``(y, rstd)``; ``rstd`` is fp32 per row."""
-    if not x.is_cuda:
+    if not K.use_native(x):
         return _rms_fwd_ref(x, weight, eps)
     rows, h = _rows(x)
     y = torch.empty_like(x)
@@ -75,7 +75,7 @@ def rmsnorm_fwd(x, weight, eps: float = 1e-5, sm_budget: int = 0, stream=None):
 def rmsnorm_bwd(dy, x, weight, rstd, weight_main_grad=None, residual_grad=None, sm_budget: int = 0, stream=None):
     """``dx = rmsnorm'(dy) (+ residual_grad)``; the weight gradient is added into
     ``weight_main_grad`` (fp32) when given, else returned."""
-    if not x.is_cuda:
+    if not K.use_native(x):
         dx, dw = _rms_bwd_ref(dy, x, weight, rstd)
         if residual_grad is not None:
             dx = dx + residual_grad.float()
@@ -99,7 +99,7 @@ def rmsnorm_bwd(dy, x, weight, rstd, weight_main_grad=None, residual_grad=None, 
 
 def layernorm_fwd(x, weight, bias, eps: float = 1e-5, sm_budget: int = 0, stream=None):
     """Returns ``(y, mu, rstd)`` like the reference's ``pylayernorm_fwd``."""
-    if not x.is_cuda:
+    if not K.use_native(x):
         return _ln_fwd_ref(x, weight, bias, eps)
     rows, h = _rows(x)
     y = torch.empty_like(x)
@@ -115,7 +115,7 @@ def layernorm_fwd(x, weight, bias, eps: float = 1e-5, sm_budget: int = 0, stream
 def layernorm_bwd(dy, x, weight, mu, rstd, weight_main_grad=None, bias_main_grad=None, residual_grad=None,
                   sm_budget: int = 0, stream=None):
     """Returns ``(dx, dw, db)``; ``dw``/``db`` are None when accumulated into the given buffers."""
-    if not x.is_cuda:
+    if not K.use_native(x):
         dx, dw, db = _ln_bwd_ref(dy, x, weight, mu, rstd)
         if residual_grad is not None:
             dx = dx + residual_grad.float()

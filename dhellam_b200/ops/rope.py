@@ -29,7 +29,7 @@ def rope_apply_(qkv, positions, cos, sin, nq: int, nkv: int, d: int, inverse: bo
     """
     T = qkv.shape[0]
     assert qkv.shape[1] == (nq + 2 * nkv) * d
-    if not qkv.is_cuda:
+    if not K.use_native(qkv):
         v = qkv[:, : (nq + nkv) * d].float().view(T, nq + nkv, d)
         c = cos[positions.long()][:, None, :]
         s = sin[positions.long()][:, None, :]

@@ -34,6 +34,9 @@ def _adam_ref(param, master, m, v, grad, lr, b1, b2, eps, wd, step, grad_scale):
 
 def adam_update(param, master, m, v, grad, lr, b1, b2, eps, wd, step, grad_scale=1.0, stream=None):
     """One fused Adam(W) update of a contiguous range; writes the low-precision copy too."""
+    if K.use_library(param):
+        from ..ops import library as LIB
+        return LIB.adam_update(param, master, m, v, grad, lr, b1, b2, eps, wd, step, grad_scale)
     if not param.is_cuda:
         return _adam_ref(param, master, m, v, grad, lr, b1, b2, eps, wd, step, grad_scale)
     fn = K.proto("dh_adam_step", [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_float, c_float,
@@ -45,6 +48,9 @@ def adam_update(param, master, m, v, grad, lr, b1, b2, eps, wd, step, grad_scale
 
 def sum_squares(t, stream=None):
     """fp32 sum of squares of a contiguous fp32 tensor (1-element tensor)."""
+    if K.use_library(t):
+        from ..ops import library as LIB
+        return LIB.sum_squares(t)
     if not t.is_cuda:
         return (t.float() ** 2).sum().reshape(1)
     out = torch.zeros(1, dtype=torch.float32, device=t.device)

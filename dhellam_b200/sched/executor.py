@@ -65,10 +65,45 @@ class StreamSet:
                 s.wait_stream(source)
 
 
+class ExposedTimer:
+    """Measures how long compute streams stand still waiting for communication.
+
+    When enabled, every place where a compute stream waits for the communication stream (an event
+    wait on a collective's completion, the arrival-counter wait in front of a GEMM that reads a
+    gathered operand, a library collective issued on the compute stream itself) is bracketed by
+    two timing events on the waiting stream: the first completes when the stream's earlier work
+    is done, the second when the wait is over, so their distance is time in which that stream had
+    nothing else to run.  ``total_ms`` sums the spans (it synchronises)."""
+
+    def __init__(self):
+        self.enabled = False
+        self.spans: List[tuple] = []
+
+    @contextlib.contextmanager
+    def span(self, stream):
+        if not self.enabled or stream is None:
+            yield
+            return
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        yield
+        e1.record(stream)
+        self.spans.append((e0, e1))
+
+    def total_ms(self) -> float:
+        torch.cuda.synchronize()
+        spans, self.spans = self.spans, []
+        return float(sum(a.elapsed_time(b) for a, b in spans))
+
+
 class Executor:
     def __init__(self, program: LayerProgram, strategy: Strategy, streams: StreamSet, profile: bool = False,
-                 trace=None):
+                 trace=None, sync_per_block: bool = False):
         self.program = program
+        # True reproduces the reference interpreter's device-wide synchronisation after every
+        # schedule block (dhellam/core/dstb.py:1266); only the benchmark's composition arm sets it
+        self.sync_per_block = sync_per_block and streams.cuda
+        self.exposed = ExposedTimer()
         self.strategy = strategy.completed(program)
         self.strategy.validate(program)
         self.streams = streams
@@ -142,6 +177,8 @@ class Executor:
             for lane, lst in order:
                 for e in lst:
                     launch(e, lane)
+            if self.sync_per_block:
+                torch.cuda.synchronize()
         for target, (op, run, b) in list(pending.items()):   # flush what no marker claimed
             self._exec(op, run, "S2", lanes, b)
 
@@ -180,7 +217,11 @@ class Executor:
             for d in op.deps:
                 rec = self._events.get(d)
                 if rec is not None and rec[1] is not stream:   # produced on another stream
-                    stream.wait_event(rec[0])
+                    if rec[1] is st.s3 and self.exposed.enabled:
+                        with self.exposed.span(stream):        # a compute stream waiting for a collective
+                            stream.wait_event(rec[0])
+                    else:
+                        stream.wait_event(rec[0])
         if budget:
             run.sm_budget[op.name] = budget
         run.env.cur_stream = stream

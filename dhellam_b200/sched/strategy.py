@@ -228,6 +228,35 @@ def _dense_tp_bwd_only(program: LayerProgram) -> Optional[List[Block]]:
     ]
 
 
+def reference_paired(program: LayerProgram) -> Optional[List[Block]]:
+    """The reference's own built-in paired schedule (dhellam/core/dstb.py:1043-1059), 17 blocks,
+    for the dense layer.  Used by the benchmark's composition arm; the engine's default is
+    ``default_paired``."""
+    act_f = "swiglu_mlp" if program.has("swiglu_mlp") else "gelu_mlp"
+    act_b = "swiglu_bwd" if program.has("swiglu_bwd") else "gelu_bwd"
+    if not program.has("fl_attn") or not program.has("gemm_mlp_c"):
+        return None
+    return [
+        Block(s1=["ln_attn"]),
+        Block(s2=["bda_mlp_bwd"], s3=["allgather_attn"]),
+        Block(s1=["gemm_attn_c", "fl_attn"], s3=["allgather_mlp_bwd"]),
+        Block(s1=["gemm_attn_l"]),
+        Block(s2=["gemm_dgrad_mlp_l", "gemm_wgrad_mlp_l"], s3=["reduce_scatter_attn"]),
+        Block(s2=[act_b]),
+        Block(s2=["gemm_dgrad_mlp_c"]),
+        Block(s2=["gemm_wgrad_mlp_c"], s3=["reduce_scatter_mlp_c_bwd"]),
+        Block(s1=["bda_attn", "ln_mlp"]),
+        Block(s2=["ln_mlp_bwd", "bda_attn_bwd"], s3=["allgather_mlp"]),
+        Block(s1=["gemm_mlp_c"], s3=["allgather_attn_bwd"]),
+        Block(s1=[act_f, "gemm_mlp_l"]),
+        Block(s2=["gemm_dgrad_attn_l", "gemm_wgrad_attn_l", "attn_bwd"], s3=["reduce_scatter_mlp"]),
+        Block(s1=["bda_mlp"]),
+        Block(s2=["gemm_dgrad_attn_c"]),
+        Block(s2=["gemm_wgrad_attn_c"], s3=["reduce_scatter_attn_c_bwd"]),
+        Block(s2=["ln_attn_bwd"]),
+    ]
+
+
 def default_paired(program: LayerProgram) -> List[Block]:
     """Built-in paired schedule.  Dense layers get the hand-placed pairing above; any other
     program gets the generic alternation: each strand's collective is launched together with

@@ -54,7 +54,8 @@ class Trainer:
             dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=self.ps.tp_group)
             if int(ok) == 0:
                 fused = None
-        if fused is None and self.device.type == "cuda" and self.ps.world > 1 and train.dhellam:
+        from . import kernels as _K
+        if fused is None and self.device.type == "cuda" and self.ps.world > 1 and train.dhellam and _K.backend() == "native":
             # Library collectives co-run with the GEMMs and occupy one SM of many SM pairs;
             # a CTA-pair GEMM then cannot place its clusters (measured 1.6x slower step),
             # so that path keeps the single-CTA tiles.
@@ -63,8 +64,16 @@ class Trainer:
         self.env = Env(cfg, self.ps, train, self.device, self.model.dtype, fused=fused)
         if strategy is None and train.schedule_config:
             strategy = Strategy.load(train.schedule_config)
+        if strategy is None and train.reference_schedule:
+            from .models.transformer import build_layer_program
+            from .sched.strategy import reference_paired
+            blocks = reference_paired(build_layer_program(cfg, cp=self.ps.cp))
+            if blocks is None:
+                raise ValueError("the reference's built-in schedule exists for the dense layer only")
+            strategy = Strategy(dcblocks=blocks)
         self.engine = DoubleStrandEngine(self.model, self.env, strategy, single_stream=single_stream or not train.dhellam,
-                                         profile=profile, trace=trace, compute_streams=train.compute_streams)
+                                         profile=profile, trace=trace, compute_streams=train.compute_streams,
+                                         sync_per_block=train.sync_per_block)
         if self.env.fused_tp and not cfg.is_moe and self.ps.cp == 1:
             # The symmetric staging slots are reused every second call; prove for THIS strategy (built in,
             # searched or user-written) and stream count that no rank can overwrite a slot another rank
@@ -73,6 +82,8 @@ class Trainer:
             from .sched.checker import check_buffer_reuse
             check_buffer_reuse(self.engine.program, self.engine.executor.strategy, FUSED_BUFFER_EFFECTS,
                                compute_streams=1 if (single_stream or not train.dhellam) else train.compute_streams)
+        if fused is not None:
+            fused.exposed = self.engine.executor.exposed
         self.optimizer = MixedPrecisionAdam(self.model, train, self.ps, distributed=distributed_optimizer)
         if self.ps.dp * self.ps.cp > 1 and not distributed_optimizer:
             from .parallel.dp import OverlappedGradReducer
