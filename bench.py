@@ -247,7 +247,8 @@ def measure(args, impl: str, steps: int, warmup: int, do_e2e: bool, world: int, 
         from dhellam_b200.ops import library as LIB
         res["attention_impl"] = LIB.ATTENTION_IMPL
     # free the model, the optimizer state and the symmetric buffers before the next arm
-    tr.engine = tr.optimizer = tr.model = tr.env = None
+    loss = l = None
+    tr.close()
     del tr
     gc.collect()
     torch.cuda.empty_cache()

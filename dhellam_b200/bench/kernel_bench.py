@@ -73,7 +73,30 @@ def build(kernel, a):
         return (lambda: G.gemm_tn_acc(dy, x, g, sm_budget=a.sm_budget)), 2.0 * M * Nn * Kd, 2.0 * (M * Kd + M * Nn) + 8.0 * Nn * Kd
     if kernel == "torch_nt":
         x, w = bf(M, Kd), bf(Nn, Kd)
-        return (lambda: torch.matmul(x, w.t())), 2.0 * M * Nn * Kd, 2.0 * (M * Kd + Nn * Kd + M * Nn)
+        out = torch.empty(M, Nn, dtype=torch.bfloat16, device="cuda")
+        return (lambda: torch.matmul(x, w.t(), out=out)), 2.0 * M * Nn * Kd, 2.0 * (M * Kd + Nn * Kd + M * Nn)
+    if kernel == "torch_nn":
+        dy, w = bf(M, Nn), bf(Nn, Kd)
+        out = torch.empty(M, Kd, dtype=torch.bfloat16, device="cuda")
+        return (lambda: torch.matmul(dy, w, out=out)), 2.0 * M * Nn * Kd, 2.0 * (M * Kd + Nn * Kd + M * Nn)
+    if kernel == "torch_tn":        # the library's weight gradient: bf16 product, then added into the fp32 buffer
+        dy, x = bf(M, Nn), bf(M, Kd)
+        g = torch.zeros(Nn, Kd, device="cuda")
+        return (lambda: g.add_(torch.matmul(dy.t(), x))), 2.0 * M * Nn * Kd, 2.0 * (M * Kd + M * Nn) + 8.0 * Nn * Kd
+    if kernel in ("flash_fwd", "flash_bwd"):      # the flash-attn 2 package (or SDPA) on the same operands, for comparison
+        from ..ops import library as LIB
+        S, B, H, Hk, d = a.seq, a.batch, a.heads, a.kv_heads, 128
+        qkv = bf(S, B, H + 2 * Hk, d)
+        q, k, v = qkv[:, :, :H], qkv[:, :, H:H + Hk], qkv[:, :, H + Hk:]
+        fl = 4.0 * S * S * d * H * B * (0.5 if a.causal else 1.0)
+        sc = 1.0 / d ** 0.5
+        if kernel == "flash_fwd":
+            return (lambda: LIB.attn_fwd(q, k, v, a.causal, sc)), fl, 2.0 * (qkv.numel() + S * B * H * d)
+        o, lse = LIB.attn_fwd(q, k, v, a.causal, sc)
+        do = bf(S, B, H, d)
+        dqkv = torch.empty_like(qkv)
+        dq, dk, dv = dqkv[:, :, :H], dqkv[:, :, H:H + Hk], dqkv[:, :, H + Hk:]
+        return (lambda: LIB.attn_bwd(do, q, k, v, o, lse, dq, dk, dv, a.causal, sc)), 2.5 * fl, 2.0 * (3 * qkv.numel() + 2 * do.numel())
     if kernel in ("attn_fwd", "attn_bwd"):
         S, B, H, Hk, d = a.seq, a.batch, a.heads, a.kv_heads, 128
         qkv = bf(S, B, H + 2 * Hk, d)
@@ -108,12 +131,15 @@ def build(kernel, a):
     raise SystemExit(f"unknown kernel {kernel}")
 
 
-HEADLINE = [
-    ("gemm_nt", dict(m=16384, n=1280, k=8192)), ("gemm_nt", dict(m=16384, n=8192, k=1024)),
-    ("gemm_nt", dict(m=16384, n=7168, k=8192)), ("gemm_nt", dict(m=16384, n=8192, k=3584)),
-    ("gemm_nn", dict(m=16384, n=7168, k=8192)), ("gemm_tn", dict(m=16384, n=7168, k=8192)),
-    ("gemm_nt", dict(m=16384, n=16032, k=8192)), ("torch_nt", dict(m=16384, n=7168, k=8192)),
-    ("attn_fwd", dict(seq=4096, batch=4, heads=8, kv_heads=1)), ("attn_bwd", dict(seq=4096, batch=4, heads=8, kv_heads=1)),
+# the per-GPU GEMM shapes of the 8-way tensor-parallel headline run, each followed by the library (cuBLAS through
+# torch.matmul) on the same operands in the same call
+_G = [("nt", dict(m=16384, n=1280, k=8192)), ("nt", dict(m=16384, n=8192, k=1024)), ("nt", dict(m=16384, n=7168, k=8192)),
+      ("nt", dict(m=16384, n=8192, k=3584)), ("nn", dict(m=16384, n=7168, k=8192)), ("nn", dict(m=16384, n=1024, k=8192)),
+      ("tn", dict(m=16384, n=7168, k=8192)), ("tn", dict(m=16384, n=8192, k=3584)), ("tn", dict(m=16384, n=1280, k=8192)),
+      ("nt", dict(m=16384, n=16032, k=8192))]
+HEADLINE = [(f"{lib}_{kind}", shape) for kind, shape in _G for lib in ("gemm", "torch")] + [
+    ("attn_fwd", dict(seq=4096, batch=4, heads=8, kv_heads=1)), ("flash_fwd", dict(seq=4096, batch=4, heads=8, kv_heads=1)),
+    ("attn_bwd", dict(seq=4096, batch=4, heads=8, kv_heads=1)), ("flash_bwd", dict(seq=4096, batch=4, heads=8, kv_heads=1)),
     ("rmsnorm_fwd", dict(m=2048, n=8192)), ("rmsnorm_bwd", dict(m=2048, n=8192)),
     ("swiglu_fwd", dict(m=16384, n=3584)), ("swiglu_bwd", dict(m=16384, n=3584)), ("ce_stats", dict(m=16384, n=16032)),
 ]
@@ -146,8 +172,12 @@ def main(argv=None):
     jobs = HEADLINE if a.suite else [(a.kernel, {})]
     for kernel, over in jobs:
         b = argparse.Namespace(**{**vars(a), **over})
-        fn, fl, by = build(kernel, b)
-        ms = time_ms(fn, a.iters, a.warmup, flush)
+        try:
+            fn, fl, by = build(kernel, b)
+            ms = time_ms(fn, a.iters, a.warmup, flush)
+        except Exception as e:                 # e.g. the flash-attn wheel has no kernel for this GPU
+            print(json.dumps({"kernel": kernel, "shape": over, "error": f"{type(e).__name__}: {str(e)[:160]}"}), flush=True)
+            continue
         rec = {"kernel": kernel, "shape": over or {k: getattr(a, k) for k in ("m", "n", "k", "seq", "batch", "heads", "kv_heads")},
                "ms": round(ms, 4), "l2": "flushed between launches" if flush is not None else "not flushed"}
         if fl:

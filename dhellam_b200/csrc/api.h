@@ -42,6 +42,13 @@ void dh_attn_set_bwd_mode(int mode);
 // Kernel choice for dh_gemm_bf16: 0 = per problem (default; also DHELLAM_GEMM_MODE), 1 = single-CTA tiles
 // (128 x 256) only, 2 = CTA-pair tiles (256 x 256, tcgen05 cta_group::2) whenever M > 128.
 void dh_gemm_set_mode(int mode);
+// Split of an accumulating (fp32, add-in-place) GEMM along K into n atomic-add work items per tile:
+// -1 = heuristic (fill the last wave), 0 / 1 = off, n = forced.
+void dh_gemm_set_splitk(int n);
+// dh_gemm_bf16 with the tensor-parallel collective hooks of the CTA-pair kernel (see gemm_sm100.cu).
+int dh_gemm_bf16_sync(const void* a, int64_t lda, int a_mn_major, const void* b, int64_t ldb, int b_mn_major, void* d, int64_t ldd,
+                      int d_fp32, int accumulate, int M, int N, int K, int sm_budget, const void* wait_count, unsigned wait_target,
+                      void* const* sig_ptrs, int sig_bpr, int perm_mode, int world, int rank, cudaStream_t stream);
 
 #ifdef __cplusplus
 }

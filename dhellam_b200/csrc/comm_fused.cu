@@ -279,6 +279,77 @@ __global__ void __launch_bounds__(256) rs_reduce_kernel(const RsrParams p) {
   }
 }
 
+// Row-block-wise form of the reduction above.  The producing GEMMs (dh_gemm_bf16_sync with
+// sig_ptrs) bump, on the rank that owns a 128-row block, that block's counter once per stored
+// 32-row piece of every tile; a block is complete on all ranks when its counter reaches
+// `target`.  Work items are (row block, column slice); a CTA waits (bounded) for its item's
+// block only, so the reduction of the first blocks runs while every rank's GEMM is still
+// producing the later ones.  Eight independent 16-byte reductions are in flight per thread:
+// the reduction is bound by the round trip through the switch, not by bytes.
+struct RsbParams {
+  const __nv_bfloat16* part[MAX_RANKS];
+  const __nv_bfloat16* part_mc;
+  const uint32_t* ready;          // this rank's per-block counters (local memory)
+  __nv_bfloat16* out;
+  int M, N, rank, world, blocks, slices;
+  uint32_t target;
+  DeviceStatus* status;
+};
+
+__global__ void __launch_bounds__(256) rs_reduce_blocks_kernel(const RsbParams p) {
+  __shared__ int ok_s;
+  constexpr int U = 8;
+  const int rows_per_rank = p.M / p.world;
+  const int cw = p.N / p.slices;                              // columns per slice (multiple of 8)
+  const int vec_per_row = cw >> 3;
+  const int items = p.blocks * p.slices;
+  for (int it = blockIdx.x; it < items; it += gridDim.x) {
+    const int b = it / p.slices, sl = it - b * p.slices;
+    __syncthreads();
+    if (threadIdx.x == 0) ok_s = wait_counter_sys(p.ready + b, p.target, nullptr, p.status, 660) ? 1 : 0;
+    __syncthreads();
+    if (!ok_s) return;
+    const int rows = min(BM, rows_per_rank - b * BM);
+    const int total = rows * vec_per_row;
+    const long long in_base = ((long long)p.rank * rows_per_rank + (long long)b * BM) * p.N + (long long)sl * cw;
+    const long long out_base = (long long)b * BM * p.N + (long long)sl * cw;
+    for (int i0 = threadIdx.x; i0 < total; i0 += blockDim.x * U) {
+      uint4 v[U];
+      long long off[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int i = i0 + u * blockDim.x;
+        if (i < total) {
+          const int r = i / vec_per_row, c = i - r * vec_per_row;
+          off[u] = (long long)r * p.N + c * 8;
+          if (p.part_mc != nullptr) v[u] = multimem_ld_reduce_bf16x8(p.part_mc + in_base + off[u]);
+        }
+      }
+      if (p.part_mc == nullptr) {
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          if (i0 + u * blockDim.x >= total) continue;
+          float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+          for (int q = 0; q < p.world; ++q) {
+            const uint4 w = ld_relaxed_sys_v4(p.part[(p.rank + q) % p.world] + in_base + off[u]);
+            const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const float2 f = unpack_bf16x2(ww[j]);
+              acc[2 * j] += f.x;
+              acc[2 * j + 1] += f.y;
+            }
+          }
+          v[u] = make_uint4(pack_bf16x2(acc[0], acc[1]), pack_bf16x2(acc[2], acc[3]), pack_bf16x2(acc[4], acc[5]), pack_bf16x2(acc[6], acc[7]));
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u)
+        if (i0 + u * blockDim.x < total) st_v4(p.out + out_base + off[u], v[u]);
+    }
+  }
+}
+
 template <bool B_MN>
 __global__ void __launch_bounds__(THREADS, 1)
 ag_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, const AgParams p) {
@@ -677,6 +748,31 @@ int dh_ag_push(const void* shard, void* const* stage_ptrs, void* const* count_pt
   ag_push_kernel<<<ctas, 256, 0, stream>>>(p);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) set_last_error("dh_ag_push launch failed: %s", cudaGetErrorString(e));
+  return (int)e;
+}
+
+// Row-block-wise reduce-scatter (see rs_reduce_blocks_kernel).  ready: this rank's per-block counters; target: the
+// value a complete block reaches in this call; part_ptrs / part_mc as in dh_rs_reduce.
+int dh_rs_reduce_blocks(void* const* part_ptrs, const void* part_mc, const void* ready, void* out, int M, int N, int rank, int world,
+                        unsigned target, int ctas, cudaStream_t stream) {
+  if (world < 2 || world > MAX_RANKS) { set_last_error("dh_rs_reduce_blocks: world size %d not in [2, %d]", world, MAX_RANKS); return (int)cudaErrorInvalidValue; }
+  if (M % world != 0 || N % 8 != 0) { set_last_error("dh_rs_reduce_blocks: M must divide by world and N by 8 (M=%d N=%d)", M, N); return (int)cudaErrorInvalidValue; }
+  RsbParams p;
+  for (int i = 0; i < MAX_RANKS; ++i) p.part[i] = i < world ? (const __nv_bfloat16*)part_ptrs[i] : nullptr;
+  p.part_mc = (const __nv_bfloat16*)part_mc;
+  p.ready = (const uint32_t*)ready;
+  p.out = (__nv_bfloat16*)out;
+  p.M = M; p.N = N; p.rank = rank; p.world = world;
+  p.blocks = (M / world + BM - 1) / BM;
+  if (ctas <= 0) ctas = 32;
+  int slices = 1;
+  while (p.blocks * slices < ctas && (N / (slices * 2)) % 8 == 0 && slices < 64) slices *= 2;
+  p.slices = slices;
+  p.target = target;
+  p.status = reinterpret_cast<DeviceStatus*>(dh_status_device_ptr());
+  rs_reduce_blocks_kernel<<<ctas, 256, 0, stream>>>(p);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) set_last_error("dh_rs_reduce_blocks launch failed: %s", cudaGetErrorString(e));
   return (int)e;
 }
 

@@ -20,6 +20,7 @@
 #include "tmap.h"
 
 #include <cstdlib>
+#include <cstring>
 
 namespace dh {
 
@@ -293,9 +294,7 @@ static int launch(const CUtensorMap* ta, const CUtensorMap* tb, const Params& p,
 // output tile: each loads its own 128 rows of A and its own 128-column half of B, the
 // leader's elected thread issues M = 256 MMAs that read both CTAs' shared memory, and each
 // CTA ends up with its own 128 accumulator rows in its own TMEM.  Per CTA and k-block this
-// moves 32 KiB through TMA instead of 48 KiB and leaves room for a deeper ring, which is
-// what the single-CTA kernel lacks at large shapes (its tensor pipe idles ~20% of the time
-// waiting for operands).
+// moves 32 KiB through TMA instead of 48 KiB, which leaves room for a six-slot ring.
 //
 // Barrier protocol (all barriers exist in both CTAs at the same offsets):
 //   full[s]      leader only; the leader's producer arms it with the bytes of BOTH CTAs,
@@ -306,43 +305,119 @@ static int launch(const CUtensorMap* ta, const CUtensorMap* tb, const Params& p,
 // A cluster barrier after setup keeps remote arrivals from reaching an uninitialised
 // barrier, and one before the TMEM release keeps either CTA from leaving while the other
 // can still signal it.
+//
+// Epilogue.  Each epilogue warp drains its 32 accumulator rows in chunks of 128 bytes per row
+// (64 bf16 or 32 fp32 columns): tcgen05.ld -> registers -> a 4 KiB swizzled staging tile in
+// shared memory -> one TMA store of a 32-row box (two staging tiles per warp, so the store of
+// chunk c overlaps the TMEM read of chunk c+1).  Whole 128-byte lines reach L2 instead of 32
+// scattered 16-byte pieces per store instruction.  An accumulating fp32 output (a weight
+// gradient added into main_grad) uses the reducing form of the bulk store: L2 adds the tile
+// in place and nothing is read back into the SM.  Because that add is atomic, such a GEMM may
+// also be split along K ("split_k" work items per tile, each adding its share), which fills
+// the last wave when the tile count is a poor multiple of the SM pairs.
+//
+// Collective hooks (tensor-parallel sequence all-gather in front, reduce-scatter behind):
+//   wait_count   the A operand is a staging buffer that peers are still filling; before the
+//                first load of a 128-row block the producer waits (bounded) for that block's
+//                arrival counter in LOCAL memory and then reads local memory only;
+//   sig[]        after a warp's 32 rows of a tile are stored (store completion waited for),
+//                it bumps the row block's counter on the rank that owns those rows, so the
+//                owner's reduction kernel can start on a block as soon as every rank has
+//                delivered it instead of after every rank's whole GEMM;
+//   perm_mode    visiting order of the 256-row tile rows: 1 = own shard first, then the other
+//                ranks' shards row block by row block (the order in which a simultaneous push
+//                from all ranks completes them); 2 = row block by row block over all owners.
 // ---------------------------------------------------------------------------------------
 namespace pair {
-constexpr int STAGES2 = 7;                        // ring slots allocated; Params.stages of them are used
+constexpr int RING = 6;                            // ring slots
 constexpr int TILE_M = 2 * BM;                     // 256 rows per CTA pair
 constexpr int BN_HALF = BN / 2;                    // B columns loaded by each CTA
 constexpr int A2_STAGE_BYTES = BM * BK * 2;        // 16 KiB
 constexpr int B2_STAGE_BYTES = BN_HALF * BK * 2;   // 16 KiB
 constexpr int STAGE2_BYTES = A2_STAGE_BYTES + B2_STAGE_BYTES;
+constexpr int EPI_TILE_BYTES = 32 * 128;           // 32 rows x 128 bytes
+constexpr int EPI_BYTES = 4 * 2 * EPI_TILE_BYTES;  // 4 warps x 2 staging tiles = 32 KiB
+constexpr long long PEER_WAIT_CYCLES = 40000000000ll;   // ~20 s: a peer may still be starting up
 
 struct __align__(8) Control2 {
-  uint64_t full[STAGES2];
-  uint64_t empty[STAGES2];
+  uint64_t full[RING];
+  uint64_t empty[RING];
   uint64_t acc_full[NUM_ACC];
   uint64_t acc_empty[NUM_ACC];
   uint32_t tmem_base;
   int abort_flag;
 };
-constexpr int SMEM2_BYTES = STAGES2 * STAGE2_BYTES + 1024 + 256;
+constexpr int SMEM2_BYTES = RING * STAGE2_BYTES + EPI_BYTES + 1024 + 256;
 
-__device__ __forceinline__ void tile_coords2(int t, int tiles_m, int tiles_n, int group_m, int& tm, int& tn) {
-  const int band = group_m * tiles_n;
+struct PairParams {
+  int M, N, K;
+  int tiles_m, tiles_n;
+  int stages, group_m;
+  int split_k, kb_per_split;           // work item = (tile, k range)
+  int reduce_add;                      // epilogue: 1 = add into the output (bulk reduce), 0 = plain store
+  // collective hooks (all off when null / 0)
+  const uint32_t* wait_count;          // arrival counters of A's 128-row blocks (local memory)
+  uint32_t wait_target;
+  uint32_t* sig[8];                    // per-owner arrays of row-block completion counters
+  int sig_bpr;                         // 128-row blocks per owner
+  int perm_mode, perm_world, perm_rank;
+  long long wait_budget;               // cycles for the barriers inside the CTA
+  DeviceStatus* status;
+};
+
+__device__ __forceinline__ int perm_tile_m(int i, const PairParams& p) {
+  if (p.perm_mode == 0) return i;
+  const int per = p.tiles_m / p.perm_world;
+  if (p.perm_mode == 1) {
+    if (i < per) return p.perm_rank * per + i;
+    const int k = i - per, w1 = p.perm_world - 1;
+    const int j = k / w1, r = k - j * w1;
+    return ((p.perm_rank + 1 + r) % p.perm_world) * per + j;
+  }
+  const int j = i / p.perm_world, r = i - j * p.perm_world;
+  return ((p.perm_rank + 1 + r) % p.perm_world) * per + j;
+}
+
+// Work item -> (tile row, tile column, first k-block, end k-block).
+__device__ __forceinline__ void item_coords(int item, const PairParams& p, int num_tiles, int num_kb, int& tm, int& tn, int& kb0, int& kb1) {
+  const int ks = item / num_tiles;
+  const int t = item - ks * num_tiles;
+  const int band = p.group_m * p.tiles_n;
   const int g = t / band;
-  const int first_m = g * group_m;
-  const int rows = min(group_m, tiles_m - first_m);
+  const int first_m = g * p.group_m;
+  const int rows = min(p.group_m, p.tiles_m - first_m);
   const int r = t - g * band;
-  tm = first_m + (r % rows);
+  tm = perm_tile_m(first_m + (r % rows), p);
   tn = r / rows;
+  kb0 = ks * p.kb_per_split;
+  kb1 = min(num_kb, kb0 + p.kb_per_split);
+}
+
+__device__ __forceinline__ bool wait_block_counter(const uint32_t* c, uint32_t want, volatile int* abort_flag, DeviceStatus* st, int where) {
+  if (ld_acquire_sys(c) >= want) return true;
+  const long long t0 = clock64();
+  while (true) {
+    if (ld_acquire_sys(c) >= want) return true;
+    __nanosleep(100);
+    if (*abort_flag) return false;
+    if (clock64() - t0 > PEER_WAIT_CYCLES) {
+      *abort_flag = 1;
+      report_error(st, ERR_FLAG_TIMEOUT, where, (int)want);
+      return false;
+    }
+  }
 }
 
 template <bool A_MN, bool B_MN, bool OUT_F32>
 __global__ void __launch_bounds__(THREADS, 1)
-gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, const Params p) {
+gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                 const __grid_constant__ CUtensorMap tmap_d, const PairParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sA = smem;
-  uint8_t* sB = smem + STAGES2 * A2_STAGE_BYTES;
-  Control2* ctl = reinterpret_cast<Control2*>(smem + STAGES2 * STAGE2_BYTES);
+  uint8_t* sB = smem + RING * A2_STAGE_BYTES;
+  uint8_t* sEpi = smem + RING * STAGE2_BYTES;
+  Control2* ctl = reinterpret_cast<Control2*>(smem + RING * STAGE2_BYTES + EPI_BYTES);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -350,10 +425,11 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   const int pair_id = blockIdx.x >> 1;
   const int num_pairs = gridDim.x >> 1;
   const int num_tiles = p.tiles_m * p.tiles_n;      // tiles of 256 x 256
+  const int num_items = num_tiles * p.split_k;
   const int num_kb = (p.K + BK - 1) / BK;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < STAGES2; ++s) {
+    for (int s = 0; s < RING; ++s) {
       mbar_init(&ctl->full[s], 1);
       mbar_init(&ctl->empty[s], 1);
     }
@@ -383,13 +459,22 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       int s = 0;
       uint32_t ph = 0;
       bool ok = true;
-      for (int t = pair_id; t < num_tiles && ok; t += num_pairs) {
-        int tm, tn;
-        tile_coords2(t, p.tiles_m, p.tiles_n, p.group_m, tm, tn);
+      int ready_block = -1;
+      for (int it = pair_id; it < num_items && ok; it += num_pairs) {
+        int tm, tn, kb0, kb1;
+        item_coords(it, p, num_tiles, num_kb, tm, tn, kb0, kb1);
         const int m0 = tm * TILE_M + (int)rank * BM;
         const int n0 = tn * BN + (int)rank * BN_HALF;
-        for (int kb = 0; kb < num_kb; ++kb) {
-          if (!mbar_wait(&ctl->empty[s], ph ^ 1, abort_flag, p.status, 110)) { ok = false; break; }
+        if (p.wait_count != nullptr) {
+          const int blk = m0 / BM;
+          if (blk != ready_block && m0 < p.M) {
+            if (!wait_block_counter(p.wait_count + blk, p.wait_target, abort_flag, p.status, 115)) { ok = false; break; }
+            fence_proxy_async_all();                // peers' stores -> visible to the TMA reads below
+            ready_block = blk;
+          }
+        }
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!mbar_wait(&ctl->empty[s], ph ^ 1, abort_flag, p.status, 110, p.wait_budget)) { ok = false; break; }
           if (rank == 0) mbar_expect_tx(&ctl->full[s], 2 * STAGE2_BYTES);
           const uint32_t full_leader = mapa_u32(smem_u32(&ctl->full[s]), 0);
           uint8_t* a_dst = sA + s * A2_STAGE_BYTES;
@@ -421,12 +506,14 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       int acc = 0;
       uint32_t acc_ph = 0;
       bool ok = true;
-      for (int t = pair_id; t < num_tiles && ok; t += num_pairs) {
-        if (!mbar_wait<true>(&ctl->acc_empty[acc], acc_ph ^ 1, abort_flag, p.status, 210)) { ok = false; break; }
+      for (int it = pair_id; it < num_items && ok; it += num_pairs) {
+        int tm, tn, kb0, kb1;
+        item_coords(it, p, num_tiles, num_kb, tm, tn, kb0, kb1);
+        if (!mbar_wait<true>(&ctl->acc_empty[acc], acc_ph ^ 1, abort_flag, p.status, 210, p.wait_budget)) { ok = false; break; }
         tc_fence_after();
         const uint32_t tmem_acc = tmem_base + acc * ACC_COLS;
-        for (int kb = 0; kb < num_kb; ++kb) {
-          if (!mbar_wait(&ctl->full[s], ph, abort_flag, p.status, 211)) { ok = false; break; }
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!mbar_wait(&ctl->full[s], ph, abort_flag, p.status, 211, p.wait_budget)) { ok = false; break; }
           tc_fence_after();
           const uint32_t a_base = smem_u32(sA + s * A2_STAGE_BYTES);
           const uint32_t b_base = smem_u32(sB + s * B2_STAGE_BYTES);
@@ -436,7 +523,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                                         : umma_smem_desc(a_base + kk * 32, 16, 1024);
             const uint64_t bdesc = B_MN ? umma_smem_desc(b_base + kk * 2048, BK * 128, 1024)
                                         : umma_smem_desc(b_base + kk * 32, 16, 1024);
-            umma_bf16_2sm(tmem_acc, adesc, bdesc, idesc, (kb | kk) != 0 ? 1u : 0u);
+            umma_bf16_2sm(tmem_acc, adesc, bdesc, idesc, (kb != kb0 || kk != 0) ? 1u : 0u);
           }
           const uint32_t e = smem_u32(&ctl->empty[s]);
           umma_commit_2sm(mapa_u32(e, 0));
@@ -453,23 +540,78 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     __syncwarp();
   } else {
     // ------------------------------ epilogue (both CTAs) ----------------------
+    constexpr int CH_COLS = OUT_F32 ? 32 : 64;      // columns per 128-byte chunk
+    constexpr int NCH = BN / CH_COLS;
     const int quarter = warp & 3;
+    uint8_t* stg = sEpi + quarter * (2 * EPI_TILE_BYTES);
     int acc = 0;
     uint32_t acc_ph = 0;
+    uint32_t cc = 0;                                // running chunk count -> staging tile parity
     bool ok = true;
-    for (int t = pair_id; t < num_tiles && ok; t += num_pairs) {
-      int tm, tn;
-      tile_coords2(t, p.tiles_m, p.tiles_n, p.group_m, tm, tn);
-      if (!mbar_wait(&ctl->acc_full[acc], acc_ph, abort_flag, p.status, 310)) { ok = false; break; }
+    for (int it = pair_id; it < num_items && ok; it += num_pairs) {
+      int tm, tn, kb0, kb1;
+      item_coords(it, p, num_tiles, num_kb, tm, tn, kb0, kb1);
+      if (!mbar_wait(&ctl->acc_full[acc], acc_ph, abort_flag, p.status, 310, p.wait_budget)) { ok = false; break; }
       tc_fence_after();
-      const int row = tm * TILE_M + (int)rank * BM + quarter * 32 + lane;
+      const int row0 = tm * TILE_M + (int)rank * BM + quarter * 32;     // first of this warp's 32 output rows
       const uint32_t taddr = tmem_base + acc * ACC_COLS + ((uint32_t)(quarter * 32) << 16);
-      store_acc_row<OUT_F32>(p, row, row < p.M, taddr, tn * BN);
+#pragma unroll 1
+      for (int c = 0; c < NCH; ++c) {
+        const int col0 = tn * BN + c * CH_COLS;
+        if (col0 >= p.N) break;                     // uniform across the warp
+        uint32_t r[OUT_F32 ? 32 : 64];
+        tmem_ld32(taddr + c * CH_COLS, *reinterpret_cast<uint32_t(*)[32]>(&r[0]));
+        if (!OUT_F32) tmem_ld32(taddr + c * CH_COLS + 32, *reinterpret_cast<uint32_t(*)[32]>(&r[32]));
+        // the store that read this staging tile two chunks ago must have finished reading it
+        if (lane == 0) tma_store_wait_read<1>();
+        tmem_ld_wait();
+        __syncwarp();
+        if (row0 < p.M) {
+          uint8_t* tile = stg + (cc & 1) * EPI_TILE_BYTES;
+          uint8_t* rowp = tile + lane * 128;
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            uint4 v;
+            if (OUT_F32) {
+              v = make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
+            } else {
+              v.x = pack_bf16x2(__uint_as_float(r[8 * j + 0]), __uint_as_float(r[8 * j + 1]));
+              v.y = pack_bf16x2(__uint_as_float(r[8 * j + 2]), __uint_as_float(r[8 * j + 3]));
+              v.z = pack_bf16x2(__uint_as_float(r[8 * j + 4]), __uint_as_float(r[8 * j + 5]));
+              v.w = pack_bf16x2(__uint_as_float(r[8 * j + 6]), __uint_as_float(r[8 * j + 7]));
+            }
+            // 128-byte swizzle: 16-byte chunk j of row `lane` sits at chunk position j ^ (lane & 7)
+            *reinterpret_cast<uint4*>(rowp + ((j ^ (lane & 7)) << 4)) = v;
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            if (p.reduce_add) tma_reduce_add_2d(&tmap_d, tile, col0, row0);
+            else tma_store_2d(&tmap_d, tile, col0, row0);
+            tma_store_commit();
+          }
+          ++cc;
+        }
+      }
+      // the accumulator has been read out: hand the TMEM buffer back before the stores drain
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(&ctl->acc_empty[acc], 0);
+      if (p.sig[0] != nullptr && row0 < p.M) {
+        // this warp's 32 rows of the tile are in memory -> tell the rank that owns the row block
+        if (lane == 0) {
+          tma_store_wait<0>();
+          fence_proxy_async_all();
+          asm volatile("fence.acq_rel.sys;" ::: "memory");
+          const int blk = row0 / BM;
+          red_add_release_sys(p.sig[blk / p.sig_bpr] + (blk % p.sig_bpr), 1u);
+        }
+        __syncwarp();
+      }
       if (++acc == NUM_ACC) { acc = 0; acc_ph ^= 1; }
     }
+    if (lane == 0) tma_store_wait<0>();             // shared memory must outlive the bulk stores
+    __syncwarp();
   }
 
   // ------------------------------ teardown ------------------------------------
@@ -483,7 +625,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 }
 
 template <bool A_MN, bool B_MN, bool OUT_F32>
-static int launch_pair(const CUtensorMap* ta, const CUtensorMap* tb, const Params& p, int pairs, cudaStream_t stream) {
+static int launch_pair(const CUtensorMap* ta, const CUtensorMap* tb, const CUtensorMap* td, const PairParams& p, int pairs,
+                       cudaStream_t stream) {
   auto kern = gemm_pair_kernel<A_MN, B_MN, OUT_F32>;
   static PerDeviceFlags configured_on;
   bool& configured = device_flag(configured_on);
@@ -507,7 +650,7 @@ static int launch_pair(const CUtensorMap* ta, const CUtensorMap* tb, const Param
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, *ta, *tb, p);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, *ta, *tb, *td, p);
   if (e != cudaSuccess) set_last_error("pair gemm launch failed: %s", cudaGetErrorString(e));
   return (int)e;
 }
@@ -528,16 +671,55 @@ static int gemm_mode() {
 
 extern "C" void dh_gemm_set_mode(int mode) { dh::gemm::g_gemm_mode = mode; }
 
-extern "C" int dh_gemm_bf16(const void* a, int64_t lda, int a_mn_major, const void* b, int64_t ldb, int b_mn_major, void* d,
-                            int64_t ldd, int d_fp32, int accumulate, int M, int N, int K, int epilogue, int sm_budget,
-                            cudaStream_t stream) {
-  using namespace dh;
-  using namespace dh::gemm;
-  if (M <= 0 || N <= 0 || K <= 0) return 0;
-  if (epilogue != 0) {
-    set_last_error("dh_gemm_bf16: unknown epilogue %d", epilogue);
-    return (int)cudaErrorInvalidValue;
+namespace dh {
+namespace gemm {
+
+// Work items per tile along K for an accumulating (atomic-add) output: the smallest split that
+// brings the last wave's occupancy above 93 %, or 1.  DHELLAM_GEMM_SPLITK = 0 / 1 turns it off,
+// = n forces n.
+static int g_splitk_override = -1;     // dh_gemm_set_splitk: -1 = follow the environment / heuristic
+
+static int choose_split_k(int tiles, int pairs, int num_kb) {
+  static int forced = -1;
+  if (g_splitk_override >= 0) {
+    int b = g_splitk_override < 1 ? 1 : g_splitk_override;
+    while (b > 1 && num_kb / b < 2) --b;
+    return b;
   }
+  if (forced < 0) {
+    const char* e = getenv("DHELLAM_GEMM_SPLITK");
+    forced = e ? atoi(e) : 0;
+    if (forced < 0) forced = 0;
+    if (e && forced == 0) forced = 1;
+  }
+  int best = 1;
+  if (forced >= 1) {
+    best = forced;
+  } else {
+    auto eff = [&](int s) { const long long it = (long long)tiles * s; return (double)it / (double)(((it + pairs - 1) / pairs) * pairs); };
+    double be = eff(1);
+    if (be < 0.93) {
+      for (int s = 2; s <= 4; ++s) {
+        const double e2 = eff(s);
+        if (e2 > be + 0.03) { be = e2; best = s; }
+      }
+    }
+  }
+  while (best > 1 && num_kb / best < 16) --best;       // keep every share long enough to amortise its prologue
+  return best < 1 ? 1 : best;
+}
+
+struct SyncArgs {
+  const void* wait_count = nullptr;
+  unsigned wait_target = 0;
+  void* const* sig_ptrs = nullptr;
+  int sig_bpr = 0;
+  int perm_mode = 0, world = 1, rank = 0;
+};
+
+static int gemm_impl(const void* a, int64_t lda, int a_mn_major, const void* b, int64_t ldb, int b_mn_major, void* d, int64_t ldd,
+                     int d_fp32, int accumulate, int M, int N, int K, int sm_budget, const SyncArgs& sy, cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
   if (accumulate && !d_fp32) {
     set_last_error("dh_gemm_bf16: accumulate needs an fp32 output");
     return (int)cudaErrorInvalidValue;
@@ -547,14 +729,19 @@ extern "C" int dh_gemm_bf16(const void* a, int64_t lda, int a_mn_major, const vo
     set_last_error("dh_gemm_bf16: output must be 16-byte aligned with ldd a multiple of %d", out_vec);
     return (int)cudaErrorInvalidValue;
   }
+  const bool hooks = sy.wait_count != nullptr || sy.sig_ptrs != nullptr || sy.perm_mode != 0;
   const int mode = gemm_mode();
-  const bool use_pair = mode != 1 && M > BM;
+  const bool use_pair = (mode != 1 && M > BM) || hooks;
+  if (hooks && sy.world > 8) {
+    set_last_error("dh_gemm_bf16_sync: at most 8 ranks");
+    return (int)cudaErrorInvalidValue;
+  }
   const int b_rows = use_pair ? pair::BN_HALF : BN;
   static int pair_stages = 0, pair_group = 0;
   if (pair_stages == 0) {
     const char* e = getenv("DHELLAM_GEMM_STAGES");
-    pair_stages = e ? atoi(e) : 6;
-    if (pair_stages < 2 || pair_stages > pair::STAGES2) pair_stages = 6;
+    pair_stages = e ? atoi(e) : pair::RING;
+    if (pair_stages < 2 || pair_stages > pair::RING) pair_stages = pair::RING;
     e = getenv("DHELLAM_GEMM_GROUP");
     pair_group = e ? atoi(e) : 8;        // 8 x 256 rows per L2 band measured best at the large shapes
     if (pair_group < 1) pair_group = 8;
@@ -565,38 +752,72 @@ extern "C" int dh_gemm_bf16(const void* a, int64_t lda, int a_mn_major, const vo
   const CUtensorMap* tb = b_mn_major ? get_tmap_2d(b, 2, (uint64_t)N, (uint64_t)K, (uint64_t)ldb * 2, 64, BK, true)
                                      : get_tmap_2d(b, 2, (uint64_t)K, (uint64_t)N, (uint64_t)ldb * 2, BK, b_rows, true);
   if (!ta || !tb) return (int)cudaErrorInvalidValue;
+  const int sms = dh_sm_count();
+  int budget = (sm_budget <= 0 || sm_budget > sms) ? sms : sm_budget;
+  const int sel = (a_mn_major ? 4 : 0) | (b_mn_major ? 2 : 0) | (d_fp32 ? 1 : 0);
+  DeviceStatus* status = reinterpret_cast<DeviceStatus*>(dh_status_device_ptr());
 
+  if (use_pair) {
+    using namespace pair;
+    PairParams p;
+    memset(&p, 0, sizeof(p));
+    p.M = M; p.N = N; p.K = K;
+    p.tiles_m = (M + TILE_M - 1) / TILE_M;
+    p.tiles_n = (N + BN - 1) / BN;
+    p.stages = pair_stages;
+    p.group_m = pair_group;
+    p.status = status;
+    const int num_tiles = p.tiles_m * p.tiles_n;
+    const int num_kb = (K + BK - 1) / BK;
+    int pairs = budget / 2;
+    if (pairs < 1) pairs = 1;
+    p.reduce_add = accumulate ? 1 : 0;
+    p.split_k = accumulate ? choose_split_k(num_tiles, pairs, num_kb) : 1;
+    p.kb_per_split = (num_kb + p.split_k - 1) / p.split_k;
+    while (p.split_k > 1 && (p.split_k - 1) * p.kb_per_split >= num_kb) --p.split_k;   // no empty share
+    p.wait_count = reinterpret_cast<const uint32_t*>(sy.wait_count);
+    p.wait_target = sy.wait_target;
+    if (sy.sig_ptrs != nullptr) {
+      for (int i = 0; i < sy.world && i < 8; ++i) p.sig[i] = reinterpret_cast<uint32_t*>(sy.sig_ptrs[i]);
+      p.sig_bpr = sy.sig_bpr;
+      if (p.sig_bpr <= 0) { set_last_error("dh_gemm_bf16_sync: blocks per rank must be positive"); return (int)cudaErrorInvalidValue; }
+    }
+    // the row order follows the ranks' shards only when every shard is a whole number of 256-row tiles
+    if (sy.perm_mode != 0 && sy.world > 1 && p.tiles_m % sy.world == 0 && M % TILE_M == 0) {
+      p.perm_mode = sy.perm_mode; p.perm_world = sy.world; p.perm_rank = sy.rank;
+      p.group_m = sy.perm_mode == 1 ? (p.tiles_m / sy.world < pair_group ? p.tiles_m / sy.world : pair_group) : pair_group;
+    }
+    // barriers inside the CTA sit downstream of a peer wait, so they must outlast it
+    p.wait_budget = (p.wait_count != nullptr) ? 2 * PEER_WAIT_CYCLES : (long long)DH_WAIT_BUDGET_CYCLES;
+    const int num_items = num_tiles * p.split_k;
+    if (pairs > num_items) pairs = num_items;
+    CUtensorMap td;
+    if (!encode_tmap_2d_into(&td, d, d_fp32 ? 4 : 2, (uint64_t)N, (uint64_t)M, (uint64_t)ldd * (d_fp32 ? 4 : 2), d_fp32 ? 32 : 64, 32, true))
+      return (int)cudaErrorInvalidValue;
+    switch (sel) {
+      case 0: return launch_pair<false, false, false>(ta, tb, &td, p, pairs, stream);
+      case 1: return launch_pair<false, false, true>(ta, tb, &td, p, pairs, stream);
+      case 2: return launch_pair<false, true, false>(ta, tb, &td, p, pairs, stream);
+      case 3: return launch_pair<false, true, true>(ta, tb, &td, p, pairs, stream);
+      case 4: return launch_pair<true, false, false>(ta, tb, &td, p, pairs, stream);
+      case 5: return launch_pair<true, false, true>(ta, tb, &td, p, pairs, stream);
+      case 6: return launch_pair<true, true, false>(ta, tb, &td, p, pairs, stream);
+      default: return launch_pair<true, true, true>(ta, tb, &td, p, pairs, stream);
+    }
+  }
   Params p;
   p.d = d;
   p.ldd = ldd;
   p.M = M;
   p.N = N;
   p.K = K;
-  p.tiles_m = use_pair ? (M + pair::TILE_M - 1) / pair::TILE_M : (M + BM - 1) / BM;
+  p.tiles_m = (M + BM - 1) / BM;
   p.tiles_n = (N + BN - 1) / BN;
   p.accumulate = accumulate;
-  p.stages = pair_stages;
-  p.group_m = pair_group;
-  p.status = reinterpret_cast<DeviceStatus*>(dh_status_device_ptr());
-  const int sms = dh_sm_count();
-  int budget = (sm_budget <= 0 || sm_budget > sms) ? sms : sm_budget;
+  p.stages = 0;
+  p.group_m = 0;
+  p.status = status;
   const int num_tiles = p.tiles_m * p.tiles_n;
-  const int sel = (a_mn_major ? 4 : 0) | (b_mn_major ? 2 : 0) | (d_fp32 ? 1 : 0);
-  if (use_pair) {
-    int pairs = budget / 2;
-    if (pairs < 1) pairs = 1;
-    if (pairs > num_tiles) pairs = num_tiles;
-    switch (sel) {
-      case 0: return pair::launch_pair<false, false, false>(ta, tb, p, pairs, stream);
-      case 1: return pair::launch_pair<false, false, true>(ta, tb, p, pairs, stream);
-      case 2: return pair::launch_pair<false, true, false>(ta, tb, p, pairs, stream);
-      case 3: return pair::launch_pair<false, true, true>(ta, tb, p, pairs, stream);
-      case 4: return pair::launch_pair<true, false, false>(ta, tb, p, pairs, stream);
-      case 5: return pair::launch_pair<true, false, true>(ta, tb, p, pairs, stream);
-      case 6: return pair::launch_pair<true, true, false>(ta, tb, p, pairs, stream);
-      default: return pair::launch_pair<true, true, true>(ta, tb, p, pairs, stream);
-    }
-  }
   const int grid = num_tiles < budget ? num_tiles : budget;
   switch (sel) {
     case 0: return launch<false, false, false>(ta, tb, p, grid, stream);
@@ -608,4 +829,43 @@ extern "C" int dh_gemm_bf16(const void* a, int64_t lda, int a_mn_major, const vo
     case 6: return launch<true, true, false>(ta, tb, p, grid, stream);
     default: return launch<true, true, true>(ta, tb, p, grid, stream);
   }
+}
+
+}  // namespace gemm
+}  // namespace dh
+
+// Work items per tile along K for accumulating outputs: -1 = heuristic (default; DHELLAM_GEMM_SPLITK overrides),
+// 0 / 1 = never split, n = always n (as far as K allows).
+extern "C" void dh_gemm_set_splitk(int n) { dh::gemm::g_splitk_override = n; }
+
+extern "C" int dh_gemm_bf16(const void* a, int64_t lda, int a_mn_major, const void* b, int64_t ldb, int b_mn_major, void* d,
+                            int64_t ldd, int d_fp32, int accumulate, int M, int N, int K, int epilogue, int sm_budget,
+                            cudaStream_t stream) {
+  if (epilogue != 0) {
+    dh::set_last_error("dh_gemm_bf16: unknown epilogue %d", epilogue);
+    return (int)cudaErrorInvalidValue;
+  }
+  return dh::gemm::gemm_impl(a, lda, a_mn_major, b, ldb, b_mn_major, d, ldd, d_fp32, accumulate, M, N, K, sm_budget, dh::gemm::SyncArgs(),
+                             stream);
+}
+
+// The same product with the tensor-parallel collective hooks of the CTA-pair kernel:
+//   wait_count / wait_target  A is an all-gather staging buffer: wait per 128-row block for its arrival counter
+//   sig_ptrs / sig_bpr        D is this rank's partial product of a reduce-scatter: after each stored row block bump
+//                             its counter on the owning rank (sig_ptrs[owner][block within the owner's shard])
+//   perm_mode                 0 natural row order, 1 own shard first then the others block by block, 2 block by
+//                             block over all owners
+extern "C" int dh_gemm_bf16_sync(const void* a, int64_t lda, int a_mn_major, const void* b, int64_t ldb, int b_mn_major, void* d,
+                                 int64_t ldd, int d_fp32, int accumulate, int M, int N, int K, int sm_budget, const void* wait_count,
+                                 unsigned wait_target, void* const* sig_ptrs, int sig_bpr, int perm_mode, int world, int rank,
+                                 cudaStream_t stream) {
+  dh::gemm::SyncArgs sy;
+  sy.wait_count = wait_count;
+  sy.wait_target = wait_target;
+  sy.sig_ptrs = sig_ptrs;
+  sy.sig_bpr = sig_bpr;
+  sy.perm_mode = perm_mode;
+  sy.world = world;
+  sy.rank = rank;
+  return dh::gemm::gemm_impl(a, lda, a_mn_major, b, ldb, b_mn_major, d, ldd, d_fp32, accumulate, M, N, K, sm_budget, sy, stream);
 }

@@ -63,9 +63,14 @@ struct TmapHash {
     return (size_t)h;
   }
 };
-// Tensor maps are immutable once encoded; entries are never evicted (a training job
-// touches a few hundred distinct (pointer, shape) pairs).
+// Tensor maps are immutable once encoded.  Entries are never evicted (callers keep the returned
+// pointer until their launch, without a lock), so the cache is capped instead: a training job
+// touches a few hundred distinct (pointer, shape) pairs; once kMaxCached maps exist, further
+// ones are encoded into a small per-thread ring and stay valid for the next kRing calls of that
+// thread, which is far more than one launch needs.
 static std::unordered_map<TmapKey, CUtensorMap*, TmapHash> g_tmaps;
+static constexpr size_t kMaxCached = 16384;
+static constexpr int kRing = 64;
 
 static const CUtensorMap* encode_cached(const TmapKey& key, CUtensorMapDataType dt, int rank, void* base,
                                         const cuuint64_t* dims, const cuuint64_t* strides, const cuuint32_t* box,
@@ -75,7 +80,10 @@ static const CUtensorMap* encode_cached(const TmapKey& key, CUtensorMapDataType 
   if (it != g_tmaps.end()) return it->second;
   EncodeTiledFn enc = get_encode();
   if (!enc) return nullptr;
-  CUtensorMap* m = new CUtensorMap;
+  const bool cache_full = g_tmaps.size() >= kMaxCached;
+  static thread_local CUtensorMap ring[kRing];
+  static thread_local int ring_pos = 0;
+  CUtensorMap* m = cache_full ? &ring[ring_pos++ % kRing] : new CUtensorMap;
   cuuint32_t estr[5] = {1, 1, 1, 1, 1};
   CUresult r = enc(m, dt, (cuuint32_t)rank, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                    swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
@@ -84,10 +92,10 @@ static const CUtensorMap* encode_cached(const TmapKey& key, CUtensorMapDataType 
     set_last_error("cuTensorMapEncodeTiled failed: code %d (base %p, dims %llu x %llu, stride %llu, box %u x %u)", (int)r,
                    base, (unsigned long long)dims[0], (unsigned long long)dims[1], (unsigned long long)strides[0], box[0],
                    box[1]);
-    delete m;
+    if (!cache_full) delete m;
     return nullptr;
   }
-  g_tmaps.emplace(key, m);
+  if (!cache_full) g_tmaps.emplace(key, m);
   return m;
 }
 
@@ -202,6 +210,29 @@ extern "C" int dh_probe_flag_wait(const void* flag, uint32_t expect, long long b
 
 // Encodes a 4-D tensor map straight into caller-provided storage (no cache entry, no heap).
 namespace dh {
+bool encode_tmap_2d_into(CUtensorMap* out, const void* base, int elem_bytes, uint64_t inner, uint64_t outer,
+                         uint64_t row_stride_bytes, uint32_t box_inner, uint32_t box_outer, bool swizzle128) {
+  if ((reinterpret_cast<uintptr_t>(base) & 15) != 0 || (row_stride_bytes & 15) != 0) {
+    set_last_error("TMA operand must be 16-byte aligned with a 16-byte multiple row stride (base %p, stride %llu)", base,
+                   (unsigned long long)row_stride_bytes);
+    return false;
+  }
+  EncodeTiledFn enc = get_encode();
+  if (!enc) return false;
+  cuuint64_t dims[2] = {inner, outer};
+  cuuint64_t strides[1] = {row_stride_bytes};
+  cuuint32_t box[2] = {box_inner, box_outer};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(out, dtype_of(elem_bytes), 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    set_last_error("cuTensorMapEncodeTiled (output) failed: code %d (base %p, dims %llu x %llu, stride %llu)", (int)r, base,
+                   (unsigned long long)inner, (unsigned long long)outer, (unsigned long long)row_stride_bytes);
+    return false;
+  }
+  return true;
+}
 bool encode_tmap_4d_into(CUtensorMap* out, const void* base, int elem_bytes, const uint64_t dims[4], const uint64_t strides_bytes[3],
                          const uint32_t box[4], bool swizzle128) {
   if ((reinterpret_cast<uintptr_t>(base) & 15) != 0 || (strides_bytes[0] & 15) != 0 || (strides_bytes[1] & 15) != 0 ||

@@ -23,6 +23,11 @@ const CUtensorMap* get_tmap_3d(const void* base, int elem_bytes, uint64_t d0, ui
 const CUtensorMap* get_tmap_4d(const void* base, int elem_bytes, const uint64_t dims[4], const uint64_t strides_bytes[3],
                                const uint32_t box[4], bool swizzle128);
 
+// Encodes a 2-D map into caller-provided storage without touching the cache: for output tensors,
+// whose addresses change from call to call.  Returns false on failure.
+bool encode_tmap_2d_into(CUtensorMap* out, const void* base, int elem_bytes, uint64_t inner, uint64_t outer,
+                         uint64_t row_stride_bytes, uint32_t box_inner, uint32_t box_outer, bool swizzle128);
+
 void set_last_error(const char* fmt, ...);
 
 // cudaFuncSetAttribute applies to the function on the CURRENT device only, so "already

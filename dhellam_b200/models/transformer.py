@@ -148,7 +148,8 @@ def f_gemm_attn_c(run):
         # the gathered operand is not kept: the backward re-gathers the (8x smaller) shard
         shard = _use(run, run.v.pop("ln1_shard"))
         if _split_site(env, p.column_attn_weight):
-            qkv = G.gemm_nt(env.fused.gather_wait("attn_c"), p.column_attn_weight, sm_budget=run.budget("gemm_attn_c"))
+            full, sync = env.fused.gather_consume("attn_c")
+            qkv = G.gemm_nt(full, p.column_attn_weight, sm_budget=run.budget("gemm_attn_c"), sync=sync)
         else:
             qkv, _ = env.fused.ag_gemm(shard, p.column_attn_weight, "attn_c", sm_budget=run.budget("gemm_attn_c"))
         run.acts["ln1_shard"] = shard
@@ -189,8 +190,8 @@ def f_gemm_attn_l(run):
     env, p = run.env, run.params
     a = _use(run, run.v.pop("attn_out"))
     if env.fused_tp and _split_site(env, p.linear_attn_weight):
-        part = env.fused.partial_buffer("attn_l", a.shape[0], p.linear_attn_weight.shape[0])
-        G.gemm_nt(a, p.linear_attn_weight, out=part, sm_budget=run.budget("gemm_attn_l"))
+        part, sync = env.fused.partial_produce("attn_l", a.shape[0], p.linear_attn_weight.shape[0])
+        G.gemm_nt(a, p.linear_attn_weight, out=part, sm_budget=run.budget("gemm_attn_l"), sync=sync)
     elif env.fused_tp:
         run.v["proj"] = env.fused.gemm_rs(a, p.linear_attn_weight, "attn_l", sm_budget=run.budget("gemm_attn_l"))
     else:
@@ -235,7 +236,8 @@ def f_gemm_mlp_c(run):
     if env.fused_tp:
         shard = _use(run, run.v.pop("ln2_shard"))
         if _split_site(env, p.column_mlp_weight):
-            fc1 = G.gemm_nt(env.fused.gather_wait("mlp_c"), p.column_mlp_weight, sm_budget=run.budget("gemm_mlp_c"))
+            full, sync = env.fused.gather_consume("mlp_c")
+            fc1 = G.gemm_nt(full, p.column_mlp_weight, sm_budget=run.budget("gemm_mlp_c"), sync=sync)
         else:
             fc1, _ = env.fused.ag_gemm(shard, p.column_mlp_weight, "mlp_c", sm_budget=run.budget("gemm_mlp_c"))
         run.acts["ln2_shard"] = shard
@@ -261,8 +263,8 @@ def f_gemm_mlp_l(run):
     env, p = run.env, run.params
     a = _use(run, run.v.pop("act"))
     if env.fused_tp and _split_site(env, p.linear_mlp_weight):
-        part = env.fused.partial_buffer("mlp_l", a.shape[0], p.linear_mlp_weight.shape[0])
-        G.gemm_nt(a, p.linear_mlp_weight, out=part, sm_budget=run.budget("gemm_mlp_l"))
+        part, sync = env.fused.partial_produce("mlp_l", a.shape[0], p.linear_mlp_weight.shape[0])
+        G.gemm_nt(a, p.linear_mlp_weight, out=part, sm_budget=run.budget("gemm_mlp_l"), sync=sync)
     elif env.fused_tp:
         run.v["fc2"] = env.fused.gemm_rs(a, p.linear_mlp_weight, "mlp_l", sm_budget=run.budget("gemm_mlp_l"))
     else:
@@ -312,8 +314,8 @@ def b_gemm_dgrad_mlp_l(run):
     env, p = run.env, run.params
     if env.fused_tp and _split_site(env, p.linear_mlp_weight, True):
         _use(run, run.v.pop("d_fc2_shard"))
-        full = env.fused.gather_wait("mlp_l_bwd")
-        d_act = G.gemm_nn(full, p.linear_mlp_weight, sm_budget=run.budget("gemm_dgrad_mlp_l"))
+        full, sync = env.fused.gather_consume("mlp_l_bwd")
+        d_act = G.gemm_nn(full, p.linear_mlp_weight, sm_budget=run.budget("gemm_dgrad_mlp_l"), sync=sync)
         run.v["d_fc2_full"] = full
     elif env.fused_tp:
         d_act, full = env.fused.ag_gemm(_use(run, run.v.pop("d_fc2_shard")), p.linear_mlp_weight, "mlp_l_bwd", transpose_w=True,
@@ -343,8 +345,8 @@ def b_gemm_dgrad_mlp_c(run):
     env, p = run.env, run.params
     d_fc1 = _use(run, run.v["d_fc1"])
     if env.fused_tp and _split_site(env, p.column_mlp_weight, True):
-        part = env.fused.partial_buffer("mlp_c_bwd", d_fc1.shape[0], p.column_mlp_weight.shape[1])
-        G.gemm_nn(d_fc1, p.column_mlp_weight, out=part, sm_budget=run.budget("gemm_dgrad_mlp_c"))
+        part, sync = env.fused.partial_produce("mlp_c_bwd", d_fc1.shape[0], p.column_mlp_weight.shape[1])
+        G.gemm_nn(d_fc1, p.column_mlp_weight, out=part, sm_budget=run.budget("gemm_dgrad_mlp_c"), sync=sync)
     elif env.fused_tp:
         run.v["d_ln2"] = env.fused.gemm_rs(d_fc1, p.column_mlp_weight, "mlp_c_bwd", transpose_w=True,
                                            sm_budget=run.budget("gemm_dgrad_mlp_c"))
@@ -398,8 +400,8 @@ def b_gemm_dgrad_attn_l(run):
     env, p = run.env, run.params
     if env.fused_tp and _split_site(env, p.linear_attn_weight, True):
         _use(run, run.v.pop("d_proj_shard"))
-        full = env.fused.gather_wait("attn_l_bwd")
-        d_o = G.gemm_nn(full, p.linear_attn_weight, sm_budget=run.budget("gemm_dgrad_attn_l"))
+        full, sync = env.fused.gather_consume("attn_l_bwd")
+        d_o = G.gemm_nn(full, p.linear_attn_weight, sm_budget=run.budget("gemm_dgrad_attn_l"), sync=sync)
         run.v["d_proj_full"] = full
     elif env.fused_tp:
         d_o, full = env.fused.ag_gemm(_use(run, run.v.pop("d_proj_shard")), p.linear_attn_weight, "attn_l_bwd", transpose_w=True,
@@ -438,8 +440,8 @@ def b_gemm_dgrad_attn_c(run):
     env, p = run.env, run.params
     d_qkv = _use(run, run.v["d_qkv"])
     if env.fused_tp and _split_site(env, p.column_attn_weight, True):
-        part = env.fused.partial_buffer("attn_c_bwd", d_qkv.shape[0], p.column_attn_weight.shape[1])
-        G.gemm_nn(d_qkv, p.column_attn_weight, out=part, sm_budget=run.budget("gemm_dgrad_attn_c"))
+        part, sync = env.fused.partial_produce("attn_c_bwd", d_qkv.shape[0], p.column_attn_weight.shape[1])
+        G.gemm_nn(d_qkv, p.column_attn_weight, out=part, sm_budget=run.budget("gemm_dgrad_attn_c"), sync=sync)
     elif env.fused_tp:
         run.v["d_ln1"] = env.fused.gemm_rs(d_qkv, p.column_attn_weight, "attn_c_bwd", transpose_w=True,
                                            sm_budget=run.budget("gemm_dgrad_attn_c"))
@@ -515,8 +517,14 @@ def build_layer_program(cfg: ModelConfig, cp: int = 1) -> LayerProgram:
     P = LayerProgram(cfg.name)
     act_f, act_b = ("swiglu_mlp", "swiglu_bwd") if cfg.gated else ("gelu_mlp", "gelu_bwd")
 
+    # A reduce-scatter reads its GEMM's partial product row block by row block behind per-block counters,
+    # so it only needs the GEMM to have been LAUNCHED, not finished (the executor honours this when the
+    # engine runs the row-block-wise reduction; otherwise it is an ordinary dependency).
+    pipelined = {"reduce_scatter_attn": ("gemm_attn_l",), "reduce_scatter_mlp": ("gemm_mlp_l",),
+                 "reduce_scatter_mlp_c_bwd": ("gemm_dgrad_mlp_c",), "reduce_scatter_attn_c_bwd": ("gemm_dgrad_attn_c",)}
+
     def add(name, strand, kind, fn, deps, res, deferrable=False):
-        P.add(Op(name, strand, kind, fn, tuple(deps), res, _id(name), deferrable))
+        P.add(Op(name, strand, kind, fn, tuple(deps), res, _id(name), deferrable, pipelined.get(name, ())))
 
     # ------------------------------ forward strand
     add("ln_attn", FWD, COMPUTE, f_ln_attn, [], MEM)

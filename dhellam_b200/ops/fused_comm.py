@@ -125,6 +125,17 @@ class FusedTP:
         self.paired = True                # set by the engine before every layer run
         self.rs_ctas = int(os.environ.get("DHELLAM_RS_CTAS", "0")) or max(16, 128 // self.world)
         self.exposed = None               # the engine's ExposedTimer (set by the trainer); None = no measurement
+        # Tile-granular overlap between a GEMM and the collective beside it (split policy):
+        #   DHELLAM_AG_INKERNEL=1  the GEMM that consumes a gathered operand waits per 128-row block inside the kernel
+        #                          (own rows first) instead of behind a whole-buffer wait kernel;
+        #   DHELLAM_RS_BLOCKS=1    the GEMM that produces a partial product signals every finished row block to its
+        #                          owner, whose reduction kernel starts on a block as soon as all ranks delivered it.
+        # (not with two compute streams: a GEMM that spins on arrival counters holds every SM's shared memory, so the
+        #  other strand's GEMM, whose output some peer's push may be waiting for, could never start)
+        self.ag_inkernel = os.environ.get("DHELLAM_AG_INKERNEL", "1") != "0" and getattr(train, "compute_streams", 1) < 2
+        self.rs_blocks = os.environ.get("DHELLAM_RS_BLOCKS", "1") != "0"
+        self.total_sig = {t: [0, 0] for t in RS_TAGS}      # block-counter value reached so far, per (tag, slot)
+        self._sig_arrays = {}
 
     def split(self, M: int, N: int, Kd: int) -> bool:
         """Whether the collective beside the GEMM ``[M, Kd] x [Kd, N]`` runs as its own kernel."""
@@ -236,6 +247,21 @@ class FusedTP:
             K.check(fn(self.ptrs[self.rank] + self.off_agc[tag][slot], M // 128, target, s.cuda_stream), "dh_wait_counters")
         return self._stage_view(tag, slot, M, Kd)
 
+    def gather_consume(self, tag: str):
+        """For a GEMM that reads the gathered operand of ``tag`` as its A matrix: returns
+        ``(view, GemmSync or None)``.  With in-kernel waiting the kernel itself waits per 128-row
+        block for the arrival counters (own rows first); otherwise a whole-buffer wait kernel is
+        launched in front (also while exposed communication is being measured, so that the waiting
+        time shows up between events: an upper bound of what the in-kernel form exposes)."""
+        measuring = self.exposed is not None and self.exposed.enabled
+        if not self.ag_inkernel or measuring:
+            return self.gather_wait(tag), None
+        from .gemm import GemmSync
+        slot, target, M, Kd, ev = self._pending[tag].popleft()
+        sync = GemmSync(wait_count=self.ptrs[self.rank] + self.off_agc[tag][slot], wait_target=target, perm_mode=1,
+                        world=self.world, rank=self.rank)
+        return self._stage_view(tag, slot, M, Kd), sync
+
     def all_gather(self, shard, tag: str):
         self.gather_start(shard, tag)
         return self.gather_wait(tag)
@@ -248,14 +274,39 @@ class FusedTP:
         slot = self.calls_split[tag] & 1
         self.calls_split[tag] += 1
         off = self.off_split[tag][slot]
-        self._split_pending[tag] = (slot, (self.calls_split[tag] + 1) // 2, M, N)
+        self._split_pending[tag] = (slot, (self.calls_split[tag] + 1) // 2, M, N, None)
         return self.buf[off:off + M * N * 2].view(torch.bfloat16).view(M, N)
+
+    def partial_produce(self, tag: str, M: int, N: int):
+        """Like ``partial_buffer`` but for a GEMM that signals finished row blocks: returns
+        ``(buffer, GemmSync or None)``; ``rs_reduce(tag)`` then runs the row-block-wise reduction,
+        which may be launched as soon as the GEMM has been launched."""
+        buf = self.partial_buffer(tag, M, N)
+        if not self.rs_blocks or (M // self.world) % 128 != 0:
+            return buf, None
+        from .gemm import GemmSync
+        slot, use, _, _, _ = self._split_pending[tag]
+        tiles_n = (N + 255) // 256
+        self.total_sig[tag][slot] += self.world * 4 * tiles_n       # every rank: 4 epilogue warps per tile column
+        target = self.total_sig[tag][slot]
+        key = (tag, slot)
+        if key not in self._sig_arrays:
+            self._sig_arrays[key] = self._ptr_array(self.off_rsflag[tag][slot])
+        self._split_pending[tag] = (slot, use, M, N, target)
+        return buf, GemmSync(sig_ptrs=self._sig_arrays[key], sig_bpr=M // self.world // 128, perm_mode=2, world=self.world,
+                             rank=self.rank)
 
     def rs_reduce(self, tag: str):
         """Runs on the current stream, which must already wait for the GEMM that filled the buffer."""
-        slot, use, M, N = self._split_pending.pop(tag)
+        slot, use, M, N, block_target = self._split_pending.pop(tag)
         out = torch.empty((M // self.world, N), dtype=torch.bfloat16, device=self.device)
         s = torch.cuda.current_stream(self.device)
+        if block_target is not None:
+            fn = K.proto("dh_rs_reduce_blocks", [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_uint, c_int, c_void_p])
+            off = self.off_split[tag][slot]
+            K.check(fn(self._ptr_array(off), self._mc(off), self.ptrs[self.rank] + self.off_rsflag[tag][slot], out.data_ptr(), M, N,
+                       self.rank, self.world, block_target, self.rs_ctas, s.cuda_stream), "dh_rs_reduce_blocks")
+            return out
         fn = K.proto("dh_rs_reduce", [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_uint, c_int, c_void_p])
         off = self.off_split[tag][slot]
         K.check(fn(self._ptr_array(off), self._mc(off), self._ptr_array(self.off_rsflag[tag][slot]), out.data_ptr(), M, N, self.rank,

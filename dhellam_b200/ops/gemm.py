@@ -14,7 +14,7 @@ knob the dual-strand scheduler uses in place of the reference's TPC masks
 """
 from __future__ import annotations
 
-from ctypes import c_int, c_int64, c_void_p
+from ctypes import c_int, c_int64, c_uint, c_void_p
 
 import torch
 
@@ -22,6 +22,24 @@ from .. import kernels as K
 
 _GEMM_ARGS = [c_void_p, c_int64, c_int, c_void_p, c_int64, c_int, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_int,
               c_int, c_int, c_void_p]
+_GEMM_SYNC_ARGS = [c_void_p, c_int64, c_int, c_void_p, c_int64, c_int, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_int,
+                   c_int, c_void_p, c_uint, c_void_p, c_int, c_int, c_int, c_int, c_void_p]
+
+
+class GemmSync:
+    """Collective hooks of the CTA-pair GEMM (``dh_gemm_bf16_sync``), built by ``ops.fused_comm.FusedTP``.
+
+    ``wait_count`` / ``wait_target``: the A operand is an all-gather staging buffer; the kernel
+    waits per 128-row block for that block's arrival counter.  ``sig_ptrs`` / ``sig_bpr``: the
+    output is this rank's partial product of a reduce-scatter; after every stored row block the
+    kernel bumps the block's counter on the owning rank.  ``perm_mode``: row visiting order
+    (1 = own shard first then the others block by block, 2 = block by block over all owners)."""
+
+    def __init__(self, wait_count: int = 0, wait_target: int = 0, sig_ptrs=None, sig_bpr: int = 0, perm_mode: int = 0,
+                 world: int = 1, rank: int = 0):
+        self.wait_count, self.wait_target = wait_count, wait_target
+        self.sig_ptrs, self.sig_bpr = sig_ptrs, sig_bpr
+        self.perm_mode, self.world, self.rank = perm_mode, world, rank
 
 
 def _native(*ts) -> bool:
@@ -39,7 +57,15 @@ def _check2d(t, name):
         raise ValueError(f"{name} must be bfloat16, got {t.dtype}")
 
 
-def _launch(a, a_mn, b, b_mn, d, accumulate, M, N, Kdim, sm_budget, stream):
+def _launch(a, a_mn, b, b_mn, d, accumulate, M, N, Kdim, sm_budget, stream, sync: "GemmSync | None" = None):
+    if sync is not None:
+        fn = K.proto("dh_gemm_bf16_sync", _GEMM_SYNC_ARGS)
+        rc = fn(a.data_ptr(), a.stride(0), int(a_mn), b.data_ptr(), b.stride(0), int(b_mn), d.data_ptr(), d.stride(0),
+                int(d.dtype == torch.float32), int(accumulate), M, N, Kdim, int(sm_budget), sync.wait_count or None,
+                int(sync.wait_target), sync.sig_ptrs, int(sync.sig_bpr), int(sync.perm_mode), int(sync.world), int(sync.rank),
+                K.stream_ptr(stream))
+        K.check(rc, "dh_gemm_bf16_sync")
+        return
     fn = K.proto("dh_gemm_bf16", _GEMM_ARGS)
     rc = fn(a.data_ptr(), a.stride(0), int(a_mn), b.data_ptr(), b.stride(0), int(b_mn), d.data_ptr(), d.stride(0),
             int(d.dtype == torch.float32), int(accumulate), M, N, Kdim, 0, int(sm_budget), K.stream_ptr(stream))
@@ -52,8 +78,13 @@ def set_gemm_mode(mode: int):
     K.proto("dh_gemm_set_mode", [c_int], None)(int(mode))
 
 
-def gemm_nt(x, w, out=None, sm_budget: int = 0, stream=None, out_dtype=None):
-    """``x [M,K] @ w[N,K]ᵀ -> [M,N]``."""
+def set_gemm_splitk(n: int):
+    """K split of accumulating GEMMs (weight gradients): -1 heuristic (default), 0/1 off, n forced."""
+    K.proto("dh_gemm_set_splitk", [c_int], None)(int(n))
+
+
+def gemm_nt(x, w, out=None, sm_budget: int = 0, stream=None, out_dtype=None, sync: "GemmSync | None" = None):
+    """``x [M,K] @ w[N,K]ᵀ -> [M,N]``.  ``sync`` adds the collective hooks (GPU only)."""
     M, Kd = x.shape
     N = w.shape[0]
     assert w.shape[1] == Kd, (x.shape, w.shape)
@@ -69,12 +100,12 @@ def gemm_nt(x, w, out=None, sm_budget: int = 0, stream=None, out_dtype=None):
     _check2d(x, "x"), _check2d(w, "w")
     if out is None:
         out = torch.empty((M, N), dtype=out_dtype or torch.bfloat16, device=x.device)
-    _launch(x, False, w, False, out, False, M, N, Kd, sm_budget, stream)
+    _launch(x, False, w, False, out, False, M, N, Kd, sm_budget, stream, sync)
     return out
 
 
-def gemm_nn(dy, w, out=None, sm_budget: int = 0, stream=None):
-    """``dy [M,N] @ w[N,K] -> [M,K]``."""
+def gemm_nn(dy, w, out=None, sm_budget: int = 0, stream=None, sync: "GemmSync | None" = None):
+    """``dy [M,N] @ w[N,K] -> [M,K]``.  ``sync`` adds the collective hooks (GPU only)."""
     M, N = dy.shape
     Kd = w.shape[1]
     assert w.shape[0] == N, (dy.shape, w.shape)
@@ -91,7 +122,7 @@ def gemm_nn(dy, w, out=None, sm_budget: int = 0, stream=None):
     if out is None:
         out = torch.empty((M, Kd), dtype=torch.bfloat16, device=dy.device)
     # contraction over N: A = dy (K-major in the kernel's terms), B = w stored [N][K] = MN-major
-    _launch(dy, False, w, True, out, False, M, Kd, N, sm_budget, stream)
+    _launch(dy, False, w, True, out, False, M, Kd, N, sm_budget, stream, sync)
     return out
 
 

@@ -284,13 +284,17 @@ def check_buffer_reuse(program: LayerProgram, strategy: Strategy, effects: Dict[
                     raise RaceError(f"{launches[i].op} reduces {site} but no partial product was written")
                 tgt["reduced"] = True
                 tgt["readers"].append(i)
-                syncs.append((i, i))
+                # The reduction on rank R finishes only after every rank's GEMM has delivered every row
+                # block of R (per-block counters; or, in the whole-buffer form, after every rank announced,
+                # which it does after its GEMM).  So the contribution is the GEMM that wrote the partial
+                # product and the completion is the reduction.
+                syncs.append((tgt["writers"][0], i))
             else:
                 raise ValueError(f"unknown buffer action {action!r}")
 
     def ordered_across_ranks(r: int, w: int) -> bool:
         for c, d in syncs:
-            if r in before[c] and (d in before[w] or (d == w and c != d)):
+            if (r in before[c] or r == c) and r != d and (d in before[w] or d == w):
                 return True
         return False
 

@@ -104,6 +104,11 @@ class Executor:
         # schedule block (dhellam/core/dstb.py:1266); only the benchmark's composition arm sets it
         self.sync_per_block = sync_per_block and streams.cuda
         self.exposed = ExposedTimer()
+        # producers whose consumers synchronise with them inside the kernels: for those an event is also
+        # recorded BEFORE the producer runs, and the consumer waits for that one only
+        self.pipeline = False
+        self._pipelined_producers = {d for o in list(program.fwd.values()) + list(program.bwd.values()) for d in o.pipelined_deps}
+        self._pre_events: Dict[str, object] = {}
         self.strategy = strategy.completed(program)
         self.strategy.validate(program)
         self.streams = streams
@@ -215,6 +220,9 @@ class Executor:
                 stream.wait_event(ev)
         elif st.cuda:
             for d in op.deps:
+                if self.pipeline and d in op.pipelined_deps and d in self._pre_events:
+                    stream.wait_event(self._pre_events[d])     # ordered after the producer's launch point only
+                    continue
                 rec = self._events.get(d)
                 if rec is not None and rec[1] is not stream:   # produced on another stream
                     if rec[1] is st.s3 and self.exposed.enabled:
@@ -225,6 +233,10 @@ class Executor:
         if budget:
             run.sm_budget[op.name] = budget
         run.env.cur_stream = stream
+        if st.cuda and self.pipeline and op.name in self._pipelined_producers:
+            pre = self._pre_events.get(op.name) or torch.cuda.Event()
+            pre.record(stream)
+            self._pre_events[op.name] = pre
         if self.nvtx:
             torch.cuda.nvtx.range_push(f"{'F' if op.strand == FWD else 'B'}:{op.name} L{run.layer_index} mb{getattr(run.mb, 'index', -1)}")
         with st.ctx(stream):

@@ -31,6 +31,9 @@ class Op:
     op_id: int = -1
     # deferred-wgrad support: ops named here may be postponed to a "<name>_n" marker
     deferrable: bool = False
+    # dependencies that are synchronised INSIDE the kernels (per-row-block counters): when the
+    # engine enables it, this op may start as soon as such a producer has been launched
+    pipelined_deps: Tuple[str, ...] = ()
 
 
 class LayerProgram:

@@ -84,6 +84,8 @@ class Trainer:
                                compute_streams=1 if (single_stream or not train.dhellam) else train.compute_streams)
         if fused is not None:
             fused.exposed = self.engine.executor.exposed
+            # row-block-wise reduce-scatter: the reduction kernel may start once its GEMM has been launched
+            self.engine.executor.pipeline = fused.rs_blocks and fused.policy == "split"
         self.optimizer = MixedPrecisionAdam(self.model, train, self.ps, distributed=distributed_optimizer)
         if self.ps.dp * self.ps.cp > 1 and not distributed_optimizer:
             from .parallel.dp import OverlappedGradReducer
@@ -119,6 +121,20 @@ class Trainer:
             GLOBAL_VARIABLES["loss"] = loss
             return loss
         return None
+
+    def close(self):
+        """Drops every reference this trainer (and the module-level blackboard) holds to the model,
+        the optimizer state and the symmetric buffers, so that their device memory can be freed
+        before another trainer is built in the same process."""
+        if GLOBAL_VARIABLES.get("loss_scale_func") == getattr(self.optimizer, "scale_loss", None):
+            GLOBAL_VARIABLES.pop("loss_scale_func", None)
+        GLOBAL_VARIABLES.pop("loss", None)
+        if self.engine is not None:
+            self.engine.grad_reducer = None
+            self.engine.executor = None
+        if self.env is not None:
+            self.env.fused = None
+        self.engine = self.optimizer = self.model = self.env = None
 
     def tokens_per_step(self) -> int:
         return self.train.global_batch_size * self.cfg.seq_length

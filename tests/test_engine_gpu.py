@@ -74,3 +74,46 @@ def test_gpu_training_loss_decreases():
     mbs = synthetic_step_batches(cfg, train, tr.ps, 0, "cuda")
     losses = [float(tr.train_step(mbs)) for _ in range(8)]
     assert losses[-1] < losses[0] - 0.5, losses
+
+
+def test_library_backend_composition_matches_native_and_frees_memory():
+    """The benchmark's composition arm (PyTorch / cuBLAS / flash-attn ops, the reference's 17-block
+    schedule, one device synchronisation per block) trains the same model to the same losses as
+    the native kernels, and ``Trainer.close`` really releases the first trainer's memory."""
+    import gc
+    from dhellam_b200 import kernels as K
+    from dhellam_b200.config import ParallelConfig, TrainConfig
+    from dhellam_b200.data import synthetic_step_batches
+    from dhellam_b200.models.sharding import random_full_head, random_full_layer
+    from dhellam_b200.parallel import state as PS
+    from dhellam_b200.trainer import Trainer
+    cfg = _cfgs("llama")
+    layers = [random_full_layer(cfg, i, 5) for i in range(cfg.num_layers)]
+    head = random_full_head(cfg, 5)
+    out = {}
+    try:
+        for backend in ("native", "library"):
+            K.set_backend(backend)
+            PS.set_state(None)
+            train = TrainConfig(micro_batch_size=2, global_batch_size=4, dtype="bf16", lr=1e-3, weight_decay=0.0,
+                                reference_schedule=(backend == "library"), sync_per_block=(backend == "library"))
+            tr = Trainer(cfg, ParallelConfig(), train, device="cuda")
+            for i, w in enumerate(layers):
+                tr.model.load_full_layer_weights(i, {k: v.to("cuda") for k, v in w.items()})
+            tr.model.load_full_head_weights({k: v.to("cuda") for k, v in head.items()})
+            tr.optimizer.reload_master_from_params() if hasattr(tr.optimizer, "reload_master_from_params") else \
+                tr.optimizer.master.copy_(tr.model.flat_param[tr.optimizer.lo:tr.optimizer.hi].float())
+            before = K.launch_count()
+            out[backend] = [float(tr.train_step(synthetic_step_batches(cfg, train, tr.ps, s, "cuda"))) for s in range(3)]
+            if backend == "library":
+                assert K.launch_count() == before, "the composition arm must not call into the kernel library"
+            tr.close()
+            del tr
+            gc.collect()
+            torch.cuda.empty_cache()
+            assert torch.cuda.memory_allocated() < 64 * 2**20, torch.cuda.memory_allocated()
+    finally:
+        K.set_backend("native")
+    for a, b in zip(out["native"], out["library"]):
+        assert abs(a - b) / abs(a) < 2e-2, out
+    assert out["library"][-1] < out["library"][0], out

@@ -66,3 +66,24 @@ def test_moe_engine_matches_autograd():
             for n in m.shapes:
                 g = getattr(m, f"{n}_{which}").main_grad
                 assert torch.isfinite(g).all()
+
+
+def test_trainer_close_releases_model_and_optimizer_state():
+    import gc
+    import weakref
+    from dhellam_b200.config import ParallelConfig, TrainConfig, preset
+    from dhellam_b200.data import synthetic_step_batches
+    from dhellam_b200.parallel import state as PS
+    from dhellam_b200.trainer import Trainer
+    cfg = preset("tiny-llama", seq_length=32)
+    train = TrainConfig(micro_batch_size=1, global_batch_size=2, dtype="fp32")
+    PS.set_state(None)
+    tr = Trainer(cfg, ParallelConfig(), train, device="cpu")
+    loss = tr.train_step(synthetic_step_batches(cfg, train, tr.ps, 0, "cpu"))
+    w_param, w_master = weakref.ref(tr.model.flat_param), weakref.ref(tr.optimizer.master)
+    del loss
+    tr.close()
+    del tr
+    gc.collect()
+    assert w_param() is None and w_master() is None
+    PS.set_state(None)

@@ -52,6 +52,47 @@ def test_gemm_three_layouts(M, N, K_, gemm_mode):
     assert rel(g2, dy.float().t() @ x.float()) < 1e-4
 
 
+@pytest.mark.parametrize("split", [2, 3, 4])
+def test_gemm_weight_gradient_split_along_k_adds_atomically(split):
+    """An accumulating GEMM may be cut into ``split`` work items per tile that each add their share
+    into the fp32 output with the reducing bulk store; the result must not depend on the split."""
+    from dhellam_b200.ops.gemm import gemm_tn_acc, set_gemm_mode, set_gemm_splitk
+    set_gemm_mode(2)
+    try:
+        for M, N, K_ in ((4096, 520, 392), (1000, 256, 256), (8192, 1280, 512)):
+            dy, x = bf(M, N), bf(M, K_)
+            ref = 3.0 + dy.float().t() @ x.float()
+            set_gemm_splitk(split)
+            g = torch.full((N, K_), 3.0, device=DEV)
+            gemm_tn_acc(dy, x, g)
+            assert rel(g, ref) < 1e-4, (M, N, K_, rel(g, ref))
+    finally:
+        set_gemm_splitk(-1)
+        set_gemm_mode(0)
+
+
+@pytest.mark.parametrize("M,N,K_,kind", [(16384, 1280, 8192, "nt"), (16384, 8192, 1024, "nt"), (16384, 7168, 8192, "nn"),
+                                         (16384, 16032, 2048, "nt"), (16384, 3584, 8192, "tn"), (16384, 1280, 8192, "tn")])
+def test_gemm_headline_shapes_against_fp32(M, N, K_, kind):
+    """The per-GPU shapes of the 8-way tensor-parallel headline run (16384 rows) against an fp32 product."""
+    from dhellam_b200.ops.gemm import gemm_nn, gemm_nt, gemm_tn_acc
+    if kind == "nt":
+        x, w = bf(M, K_), bf(N, K_, scale=0.05)
+        got, ref = gemm_nt(x, w), x.float() @ w.float().t()
+        tol = 5e-3
+    elif kind == "nn":
+        dy, w = bf(M, N), bf(N, K_, scale=0.05)
+        got, ref = gemm_nn(dy, w), dy.float() @ w.float()
+        tol = 5e-3
+    else:
+        dy, x = bf(M, N, scale=0.1), bf(M, K_)
+        got = torch.ones(N, K_, device=DEV)
+        gemm_tn_acc(dy, x, got)
+        ref = 1 + dy.float().t() @ x.float()
+        tol = 1e-4
+    assert rel(got, ref) < tol, rel(got, ref)
+
+
 def test_gemm_sm_budget_and_strided_output(gemm_mode):
     from dhellam_b200.ops.gemm import gemm_nt
     x, w = bf(512, 512), bf(768, 512)

@@ -79,6 +79,7 @@ def _fused_worker(rank, world, rows, h, n_out, iters):
     cfg = ModelConfig(hidden_size=h, seq_length=rows, num_attention_heads=h // 128, num_query_groups=h // 128)
     fused = FusedTP(ps, cfg, TrainConfig(micro_batch_size=1), dev, max_rows=rows, width=h)
     torch.manual_seed(100 + rank)
+    side = torch.cuda.Stream()
     for it in range(iters):
         shard = (torch.randn(rows // world, h, device=dev)).to(torch.bfloat16)
         w = (torch.randn(n_out, h, device=dev) * 0.05).to(torch.bfloat16)
@@ -115,6 +116,36 @@ def _fused_worker(rank, world, rows, h, n_out, iters):
             got4 = fused.rs_reduce("attn_l")
             fused.mc_ptr = keep
             assert _rel(got4, ref) < 1e-2, (_rel(got4, ref), mc)
+        # tile-granular forms: the GEMM waits per 128-row block for the pushed rows inside the kernel (own shard
+        # first), and the producing GEMM signals finished row blocks to the reduction kernel, which is launched
+        # on another stream right after the GEMM's launch point
+        fused.gather_start(shard, "attn_c", stream=side)
+        view, sync = fused.gather_consume("attn_c")
+        assert sync is not None
+        out5 = gemm_nt(view, w, sync=sync)
+        torch.cuda.synchronize()
+        assert torch.equal(view, full_ref) and _rel(out5, gemm_nt(full_ref, w)) < 1e-3
+        fused.gather_start(shard, "mlp_l_bwd", stream=side)
+        view, sync = fused.gather_consume("mlp_l_bwd")
+        out6 = gemm_nn(view, wt, sync=sync)
+        assert _rel(out6, gemm_nn(full_ref, wt)) < 1e-3
+        for mc in (fused.mc_ptr, 0):
+            keep, fused.mc_ptr = fused.mc_ptr, mc
+            part, sync = fused.partial_produce("mlp_l", rows, h)
+            assert sync is not None
+            launched = torch.cuda.Event()
+            launched.record()
+            gemm_nt(a, w2, out=part, sync=sync)
+            side.wait_event(launched)
+            with torch.cuda.stream(side):
+                got7 = fused.rs_reduce("mlp_l")
+            torch.cuda.current_stream().wait_stream(side)
+            fused.mc_ptr = keep
+            assert _rel(got7, ref) < 1e-2, (_rel(got7, ref), mc)
+            part, sync = fused.partial_produce("mlp_c_bwd", rows, h)
+            gemm_nn(a, w3, out=part, sync=sync)
+            got8 = fused.rs_reduce("mlp_c_bwd")
+            assert _rel(got8, ref3) < 1e-2, _rel(got8, ref3)
     torch.cuda.synchronize()
     st = K.read_status()
     assert st.code == 0, (st.code, st.where, st.extra)
