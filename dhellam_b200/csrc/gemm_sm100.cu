@@ -16,6 +16,7 @@
 // (csrc/operators/gemm.cu:3-142) and of torch.matmul / torch.addmm(out=main_grad) on
 // its training path (dhellam/operators/layernorm_column.py:32,239,290-292).
 #include "api.h"
+#include "comm_device.cuh"
 #include "ptx.cuh"
 #include "tmap.h"
 
@@ -346,7 +347,9 @@ struct __align__(8) Control2 {
   uint64_t acc_empty[NUM_ACC];
   uint32_t tmem_base;
   int abort_flag;
+  int comm_flag;
 };
+constexpr int COMM_THREADS = 64;                   // two communication warps per CTA in the COMM form of the kernel
 constexpr int SMEM2_BYTES = RING * STAGE2_BYTES + EPI_BYTES + 1024 + 256;
 
 struct PairParams {
@@ -363,6 +366,11 @@ struct PairParams {
   int perm_mode, perm_world, perm_rank;
   long long wait_budget;               // cycles for the barriers inside the CTA
   DeviceStatus* status;
+  // collective carried by the communication warps (COMM form of the kernel only):
+  // 0 none, 1 = push this rank's shard of the gathered A operand, 2 = reduce this rank's rows of the partial products
+  int comm_kind;
+  comm::PushJob push;
+  comm::ReduceJob reduce;
 };
 
 __device__ __forceinline__ int perm_tile_m(int i, const PairParams& p) {
@@ -408,8 +416,12 @@ __device__ __forceinline__ bool wait_block_counter(const uint32_t* c, uint32_t w
   }
 }
 
-template <bool A_MN, bool B_MN, bool OUT_F32>
-__global__ void __launch_bounds__(THREADS, 1)
+// COMM = true adds two communication warps to every CTA (256 threads instead of 192): they carry the
+// collective that belongs to this GEMM (the push of this rank's shard of the gathered A operand, or the
+// row-block-wise reduction of the partial products this GEMM and its peers signal), spread evenly over all
+// SMs, so that compute and transfer are ONE kernel and no SM carries more communication work than another.
+template <bool A_MN, bool B_MN, bool OUT_F32, bool COMM>
+__global__ void __launch_bounds__(COMM ? THREADS + COMM_THREADS : THREADS, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                  const __grid_constant__ CUtensorMap tmap_d, const PairParams p) {
   extern __shared__ uint8_t smem_raw[];
@@ -438,6 +450,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       mbar_init(&ctl->acc_empty[a], 8);
     }
     ctl->abort_flag = 0;
+    ctl->comm_flag = 1;
     mbar_fence_init();
   }
   if (warp == 1) {
@@ -538,6 +551,15 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       }
     }
     __syncwarp();
+  } else if (COMM && warp >= 6) {
+    // ------------------------------ communication warps (both CTAs) -----------
+    const int tid = (int)threadIdx.x - THREADS;
+    auto group_sync = [] { asm volatile("bar.sync 1, 64;" ::: "memory"); };
+    if (p.comm_kind == 1) {
+      comm::push_rows(p.push, (int)blockIdx.x, (int)gridDim.x, tid, COMM_THREADS, group_sync);
+    } else if (p.comm_kind == 2) {
+      comm::reduce_rows(p.reduce, (int)blockIdx.x, (int)gridDim.x, tid, COMM_THREADS, group_sync, &ctl->comm_flag, p.status, 665);
+    }
   } else {
     // ------------------------------ epilogue (both CTAs) ----------------------
     constexpr int CH_COLS = OUT_F32 ? 32 : 64;      // columns per 128-byte chunk
@@ -624,10 +646,10 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   }
 }
 
-template <bool A_MN, bool B_MN, bool OUT_F32>
+template <bool A_MN, bool B_MN, bool OUT_F32, bool COMM = false>
 static int launch_pair(const CUtensorMap* ta, const CUtensorMap* tb, const CUtensorMap* td, const PairParams& p, int pairs,
                        cudaStream_t stream) {
-  auto kern = gemm_pair_kernel<A_MN, B_MN, OUT_F32>;
+  auto kern = gemm_pair_kernel<A_MN, B_MN, OUT_F32, COMM>;
   static PerDeviceFlags configured_on;
   bool& configured = device_flag(configured_on);
   if (!configured) {
@@ -640,7 +662,7 @@ static int launch_pair(const CUtensorMap* ta, const CUtensorMap* tb, const CUten
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(2 * pairs);
-  cfg.blockDim = dim3(THREADS);
+  cfg.blockDim = dim3(COMM ? THREADS + COMM_THREADS : THREADS);
   cfg.dynamicSmemBytes = SMEM2_BYTES;
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
@@ -715,6 +737,9 @@ struct SyncArgs {
   void* const* sig_ptrs = nullptr;
   int sig_bpr = 0;
   int perm_mode = 0, world = 1, rank = 0;
+  int comm_kind = 0;                       // collective carried by the kernel's own communication warps
+  const comm::PushJob* push = nullptr;
+  const comm::ReduceJob* reduce = nullptr;
 };
 
 static int gemm_impl(const void* a, int64_t lda, int a_mn_major, const void* b, int64_t ldb, int b_mn_major, void* d, int64_t ldd,
@@ -790,10 +815,18 @@ static int gemm_impl(const void* a, int64_t lda, int a_mn_major, const void* b, 
     // barriers inside the CTA sit downstream of a peer wait, so they must outlast it
     p.wait_budget = (p.wait_count != nullptr) ? 2 * PEER_WAIT_CYCLES : (long long)DH_WAIT_BUDGET_CYCLES;
     const int num_items = num_tiles * p.split_k;
-    if (pairs > num_items) pairs = num_items;
+    if (sy.comm_kind == 0 && pairs > num_items) pairs = num_items;     // the communication warps use every CTA of the budget
     CUtensorMap td;
     if (!encode_tmap_2d_into(&td, d, d_fp32 ? 4 : 2, (uint64_t)N, (uint64_t)M, (uint64_t)ldd * (d_fp32 ? 4 : 2), d_fp32 ? 32 : 64, 32, true))
       return (int)cudaErrorInvalidValue;
+    if (sy.comm_kind != 0) {
+      if (a_mn_major || d_fp32) { set_last_error("dh_gemm_bf16: a GEMM that carries a collective has a K-major A and a bf16 output"); return (int)cudaErrorInvalidValue; }
+      p.comm_kind = sy.comm_kind;
+      if (sy.push) p.push = *sy.push;
+      if (sy.reduce) p.reduce = *sy.reduce;
+      return b_mn_major ? launch_pair<false, true, false, true>(ta, tb, &td, p, pairs, stream)
+                        : launch_pair<false, false, false, true>(ta, tb, &td, p, pairs, stream);
+    }
     switch (sel) {
       case 0: return launch_pair<false, false, false>(ta, tb, &td, p, pairs, stream);
       case 1: return launch_pair<false, false, true>(ta, tb, &td, p, pairs, stream);
@@ -868,4 +901,62 @@ extern "C" int dh_gemm_bf16_sync(const void* a, int64_t lda, int a_mn_major, con
   sy.world = world;
   sy.rank = rank;
   return dh::gemm::gemm_impl(a, lda, a_mn_major, b, ldb, b_mn_major, d, ldd, d_fp32, accumulate, M, N, K, sm_budget, sy, stream);
+}
+
+int dh_fill_push_job(dh::comm::PushJob& p, const char* who, const void* shard, void* const* stage_ptrs, void* const* count_ptrs,
+                     void* stage_mc, int M, int K, int rank, int world, int slices);
+int dh_fill_reduce_job(dh::comm::ReduceJob& p, const char* who, void* const* part_ptrs, const void* part_mc, const void* ready, void* out,
+                       int M, int N, int rank, int world, unsigned target, int slices);
+
+// Sequence all-gather -> GEMM in ONE kernel: the communication warps of every CTA push this rank's
+// [M / world, K] shard into every rank's staging buffer (multimem.st through the switch, or per-peer
+// stores) and raise the per-row-block arrival counters, while the tensor-core warps multiply the staged
+// operand, own rows first, waiting per 128-row block for its counter and reading local memory only.
+//   stage_ptrs / count_ptrs: `world` device pointers (index = rank); stage_mc: multicast alias or null
+//   target_base: counter value before this call; every counter rises by `slices`
+// After the call the local staging buffer holds the gathered [M, K] operand (kept for the weight gradient).
+extern "C" int dh_ag_gemm_bf16(const void* shard, void* const* stage_ptrs, void* const* count_ptrs, void* stage_mc, const void* b,
+                               int64_t ldb, int b_mn_major, void* d, int64_t ldd, int M, int N, int K, int rank, int world, int slices,
+                               unsigned target_base, int sm_budget, cudaStream_t stream) {
+  dh::comm::PushJob job;
+  int rc = dh_fill_push_job(job, "dh_ag_gemm_bf16", shard, stage_ptrs, count_ptrs, stage_mc, M, K, rank, world, slices);
+  if (rc) return rc;
+  dh::gemm::SyncArgs sy;
+  sy.wait_count = count_ptrs[rank];
+  sy.wait_target = target_base + (unsigned)slices;
+  sy.perm_mode = 1;
+  sy.world = world;
+  sy.rank = rank;
+  sy.comm_kind = 1;
+  sy.push = &job;
+  return dh::gemm::gemm_impl(stage_ptrs[rank], K, 0, b, ldb, b_mn_major, d, ldd, 0, 0, M, N, K, sm_budget, sy, stream);
+}
+
+// GEMM -> sequence reduce-scatter in ONE kernel: the tensor-core warps write this rank's partial product
+// [M, N] into its symmetric buffer, row block by row block over all owners, and signal every finished row
+// block to its owner; the communication warps of the same kernel reduce this rank's own rows as soon as
+// every rank has delivered a block (in-switch multimem.ld_reduce, or peer loads) into out [M / world, N].
+//   part_ptrs / ready_ptrs: `world` device pointers (every rank's partial buffer and per-block counters)
+//   target: the counter value of a block that every rank has delivered in this call
+extern "C" int dh_gemm_rs_bf16(const void* a, int64_t lda, const void* b, int64_t ldb, int b_mn_major, void* const* part_ptrs,
+                               const void* part_mc, void* const* ready_ptrs, void* out, int M, int N, int K, int rank, int world,
+                               unsigned target, int sm_budget, cudaStream_t stream) {
+  if (world < 2 || world > 8 || M % (world * 128) != 0) {
+    dh::set_last_error("dh_gemm_rs_bf16: world %d / M %d: need 2..8 ranks and M divisible by world*128", world, M);
+    return (int)cudaErrorInvalidValue;
+  }
+  const int blocks = M / world / 128;
+  dh::comm::ReduceJob job;
+  int rc = dh_fill_reduce_job(job, "dh_gemm_rs_bf16", part_ptrs, part_mc, ready_ptrs[rank], out, M, N, rank, world, target,
+                              dh::comm::slices_for(blocks, N, dh_sm_count()));
+  if (rc) return rc;
+  dh::gemm::SyncArgs sy;
+  sy.sig_ptrs = ready_ptrs;
+  sy.sig_bpr = blocks;
+  sy.perm_mode = 2;
+  sy.world = world;
+  sy.rank = rank;
+  sy.comm_kind = 2;
+  sy.reduce = &job;
+  return dh::gemm::gemm_impl(a, lda, 0, b, ldb, b_mn_major, part_ptrs[rank], N, 0, 0, M, N, K, sm_budget, sy, stream);
 }

@@ -58,8 +58,13 @@ class FusedTP:
         self.ps, self.device = ps, torch.device(device)
         self.world, self.rank = ps.tp, ps.tp_rank
         # the shard a rank pushes is 1/tp of the operand: fewer ranks -> more bytes per rank -> more copy CTAs
-        self.copy_ctas = copy_ctas or max(8, 64 // self.world)
-        self.push_ctas = push_ctas or max(16, 96 // self.world)
+        self.sms = K.lib().dh_sm_count()
+        # Stand-alone communication kernels: how many CTAs of how many threads.  DHELLAM_COMM_SPREAD=1 launches one
+        # small CTA per SM (64 threads), which loads every SM equally beside a statically scheduled persistent GEMM;
+        # the default is a few 256-thread CTAs.
+        spread = os.environ.get("DHELLAM_COMM_SPREAD", "0") == "1"
+        self.comm_threads = 64 if spread else 256
+        self.push_ctas = push_ctas or int(os.environ.get("DHELLAM_PUSH_CTAS", "0")) or (self.sms if spread else max(16, 96 // self.world))
         rows = max_rows or train.micro_batch_size * cfg.seq_length // max(ps.cp, 1)
         width = width or cfg.hidden_size
         assert rows % (self.world * 128) == 0, "rows per micro-batch must divide by tp x 128 for the fused kernels"
@@ -67,20 +72,16 @@ class FusedTP:
         self.blocks = rows // 128
         stage_bytes = rows * width * 2
         cnt_bytes = _align(max(self.blocks, self.world) * 4)
-        # layout: AG staging (tag x 2) | RS partial slots x 2 | AG counters (tag x 2) | RS counters x 2
+        # layout: AG staging (tag x 2) | AG counters (tag x 2) | RS counters / flags (tag x 2) | RS partial products (tag x 2)
         self.off_stage, self.off_agc = {}, {}
         off = 0
         for t in AG_TAGS:
             self.off_stage[t] = [off, off + stage_bytes]
             off += 2 * stage_bytes
-        self.off_part = [off, off + stage_bytes]
-        off += 2 * stage_bytes
         cnt_base = off
         for t in AG_TAGS:
             self.off_agc[t] = [off, off + cnt_bytes]
             off += 2 * cnt_bytes
-        self.off_rsc = [off, off + cnt_bytes]
-        off += 2 * cnt_bytes
         self.off_rsflag = {}
         for t in RS_TAGS:
             self.off_rsflag[t] = [off, off + cnt_bytes]
@@ -107,8 +108,6 @@ class FusedTP:
         dist.barrier(group=group)                 # nobody pushes before every rank's counters are zero
         self.total_ag = {t: [0, 0] for t in AG_TAGS}     # counter value reached so far, per (tag, parity)
         self.calls_ag = {t: 0 for t in AG_TAGS}
-        self.total_rs = [0, 0]
-        self.n_rs = 0
         self._last = None
         self._arr = ctypes.c_void_p * self.world
         self._pending = {}
@@ -123,7 +122,7 @@ class FusedTP:
         # are within 1%.
         self.policy = os.environ.get("DHELLAM_FUSED_POLICY", "split")
         self.paired = True                # set by the engine before every layer run
-        self.rs_ctas = int(os.environ.get("DHELLAM_RS_CTAS", "0")) or max(16, 128 // self.world)
+        self.rs_ctas = int(os.environ.get("DHELLAM_RS_CTAS", "0")) or (self.sms if spread else max(16, 128 // self.world))
         self.exposed = None               # the engine's ExposedTimer (set by the trainer); None = no measurement
         # Tile-granular overlap between a GEMM and the collective beside it (split policy):
         #   DHELLAM_AG_INKERNEL=1  the GEMM that consumes a gathered operand waits per 128-row block inside the kernel
@@ -167,18 +166,26 @@ class FusedTP:
         ev.record(s)
         self._last = ev
 
-    def _next_ag(self, tag, M, Kd):
+    def _slices(self, blocks: int, width: int, groups: int) -> int:
+        """Column slices per 128-row block such that (blocks x slices) work items keep ``groups`` thread groups busy."""
+        return K.proto("dh_comm_slices", [c_int, c_int, c_int])(int(blocks), int(width), int(groups))
+
+    def _next_ag(self, tag, M, Kd, groups: int):
+        """Reserves the next staging slot of ``tag``.  Returns ``(slot, counter value before, slices)``; every
+        row-block counter of the slot rises by ``slices`` in this call."""
         slot = self.calls_ag[tag] & 1
         self.calls_ag[tag] += 1
         before = self.total_ag[tag][slot]
-        slices = K.proto("dh_ag_slices", [c_int, c_int, c_int])(M, Kd, self.world)
+        slices = self._slices(M // self.world // 128, Kd, groups)
         self.total_ag[tag][slot] = before + slices
-        return slot, before
+        return slot, before, slices
 
     # ------------------------------------------------------------------ fused ops
     def ag_gemm(self, shard, w, tag: str, transpose_w: bool = False, sm_budget: int = 0):
         """``shard [M/t, K]``; ``w [N, K]`` (or ``[K, N']`` with ``transpose_w``: the product is
-        ``gathered @ w``).  Returns ``(out [M, N], gathered [M, K] view of the staging buffer)``."""
+        ``gathered @ w``).  ONE kernel: the communication warps of the CTA-pair GEMM push the shard
+        to every rank while its tensor-core warps multiply the staged operand, own rows first.
+        Returns ``(out [M, N], gathered [M, K] view of the staging buffer)``."""
         rows_local, Kd = shard.shape
         M = rows_local * self.world
         assert M == self.rows, "the fused all-gather works on full micro-batches (fixed row count per group)"
@@ -186,32 +193,35 @@ class FusedTP:
         N = w.shape[1] if transpose_w else w.shape[0]
         assert (w.shape[0] if transpose_w else w.shape[1]) == Kd
         out = torch.empty((M, N), dtype=torch.bfloat16, device=self.device)
-        slot, before = self._next_ag(tag, M, Kd)
+        slot, before, slices = self._next_ag(tag, M, Kd, self.sms)
         s = self._chain()
         fn = K.proto("dh_ag_gemm_bf16", [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_void_p, c_int64, c_int,
                                           c_int, c_int, c_int, c_int, c_int, c_uint, c_int, c_void_p])
         K.check(fn(shard.data_ptr(), self._ptr_array(self.off_stage[tag][slot]), self._ptr_array(self.off_agc[tag][slot]),
                    self._mc(self.off_stage[tag][slot]), w.data_ptr(), w.stride(0), int(transpose_w), out.data_ptr(), out.stride(0),
-                   M, N, Kd, self.rank, self.world, self.copy_ctas, before, int(sm_budget), s.cuda_stream), "dh_ag_gemm_bf16")
+                   M, N, Kd, self.rank, self.world, slices, before, int(sm_budget), s.cuda_stream), "dh_ag_gemm_bf16")
         self._done(s)
         return out, self._stage_view(tag, slot, M, Kd)
 
-    def gemm_rs(self, a, w, tag: str = "", transpose_w: bool = False, sm_budget: int = 0):
-        """``a [M, K]``; returns this rank's ``[M/t, N]`` shard of ``sum_ranks(a @ op(w))``."""
+    def gemm_rs(self, a, w, tag: str = "attn_l", transpose_w: bool = False, sm_budget: int = 0):
+        """``a [M, K]``; returns this rank's ``[M/t, N]`` shard of ``sum_ranks(a @ op(w))``.  ONE kernel:
+        the tensor-core warps write and signal the partial product row block by row block, the
+        communication warps reduce this rank's rows as the blocks complete on all ranks."""
         M, Kd = a.shape
         assert M == self.rows and a.dtype == torch.bfloat16 and a.stride(1) == 1
         N = w.shape[1] if transpose_w else w.shape[0]
-        assert (w.shape[0] if transpose_w else w.shape[1]) == Kd and N <= self.width
+        assert (w.shape[0] if transpose_w else w.shape[1]) == Kd and N <= self.width and tag in self.off_split
         out = torch.empty((M // self.world, N), dtype=torch.bfloat16, device=self.device)
-        slot = self.n_rs & 1
-        self.n_rs += 1
-        before = self.total_rs[slot]
-        self.total_rs[slot] = before + (M // self.world // 128) * ((N + 255) // 256) * 4
+        slot = self.calls_split[tag] & 1
+        self.calls_split[tag] += 1
+        self.total_sig[tag][slot] += self.world * 4 * ((N + 255) // 256)
+        target = self.total_sig[tag][slot]
+        off = self.off_split[tag][slot]
         s = self._chain()
-        fn = K.proto("dh_gemm_rs_bf16", [c_void_p, c_int64, c_void_p, c_int64, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
-                                          c_int, c_int, c_uint, c_int, c_void_p])
-        K.check(fn(a.data_ptr(), a.stride(0), w.data_ptr(), w.stride(0), int(transpose_w), self._ptr_array(self.off_part[slot]),
-                   self._ptr_array(self.off_rsc[slot]), out.data_ptr(), M, N, Kd, self.rank, self.world, before,
+        fn = K.proto("dh_gemm_rs_bf16", [c_void_p, c_int64, c_void_p, c_int64, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                                          c_int, c_int, c_int, c_uint, c_int, c_void_p])
+        K.check(fn(a.data_ptr(), a.stride(0), w.data_ptr(), w.stride(0), int(transpose_w), self._ptr_array(off), self._mc(off),
+                   self._ptr_array(self.off_rsflag[tag][slot]), out.data_ptr(), M, N, Kd, self.rank, self.world, target,
                    int(sm_budget), s.cuda_stream), "dh_gemm_rs_bf16")
         self._done(s)
         return out
@@ -223,16 +233,16 @@ class FusedTP:
         rows_local, Kd = shard.shape
         M = rows_local * self.world
         assert M == self.rows and Kd == self.width and shard.dtype == torch.bfloat16 and shard.is_contiguous()
-        slot, before = self._next_ag(tag, M, Kd)
+        slot, before, slices = self._next_ag(tag, M, Kd, self.push_ctas)
         cur = torch.cuda.current_stream(self.device)
         s = stream if stream is not None else cur
         if s is not cur:
             s.wait_stream(cur)
             shard.record_stream(s)
-        fn = K.proto("dh_ag_push", [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_uint, c_void_p])
+        fn = K.proto("dh_ag_push", [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p])
         K.check(fn(shard.data_ptr(), self._ptr_array(self.off_stage[tag][slot]), self._ptr_array(self.off_agc[tag][slot]),
-                   self._mc(self.off_stage[tag][slot]), M, Kd, self.rank, self.world, self.push_ctas, before, s.cuda_stream),
-                "dh_ag_push")
+                   self._mc(self.off_stage[tag][slot]), M, Kd, self.rank, self.world, self.push_ctas, self.comm_threads, slices,
+                   s.cuda_stream), "dh_ag_push")
         ev = torch.cuda.Event()
         ev.record(s)
         self._pending.setdefault(tag, collections.deque()).append((slot, self.total_ag[tag][slot], M, Kd, ev))
@@ -243,8 +253,8 @@ class FusedTP:
         ctx = self.exposed.span(s) if (self.exposed is not None and self.exposed.enabled) else contextlib.nullcontext()
         with ctx:                        # the consumer's stream stands still until every rank's rows have arrived
             s.wait_event(ev)
-            fn = K.proto("dh_wait_counters", [c_void_p, c_int, c_uint, c_void_p])
-            K.check(fn(self.ptrs[self.rank] + self.off_agc[tag][slot], M // 128, target, s.cuda_stream), "dh_wait_counters")
+            fn = K.proto("dh_wait_counters", [c_void_p, c_int, c_uint, c_int64, c_void_p])
+            K.check(fn(self.ptrs[self.rank] + self.off_agc[tag][slot], M // 128, target, 0, s.cuda_stream), "dh_wait_counters")
         return self._stage_view(tag, slot, M, Kd)
 
     def gather_consume(self, tag: str):
@@ -302,10 +312,11 @@ class FusedTP:
         out = torch.empty((M // self.world, N), dtype=torch.bfloat16, device=self.device)
         s = torch.cuda.current_stream(self.device)
         if block_target is not None:
-            fn = K.proto("dh_rs_reduce_blocks", [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_uint, c_int, c_void_p])
+            fn = K.proto("dh_rs_reduce_blocks", [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_uint, c_int, c_int,
+                                                  c_void_p])
             off = self.off_split[tag][slot]
             K.check(fn(self._ptr_array(off), self._mc(off), self.ptrs[self.rank] + self.off_rsflag[tag][slot], out.data_ptr(), M, N,
-                       self.rank, self.world, block_target, self.rs_ctas, s.cuda_stream), "dh_rs_reduce_blocks")
+                       self.rank, self.world, block_target, self.rs_ctas, self.comm_threads, s.cuda_stream), "dh_rs_reduce_blocks")
             return out
         fn = K.proto("dh_rs_reduce", [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_uint, c_int, c_void_p])
         off = self.off_split[tag][slot]

@@ -261,3 +261,20 @@ def test_bounded_wait_reports_timeout_without_hanging():
     x = torch.ones(4, device=DEV)
     assert float(x.sum()) == 4.0
     assert K.read_status().code == 0
+
+
+def test_communication_wait_entry_point_gives_up_after_its_budget():
+    """The real wait in front of a consumer of gathered rows (``dh_wait_counters``) on counters that
+    nothing raises, with a budget of about a millisecond: the kernel gives up, the status word says
+    "flag timeout" at that site, and the context stays usable.  No peer is involved."""
+    from ctypes import c_int, c_int64, c_uint, c_void_p
+    from dhellam_b200 import kernels as K
+    counters = torch.zeros(16, dtype=torch.int32, device=DEV)
+    fn = K.proto("dh_wait_counters", [c_void_p, c_int, c_uint, c_int64, c_void_p])
+    K.check(fn(counters.data_ptr(), 16, 3, 2_000_000, K.stream_ptr(None)), "dh_wait_counters")
+    st = K.read_status(clear=True)
+    assert st.code == 2 and st.where == 641 and st.extra == 3, (st.code, st.where, st.extra)
+    counters.fill_(3)                          # the same wait succeeds at once when the counters are there
+    K.check(fn(counters.data_ptr(), 16, 3, 2_000_000, K.stream_ptr(None)), "dh_wait_counters")
+    assert K.read_status().code == 0
+    assert float(torch.ones(4, device=DEV).sum()) == 4.0

@@ -111,9 +111,9 @@ def _fused_worker(rank, world, rows, h, n_out, iters):
         # (or peer-load) reduction; with and without the multicast alias
         for mc in (fused.mc_ptr, 0):
             keep, fused.mc_ptr = fused.mc_ptr, mc
-            part = fused.partial_buffer("attn_l", rows, h)
+            part = fused.partial_buffer("head_bwd", rows, h)      # whole-buffer announcements: its own site
             gemm_nt(a, w2, out=part)
-            got4 = fused.rs_reduce("attn_l")
+            got4 = fused.rs_reduce("head_bwd")
             fused.mc_ptr = keep
             assert _rel(got4, ref) < 1e-2, (_rel(got4, ref), mc)
         # tile-granular forms: the GEMM waits per 128-row block for the pushed rows inside the kernel (own shard
