@@ -66,12 +66,14 @@ __device__ __forceinline__ uint4 ld_relaxed_sys_v4(const void* p) {
 
 // ------------------------------------------------------------------------------------------ all-gather push
 struct PushJob {
-  const __nv_bfloat16* shard;            // [rows_per_rank, K] this rank's rows (any memory)
+  const __nv_bfloat16* shard;            // [blocks_per_rank * 128, K] this rank's rows (any memory), row stride src_ld
   __nv_bfloat16* stage[MAX_RANKS];       // staging [M, K] on every rank (stage[rank] is local)
   __nv_bfloat16* stage_mc;               // the same staging through the multicast address (null: per-peer stores)
   uint32_t* count[MAX_RANKS];            // per row-block arrival counters on every rank
   int K;                                 // row width in elements
+  long long src_ld;                      // elements between consecutive source rows (K when contiguous)
   int rank, world, blocks_per_rank;
+  int dst_block0;                        // 128-row block of the staging buffer where the first pushed block lands
   int slices;                            // column slices per row block = counter increments per block and call
 };
 
@@ -84,8 +86,8 @@ __device__ __forceinline__ void push_rows(const PushJob& p, int group, int ngrou
   const int total = ROW_BLOCK * vec_per_row;
   for (int it = group; it < items; it += ngroups) {
     const int lb = it / p.slices, sl = it - lb * p.slices;
-    const int gb = p.rank * p.blocks_per_rank + lb;         // global row block
-    const long long src_base = (long long)lb * ROW_BLOCK * p.K + (long long)sl * cw;
+    const int gb = p.dst_block0 + lb;                       // row block in the staging buffer
+    const long long src_base = (long long)lb * ROW_BLOCK * p.src_ld + (long long)sl * cw;
     const long long dst_base = (long long)gb * ROW_BLOCK * p.K + (long long)sl * cw;
     for (int i0 = tid; i0 < total; i0 += nthreads * U) {
       uint4 v[U];
@@ -96,7 +98,7 @@ __device__ __forceinline__ void push_rows(const PushJob& p, int group, int ngrou
         if (i < total) {
           const int r = i / vec_per_row, c = i - r * vec_per_row;
           off[u] = (long long)r * p.K + c * 8;
-          v[u] = ld_nc_v4(p.shard + src_base + off[u]);
+          v[u] = ld_nc_v4(p.shard + src_base + (long long)r * p.src_ld + c * 8);
         }
       }
       if (p.stage_mc != nullptr) {
@@ -124,10 +126,15 @@ __device__ __forceinline__ void push_rows(const PushJob& p, int group, int ngrou
 struct ReduceJob {
   const __nv_bfloat16* part[MAX_RANKS];  // every rank's partial product [M][N] (symmetric memory)
   const __nv_bfloat16* part_mc;          // the same through the multicast address (null: peer loads)
-  const uint32_t* ready;                 // this rank's per-block completion counters (local memory)
-  __nv_bfloat16* out;                    // [M / world, N]
-  int M, N, rank, world, blocks, slices;
-  uint32_t target;                       // counter value of a block that every rank has delivered
+  const uint32_t* ready;                 // this rank's completion counters (local memory)
+  int ready_stride;                      // 1: one counter per row block; 0: one counter for the whole buffer
+  __nv_bfloat16* out;                    // [rows, N]: the reduced rows, row stride out_ld
+  long long out_ld;
+  int N, rank, world;
+  int in_block0;                         // first 128-row block of this rank's rows inside the partial products
+  int rows;                              // number of rows to reduce (blocks = ceil(rows / 128))
+  int blocks, slices;
+  uint32_t target;                       // counter value that means "every rank has delivered"
 };
 
 // Returns false if a bounded wait gave up (the status word says where).  `flag` is one int of shared
@@ -136,20 +143,19 @@ template <typename Sync>
 __device__ __forceinline__ bool reduce_rows(const ReduceJob& p, int group, int ngroups, int tid, int nthreads, Sync group_sync, int* flag,
                                             DeviceStatus* status, int where) {
   constexpr int U = 8;
-  const int rows_per_rank = p.M / p.world;
   const int cw = p.N / p.slices;                            // columns per slice (multiple of 8)
   const int vec_per_row = cw >> 3;
   const int items = p.blocks * p.slices;
   for (int it = group; it < items; it += ngroups) {
     const int b = it / p.slices, sl = it - b * p.slices;
     group_sync();
-    if (tid == 0) *flag = wait_counter_sys(p.ready + b, p.target, nullptr, status, where) ? 1 : 0;
+    if (tid == 0) *flag = wait_counter_sys(p.ready + b * p.ready_stride, p.target, nullptr, status, where) ? 1 : 0;
     group_sync();
     if (!*flag) return false;
-    const int rows = min(ROW_BLOCK, rows_per_rank - b * ROW_BLOCK);
+    const int rows = min(ROW_BLOCK, p.rows - b * ROW_BLOCK);
     const int total = rows * vec_per_row;
-    const long long in_base = ((long long)p.rank * rows_per_rank + (long long)b * ROW_BLOCK) * p.N + (long long)sl * cw;
-    const long long out_base = (long long)b * ROW_BLOCK * p.N + (long long)sl * cw;
+    const long long in_base = ((long long)p.in_block0 + b) * ROW_BLOCK * p.N + (long long)sl * cw;
+    const long long out_base = (long long)b * ROW_BLOCK * p.out_ld + (long long)sl * cw;
     for (int i0 = tid; i0 < total; i0 += nthreads * U) {
       uint4 v[U];
       long long off[U];
@@ -176,8 +182,12 @@ __device__ __forceinline__ bool reduce_rows(const ReduceJob& p, int group, int n
         }
       }
 #pragma unroll
-      for (int u = 0; u < U; ++u)
-        if (i0 + u * nthreads < total) st_v4(p.out + out_base + off[u], v[u]);
+      for (int u = 0; u < U; ++u) {
+        if (i0 + u * nthreads >= total) continue;
+        const int i = i0 + u * nthreads;
+        const int r = i / vec_per_row, c = i - r * vec_per_row;
+        st_v4(p.out + out_base + (long long)r * p.out_ld + c * 8, v[u]);
+      }
     }
   }
   return true;

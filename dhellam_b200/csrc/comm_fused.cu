@@ -130,8 +130,10 @@ int dh_fill_push_job(dh::comm::PushJob& p, const char* who, const void* shard, v
   }
   p.stage_mc = (__nv_bfloat16*)stage_mc;
   p.K = K;
+  p.src_ld = K;
   p.rank = rank; p.world = world;
   p.blocks_per_rank = M / world / ROW_BLOCK;
+  p.dst_block0 = rank * p.blocks_per_rank;
   p.slices = slices;
   return 0;
 }
@@ -139,14 +141,18 @@ int dh_fill_push_job(dh::comm::PushJob& p, const char* who, const void* shard, v
 int dh_fill_reduce_job(dh::comm::ReduceJob& p, const char* who, void* const* part_ptrs, const void* part_mc, const void* ready, void* out,
                        int M, int N, int rank, int world, unsigned target, int slices) {
   if (world < 2 || world > MAX_RANKS) { set_last_error("%s: world size %d not in [2, %d]", who, world, MAX_RANKS); return (int)cudaErrorInvalidValue; }
-  if (M % world != 0 || N % 8 != 0) { set_last_error("%s: M must divide by world and N by 8 (M=%d N=%d)", who, M, N); return (int)cudaErrorInvalidValue; }
+  if (M % (world * ROW_BLOCK) != 0 || N % 8 != 0) { set_last_error("%s: M must divide by world*128 and N by 8 (M=%d N=%d)", who, M, N); return (int)cudaErrorInvalidValue; }
   if (slices < 1 || N % (slices * 8) != 0) { set_last_error("%s: %d column slices do not divide N=%d into multiples of 8", who, slices, N); return (int)cudaErrorInvalidValue; }
   for (int i = 0; i < MAX_RANKS; ++i) p.part[i] = i < world ? (const __nv_bfloat16*)part_ptrs[i] : nullptr;
   p.part_mc = (const __nv_bfloat16*)part_mc;
   p.ready = (const uint32_t*)ready;
+  p.ready_stride = 1;
   p.out = (__nv_bfloat16*)out;
-  p.M = M; p.N = N; p.rank = rank; p.world = world;
-  p.blocks = (M / world + ROW_BLOCK - 1) / ROW_BLOCK;
+  p.out_ld = N;
+  p.N = N; p.rank = rank; p.world = world;
+  p.rows = M / world;
+  p.in_block0 = rank * (p.rows / ROW_BLOCK);
+  p.blocks = (p.rows + ROW_BLOCK - 1) / ROW_BLOCK;
   p.slices = slices;
   p.target = target;
   return 0;
@@ -171,6 +177,85 @@ int dh_ag_push(const void* shard, void* const* stage_ptrs, void* const* count_pt
   ag_push_kernel<<<ctas, threads, 0, stream>>>(p);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) set_last_error("dh_ag_push launch failed: %s", cudaGetErrorString(e));
+  return (int)e;
+}
+
+// Generic placement form of the push, used by context parallelism to gather the key / value rows of all
+// ranks in global sequence order: `n_blocks` 128-row blocks of `src` (row stride src_ld elements, width K)
+// land at row block `dst_block0` of every rank's buffer; each of those blocks' counters rises by `slices`.
+int dh_push_blocks(const void* src, int64_t src_ld, void* const* dst_ptrs, void* const* count_ptrs, void* dst_mc, int K, int n_blocks,
+                   int dst_block0, int rank, int world, int ctas, int threads, int slices, cudaStream_t stream) {
+  if (world < 2 || world > MAX_RANKS) { set_last_error("dh_push_blocks: world size %d not in [2, %d]", world, MAX_RANKS); return (int)cudaErrorInvalidValue; }
+  if (K % 8 != 0 || slices < 1 || K % (slices * 8) != 0 || src_ld % 8 != 0 || (reinterpret_cast<uintptr_t>(src) & 15) != 0) {
+    set_last_error("dh_push_blocks: rows must be 16-byte aligned and %d slices must divide K=%d into multiples of 8", slices, K);
+    return (int)cudaErrorInvalidValue;
+  }
+  PushJob p;
+  p.shard = (const __nv_bfloat16*)src;
+  for (int i = 0; i < MAX_RANKS; ++i) {
+    p.stage[i] = i < world ? (__nv_bfloat16*)dst_ptrs[i] : nullptr;
+    p.count[i] = i < world ? (uint32_t*)count_ptrs[i] : nullptr;
+  }
+  p.stage_mc = (__nv_bfloat16*)dst_mc;
+  p.K = K;
+  p.src_ld = src_ld;
+  p.rank = rank; p.world = world;
+  p.blocks_per_rank = n_blocks;
+  p.dst_block0 = dst_block0;
+  p.slices = slices;
+  if (ctas <= 0) ctas = 16;
+  if (threads <= 0 || threads > 256 || threads % 32 != 0) threads = 256;
+  ag_push_kernel<<<ctas, threads, 0, stream>>>(p);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) set_last_error("dh_push_blocks launch failed: %s", cudaGetErrorString(e));
+  return (int)e;
+}
+
+// Adds `value` to one counter on every rank (system-scope release): "everything this rank launched before on
+// this stream is in memory".  Pairs with dh_reduce_blocks(ready_stride = 0).
+__global__ void announce_kernel(uint32_t* c0, uint32_t* c1, uint32_t* c2, uint32_t* c3, uint32_t* c4, uint32_t* c5, uint32_t* c6, uint32_t* c7,
+                                int world, uint32_t value) {
+  uint32_t* c[8] = {c0, c1, c2, c3, c4, c5, c6, c7};
+  if ((int)threadIdx.x < world) {
+    asm volatile("fence.acq_rel.sys;" ::: "memory");
+    red_add_release_sys(c[threadIdx.x], value);
+  }
+}
+int dh_announce(void* const* counter_ptrs, int world, unsigned value, cudaStream_t stream) {
+  if (world < 1 || world > MAX_RANKS) { set_last_error("dh_announce: world size %d not in [1, %d]", world, MAX_RANKS); return (int)cudaErrorInvalidValue; }
+  uint32_t* c[8];
+  for (int i = 0; i < 8; ++i) c[i] = i < world ? (uint32_t*)counter_ptrs[i] : nullptr;
+  announce_kernel<<<1, 32, 0, stream>>>(c[0], c[1], c[2], c[3], c[4], c[5], c[6], c[7], world, value);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) set_last_error("dh_announce launch failed: %s", cudaGetErrorString(e));
+  return (int)e;
+}
+
+// Generic placement form of the reduction: `rows` rows starting at row block `in_block0` of every rank's buffer
+// (width N) are summed over the ranks into out (row stride out_ld).  ready / ready_stride / target: the counters
+// that say the rows are complete on every rank (stride 0: one counter for all of them).
+int dh_reduce_blocks(void* const* part_ptrs, const void* part_mc, const void* ready, int ready_stride, void* out, int64_t out_ld, int N,
+                     int in_block0, int rows, int rank, int world, unsigned target, int ctas, int threads, cudaStream_t stream) {
+  if (world < 2 || world > MAX_RANKS) { set_last_error("dh_reduce_blocks: world size %d not in [2, %d]", world, MAX_RANKS); return (int)cudaErrorInvalidValue; }
+  if (N % 8 != 0 || out_ld % 8 != 0 || rows <= 0) { set_last_error("dh_reduce_blocks: N and out_ld must be multiples of 8"); return (int)cudaErrorInvalidValue; }
+  if (ctas <= 0) ctas = 32;
+  if (threads <= 0 || threads > 256 || threads % 32 != 0) threads = 256;
+  ReduceJob p;
+  for (int i = 0; i < MAX_RANKS; ++i) p.part[i] = i < world ? (const __nv_bfloat16*)part_ptrs[i] : nullptr;
+  p.part_mc = (const __nv_bfloat16*)part_mc;
+  p.ready = (const uint32_t*)ready;
+  p.ready_stride = ready_stride ? 1 : 0;
+  p.out = (__nv_bfloat16*)out;
+  p.out_ld = out_ld;
+  p.N = N; p.rank = rank; p.world = world;
+  p.rows = rows;
+  p.in_block0 = in_block0;
+  p.blocks = (rows + ROW_BLOCK - 1) / ROW_BLOCK;
+  p.slices = dh::comm::slices_for(p.blocks, N, ctas);
+  p.target = target;
+  rs_reduce_blocks_kernel<<<ctas, threads, 0, stream>>>(p, reinterpret_cast<DeviceStatus*>(dh_status_device_ptr()));
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) set_last_error("dh_reduce_blocks launch failed: %s", cudaGetErrorString(e));
   return (int)e;
 }
 
