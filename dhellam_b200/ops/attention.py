@@ -38,20 +38,31 @@ def _ref_fwd(q, k, v, causal, scale):
     return o.permute(2, 0, 1, 3).contiguous(), lse, p
 
 
-def attn_fwd(q, k, v, causal: bool = True, scale: float | None = None, sm_budget: int = 0, stream=None):
-    """Returns ``(out [Sq,B,Hq,d], lse [B,Hq,Sq] fp32)``."""
+def attn_fwd(q, k, v, causal: bool = True, scale: float | None = None, sm_budget: int = 0, stream=None, out=None):
+    """Returns ``(out [Sq,B,Hq,d], lse [B,Hq,Sq] fp32)``.  ``out`` may name a contiguous destination of
+    that shape (for example a slice along the sequence of a larger output)."""
     d = q.shape[-1]
     scale = scale if scale is not None else 1.0 / math.sqrt(d)
     if K.use_library(q):
         from . import library as LIB
-        return LIB.attn_fwd(q, k, v, causal, scale)
+        o, lse = LIB.attn_fwd(q, k, v, causal, scale)
+        if out is not None:
+            out.copy_(o)
+            return out, lse
+        return o, lse
     if not q.is_cuda:
         o, lse, _ = _ref_fwd(q, k, v, causal, scale)
+        if out is not None:
+            out.copy_(o.to(q.dtype))
+            return out, lse
         return o.to(q.dtype), lse
     Sq, B, Hq, _ = q.shape
     Sk, Hk = k.shape[0], k.shape[2]
     assert q.stride(3) == 1 and k.stride(3) == 1 and v.stride(3) == 1
-    out = torch.empty((Sq, B, Hq, d), dtype=q.dtype, device=q.device)
+    if out is None:
+        out = torch.empty((Sq, B, Hq, d), dtype=q.dtype, device=q.device)
+    else:
+        assert tuple(out.shape) == (Sq, B, Hq, d) and out.is_contiguous() and out.dtype == q.dtype
     lse = torch.empty((B, Hq, Sq), dtype=torch.float32, device=q.device)
     fn = K.proto("dh_attn_fwd", [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                  c_int64, c_int64, c_int64, c_int64, c_int64, c_int64, c_int64, c_int64, c_int64,

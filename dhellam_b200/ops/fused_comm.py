@@ -323,3 +323,186 @@ class FusedTP:
         K.check(fn(self._ptr_array(off), self._mc(off), self._ptr_array(self.off_rsflag[tag][slot]), out.data_ptr(), M, N, self.rank,
                    self.world, use, self.rs_ctas, s.cuda_stream), "dh_rs_reduce")
         return out
+
+
+class FusedCP:
+    """Context-parallel key/value exchange over NVLink peer memory (one instance per context-parallel group).
+
+    The reference moves KV blocks around a ring with ``batch_isend_irecv`` and merges per-step partial
+    outputs through the log-sum-exp (dhellam/operators/ring_attn.py:43-201); its backward sends the KV
+    block and a travelling dKV accumulator around the ring (:204-411).  NVSwitch gives every GPU full
+    bandwidth to every peer, so a ring buys nothing here: every rank PUSHES its two sequence chunks
+    straight to their places in every peer's key/value buffer (global sequence order; ``multimem.st`` or
+    per-peer stores, bf16, per-128-row-block arrival counters), and each of a rank's two query chunks
+    then runs ONE causal attention call over the keys it may see: no per-step outputs, no merges.  In
+    the backward every rank writes its dK/dV contributions for all keys into its own symmetric buffer
+    and each owner reduces its two chunks over the ranks (``multimem.ld_reduce``: fp32 adds inside the
+    switch, or peer loads).
+
+    Sites are double-buffered with monotonically increasing counters like ``FusedTP``.
+    """
+    SITES = ("kv_fwd", "kv_bwd")
+
+    def __init__(self, ps, cfg, train, device, batch: int | None = None):
+        import torch.distributed._symmetric_memory as symm_mem
+        self.ps, self.device = ps, torch.device(device)
+        self.world, self.rank = ps.cp, ps.cp_rank
+        B = batch or train.micro_batch_size
+        nkv = max(cfg.num_query_groups // ps.tp, 1)
+        self.width = 2 * nkv * cfg.head_dim                     # one row: K heads then V heads
+        self.chunk_rows = cfg.seq_length // (2 * self.world) * B  # rows (sequence position x batch) per chunk
+        assert self.chunk_rows % 128 == 0, "sequence chunk x micro-batch must be a multiple of 128 rows for the peer-memory exchange"
+        self.chunk_blocks = self.chunk_rows // 128
+        self.total_rows = 2 * self.world * self.chunk_rows
+        self.total_blocks = 2 * self.world * self.chunk_blocks
+        buf_bytes = self.total_rows * self.width * 2
+        cnt_bytes = _align((self.total_blocks + 8) * 4)
+        self.off_buf, self.off_cnt = {}, {}
+        off = 0
+        for s in self.SITES + ("dkv",):
+            self.off_buf[s] = [off, off + buf_bytes]
+            off += 2 * buf_bytes
+        cnt_base = off
+        for s in self.SITES + ("dkv",):
+            self.off_cnt[s] = [off, off + cnt_bytes]
+            off += 2 * cnt_bytes
+        self.buf = symm_mem.empty(off, dtype=torch.uint8, device=self.device)
+        group = ps.cp_group
+        self.hdl = symm_mem.rendezvous(self.buf, group=group.group_name)
+        self.ptrs = [int(p) for p in self.hdl.buffer_ptrs]
+        mc = 0
+        if os.environ.get("DHELLAM_MULTIMEM", "1") != "0":
+            try:
+                mc = int(self.hdl.multicast_ptr or 0)
+            except Exception:
+                mc = 0
+        self.mc_ptr = mc
+        self.buf[cnt_base:off].zero_()
+        torch.cuda.synchronize(self.device)
+        dist.barrier(group=group)
+        self.calls = {s: 0 for s in self.SITES + ("dkv",)}
+        self.total = {s: [0, 0] for s in self.SITES + ("dkv",)}
+        self._arr = ctypes.c_void_p * self.world
+        self.ctas = max(16, 96 // self.world)
+        self.exposed = None
+
+    def chunk_ids(self):
+        """The two sequence chunks this rank holds (local rows: first half, second half)."""
+        return self.rank, 2 * self.world - 1 - self.rank
+
+    def _ptr_array(self, off):
+        return self._arr(*[p + off for p in self.ptrs])
+
+    def _mc(self, off):
+        return (self.mc_ptr + off) if self.mc_ptr else 0
+
+    def view(self, site: str, slot: int):
+        off = self.off_buf[site][slot]
+        return self.buf[off:off + self.total_rows * self.width * 2].view(torch.bfloat16).view(self.total_rows, self.width)
+
+    def push_kv(self, kv_rows, site: str, stream=None):
+        """``kv_rows [2 * chunk_rows, width]`` (row stride free): this rank's K|V rows, first chunk then second.
+        Starts pushing both chunks to their global places on every rank; returns ``(slot, target)``."""
+        assert kv_rows.shape == (2 * self.chunk_rows, self.width) and kv_rows.stride(1) == 1 and kv_rows.dtype == torch.bfloat16
+        slot = self.calls[site] & 1
+        self.calls[site] += 1
+        slices = K.proto("dh_comm_slices", [c_int, c_int, c_int])(self.chunk_blocks, self.width, self.ctas)
+        self.total[site][slot] += slices
+        cur = torch.cuda.current_stream(self.device)
+        s = stream if stream is not None else cur
+        if s is not cur:
+            s.wait_stream(cur)
+            kv_rows.record_stream(s)
+        fn = K.proto("dh_push_blocks", [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                                        c_int, c_void_p])
+        off, coff = self.off_buf[site][slot], self.off_cnt[site][slot]
+        for half, chunk in enumerate(self.chunk_ids()):
+            src = kv_rows[half * self.chunk_rows:]
+            K.check(fn(src.data_ptr(), kv_rows.stride(0), self._ptr_array(off), self._ptr_array(coff), self._mc(off), self.width,
+                       self.chunk_blocks, chunk * self.chunk_blocks, self.rank, self.world, self.ctas, 256, slices, s.cuda_stream),
+                    "dh_push_blocks")
+        return slot, self.total[site][slot]
+
+    def wait_kv(self, site: str, slot: int, target: int, n_chunks: int):
+        """Makes the current stream wait (bounded) until the first ``n_chunks`` chunks have arrived; returns
+        the gathered ``[total_rows, width]`` view."""
+        s = torch.cuda.current_stream(self.device)
+        ctx = self.exposed.span(s) if (self.exposed is not None and self.exposed.enabled) else contextlib.nullcontext()
+        with ctx:
+            fn = K.proto("dh_wait_counters", [c_void_p, c_int, c_uint, c_int64, c_void_p])
+            K.check(fn(self.ptrs[self.rank] + self.off_cnt[site][slot], n_chunks * self.chunk_blocks, target, 0, s.cuda_stream),
+                    "dh_wait_counters")
+        return self.view(site, slot)
+
+    def dkv_buffer(self):
+        """This rank's partial dK|dV buffer ``[total_rows, width]`` for the next backward; returns ``(view, slot)``."""
+        slot = self.calls["dkv"] & 1
+        self.calls["dkv"] += 1
+        return self.view("dkv", slot), slot
+
+    def reduce_dkv(self, slot: int, out_rows):
+        """Announces this rank's partial dK|dV, waits for every rank's, and reduces this rank's two chunks
+        over the ranks into ``out_rows [2 * chunk_rows, width]`` (any row stride).  Runs on the current stream,
+        after the kernels that wrote the partial buffer."""
+        assert out_rows.shape == (2 * self.chunk_rows, self.width) and out_rows.stride(1) == 1
+        s = torch.cuda.current_stream(self.device)
+        off, coff = self.off_buf["dkv"][slot], self.off_cnt["dkv"][slot]
+        self.total["dkv"][slot] += self.world
+        target = self.total["dkv"][slot]
+        ann = K.proto("dh_announce", [c_void_p, c_int, c_uint, c_void_p])
+        K.check(ann(self._ptr_array(coff), self.world, 1, s.cuda_stream), "dh_announce")
+        fn = K.proto("dh_reduce_blocks", [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_int, c_uint,
+                                          c_int, c_int, c_void_p])
+        ctx = self.exposed.span(s) if (self.exposed is not None and self.exposed.enabled) else contextlib.nullcontext()
+        with ctx:
+            for half, chunk in enumerate(self.chunk_ids()):
+                dst = out_rows[half * self.chunk_rows:]
+                K.check(fn(self._ptr_array(off), self._mc(off), self.ptrs[self.rank] + coff, 0, dst.data_ptr(), out_rows.stride(0),
+                           self.width, chunk * self.chunk_blocks, self.chunk_rows, self.rank, self.world, target, self.ctas, 256,
+                           s.cuda_stream), "dh_reduce_blocks")
+
+
+class SimulatedCP:
+    """The interface of ``FusedCP`` on library collectives (gloo / NCCL), for CPU ranks: the gather form of
+    context parallelism (chunk placement, one causal call per query chunk, zero-filled unseen keys, owner
+    reduction of dK|dV) can then be checked against autograd without GPUs.  Everything happens at call time;
+    slots and targets are dummies."""
+
+    def __init__(self, ps, cfg, train, device, batch: int | None = None):
+        self.ps, self.device = ps, torch.device(device)
+        self.world, self.rank = ps.cp, ps.cp_rank
+        B = batch or train.micro_batch_size
+        nkv = max(cfg.num_query_groups // ps.tp, 1)
+        self.width = 2 * nkv * cfg.head_dim
+        self.chunk_rows = cfg.seq_length // (2 * self.world) * B
+        self.total_rows = 2 * self.world * self.chunk_rows
+        self._bufs = {}
+        self.exposed = None
+
+    def chunk_ids(self):
+        return self.rank, 2 * self.world - 1 - self.rank
+
+    def push_kv(self, kv_rows, site: str, stream=None):
+        mine = kv_rows.contiguous()
+        parts = [torch.empty_like(mine) for _ in range(self.world)]
+        dist.all_gather(parts, mine, group=self.ps.cp_group)
+        full = torch.empty((self.total_rows, self.width), dtype=mine.dtype, device=mine.device)
+        for r, p in enumerate(parts):
+            for half, chunk in enumerate((r, 2 * self.world - 1 - r)):
+                full[chunk * self.chunk_rows:(chunk + 1) * self.chunk_rows] = p[half * self.chunk_rows:(half + 1) * self.chunk_rows]
+        self._bufs[site] = full
+        return 0, 0
+
+    def wait_kv(self, site: str, slot: int, target: int, n_chunks: int):
+        return self._bufs.pop(site)
+
+    def dkv_buffer(self):
+        dtype = next(iter(self._bufs.values())).dtype if self._bufs else torch.float32
+        self._part = torch.zeros((self.total_rows, self.width), dtype=torch.float32, device=self.device)
+        return self._part, 0
+
+    def reduce_dkv(self, slot: int, out_rows):
+        part = self._part
+        dist.all_reduce(part, group=self.ps.cp_group)
+        for half, chunk in enumerate(self.chunk_ids()):
+            out_rows[half * self.chunk_rows:(half + 1) * self.chunk_rows] = part[chunk * self.chunk_rows:(chunk + 1) * self.chunk_rows].to(out_rows.dtype)

@@ -11,7 +11,16 @@ so that the pairing search can put the other strand's compute beside each transf
 
 Capability parity: dhellam/operators/ring_attn.py:43-411 (``fa_cp_block_fwd/bwd``) and the
 unrolled ring ops of dhellam/core/dstb.py:715-722, 806-818, generalised from c = 2 to any c.
-Transport here is the library point-to-point ring (NCCL / gloo).
+
+Two transports.  The ring above over library point-to-point calls (NCCL / gloo) is the CPU path
+and the fall-back.  On GPUs with peer memory (``env.fused_cp``, see ``ops.fused_comm.FusedCP``) the
+same schedulable ops run a gather form instead: the first forward op pushes this rank's two K|V
+chunks to their global places in every peer's buffer, the last one runs one causal attention call
+per query chunk over the keys that chunk may see (chunk ``j`` sees keys ``[0, (j+1) L)``, which is
+exactly the kernel's bottom-right aligned causal mask), so there are no per-step partial outputs,
+no log-sum-exp merges and no concatenations; the backward re-gathers K|V the same way, writes this
+rank's dK|dV contributions for all keys into its symmetric buffer and reduces its own two chunks
+over the ranks inside the switch.
 """
 from __future__ import annotations
 
@@ -40,9 +49,102 @@ def _post(run, send, reverse=False):
     return recv, reqs
 
 
+def _kv_rows(run, qkv):
+    """The K|V columns of the packed QKV rows: ``[T, 2 * nkv * d]`` strided view."""
+    from ..models.transformer import _heads
+    nq, nkv, d = _heads(run.env)
+    return qkv[:, nq * d:]
+
+
+def _kv_heads_view(env, rows, B):
+    """``[S * B, 2 * nkv * d]`` gathered rows -> ``(k, v)`` as ``[S, B, nkv, d]`` strided views."""
+    from ..models.transformer import _heads
+    nq, nkv, d = _heads(env)
+    v4 = rows.view(rows.shape[0] // B, B, 2 * nkv, d)
+    return v4[:, :, :nkv], v4[:, :, nkv:]
+
+
+def _gather_fwd_step(run, i: int, c: int):
+    from ..models.transformer import _apply_rope
+    env = run.env
+    cp = env.fused_cp
+    st = run.v.setdefault("ring", {})
+    if i == 0:
+        qkv = _use(run, run.v.pop("qkv"))
+        _apply_rope(run, qkv)
+        run.acts["qkv"] = qkv
+        st["qkv"] = qkv
+        st["slot"], st["target"] = cp.push_kv(_kv_rows(run, qkv), "kv_fwd")
+    if i < c - 1:
+        return
+    qkv = st["qkv"]
+    B = run.mb.batch
+    q, _, _ = _views(run, qkv)
+    r, L = cp.rank, q.shape[0] // 2
+    a_id, b_id = cp.chunk_ids()
+    rows = cp.wait_kv("kv_fwd", st["slot"], st["target"], b_id + 1)
+    k, v = _kv_heads_view(env, rows, B)
+    o = torch.empty((q.shape[0], B, q.shape[2], q.shape[3]), dtype=q.dtype, device=q.device)
+    lses = []
+    for half, chunk in ((1, b_id), (0, a_id)):                 # the heavier chunk first
+        n = (chunk + 1) * L
+        _, lse = ATT.attn_fwd(q[half * L:(half + 1) * L], k[:n], v[:n], causal=True, scale=env.softmax_scale,
+                              out=o[half * L:(half + 1) * L])
+        lses.append(lse)
+    run.acts["attn_out"], run.acts["lse"] = o, (lses[1], lses[0])
+    run.v["attn_out"] = o.view(o.shape[0] * o.shape[1], -1)
+    run.v.pop("ring")
+
+
+def _gather_bwd_step(run, i: int, c: int):
+    from ..models.transformer import _apply_rope, _heads
+    env = run.env
+    cp = env.fused_cp
+    st = run.v.setdefault("ring_b", {})
+    if i == 0:
+        qkv = _use(run, run.acts.pop("qkv"))
+        st["qkv"] = qkv
+        st["slot"], st["target"] = cp.push_kv(_kv_rows(run, qkv), "kv_bwd")      # re-gather instead of keeping 2c chunks per layer
+    if i < c:
+        return
+    qkv = st["qkv"]
+    B = run.mb.batch
+    nq, nkv, d = _heads(env)
+    q, _, _ = _views(run, qkv)
+    L = q.shape[0] // 2
+    a_id, b_id = cp.chunk_ids()
+    rows = cp.wait_kv("kv_bwd", st["slot"], st["target"], b_id + 1)
+    k, v = _kv_heads_view(env, rows, B)
+    o = _use(run, run.acts["attn_out"])
+    lse_a, lse_b = run.acts.pop("lse")
+    do = _use(run, run.v.pop("d_attn_out")).view(o.shape)
+    dqkv = torch.empty_like(qkv)
+    dq, _, _ = _views(run, dqkv)
+    part, pslot = cp.dkv_buffer()
+    pk, pv = _kv_heads_view(env, part, B)
+    nb = (b_id + 1) * L
+    # the later chunk sees the longer key range: its dK|dV go straight into the symmetric buffer, rows it cannot see are zero
+    ATT.attn_bwd(do[L:], q[L:], k[:nb], v[:nb], o[L:], _use(run, lse_b), causal=True, scale=env.softmax_scale,
+                 dq=dq[L:], dk=pk[:nb], dv=pv[:nb])
+    if nb * B < part.shape[0]:
+        part[nb * B:].zero_()
+    na = (a_id + 1) * L
+    tmp = torch.empty((na * B, part.shape[1]), dtype=part.dtype, device=part.device)
+    tk, tv = _kv_heads_view(env, tmp, B)
+    ATT.attn_bwd(do[:L], q[:L], k[:na], v[:na], o[:L], _use(run, lse_a), causal=True, scale=env.softmax_scale,
+                 dq=dq[:L], dk=tk, dv=tv)
+    part[:na * B] += tmp
+    cp.reduce_dkv(pslot, dqkv[:, nq * d:])
+    _apply_rope(run, dqkv, inverse=True)
+    run.v["d_qkv"] = dqkv
+    run.v.pop("ring_b")
+
+
 def make_ring_fwd_step(i: int, c: int):
     def step(run):
         from ..models.transformer import _apply_rope
+        if getattr(run.env, "fused_cp", None) is not None:
+            return _gather_fwd_step(run, i, c)
         env, ps = run.env, run.env.ps
         r = ps.cp_rank
         st = run.v.setdefault("ring", {})
@@ -85,6 +187,8 @@ def make_ring_fwd_step(i: int, c: int):
 def make_ring_bwd_step(i: int, c: int):
     def step(run):
         from ..models.transformer import _apply_rope
+        if getattr(run.env, "fused_cp", None) is not None:
+            return _gather_bwd_step(run, i, c)
         env, ps = run.env, run.env.ps
         r = ps.cp_rank
         st = run.v.setdefault("ring_b", {})

@@ -62,6 +62,14 @@ class Trainer:
             from .ops.gemm import set_gemm_mode
             set_gemm_mode(1)
         self.env = Env(cfg, self.ps, train, self.device, self.model.dtype, fused=fused)
+        if train.fused_comm and self.device.type == "cuda" and self.ps.cp > 1 and _K.backend() == "native" \
+                and os.environ.get("DHELLAM_CP_RING", "0") != "1":
+            # key/value exchange of context parallelism over peer memory instead of the library ring
+            from .ops.fused_comm import FusedCP
+            self.env.fused_cp = FusedCP(self.ps, cfg, train, self.device)
+        elif self.device.type == "cpu" and self.ps.cp > 1 and os.environ.get("DHELLAM_CP_GATHER_SIM", "0") == "1":
+            from .ops.fused_comm import SimulatedCP           # the gather form on library collectives (tests on CPU ranks)
+            self.env.fused_cp = SimulatedCP(self.ps, cfg, train, self.device)
         if strategy is None and train.schedule_config:
             strategy = Strategy.load(train.schedule_config)
         if strategy is None and train.reference_schedule:
@@ -82,6 +90,8 @@ class Trainer:
             from .sched.checker import check_buffer_reuse
             check_buffer_reuse(self.engine.program, self.engine.executor.strategy, FUSED_BUFFER_EFFECTS,
                                compute_streams=1 if (single_stream or not train.dhellam) else train.compute_streams)
+        if self.env.fused_cp is not None:
+            self.env.fused_cp.exposed = self.engine.executor.exposed
         if fused is not None:
             fused.exposed = self.engine.executor.exposed
             # row-block-wise reduce-scatter: the reduction kernel may start once its GEMM has been launched
@@ -134,6 +144,7 @@ class Trainer:
             self.engine.executor = None
         if self.env is not None:
             self.env.fused = None
+            self.env.fused_cp = None
         self.engine = self.optimizer = self.model = self.env = None
 
     def tokens_per_step(self) -> int:

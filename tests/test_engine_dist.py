@@ -83,6 +83,19 @@ def test_parallel_engine_matches_autograd(name, world, par, n_mb, B, seq, ov):
     run_ranks(_worker, world, name, par, n_mb, B, seq, ov)
 
 
+GATHER_CASES = [("tiny-llama", 2, dict(cp=2), 2, 2, 32, {}), ("tiny-llama", 4, dict(cp=4), 2, 1, 64, {}),
+                ("tiny-gpt", 4, dict(tp=2, cp=2), 2, 1, 32, {})]
+
+
+@pytest.mark.parametrize("name,world,par,n_mb,B,seq,ov", GATHER_CASES, ids=[f"gather-{c[0]}-{'x'.join(f'{k}{v}' for k, v in c[2].items())}" for c in GATHER_CASES])
+def test_context_parallel_gather_form_matches_autograd(name, world, par, n_mb, B, seq, ov, monkeypatch):
+    """The gather form of context parallelism (what GPUs run over peer memory) on CPU ranks through the
+    simulator of the exchange: chunk placement in global order, one bottom-right aligned causal call per
+    query chunk, zero rows for unseen keys, owner reduction of dK|dV."""
+    monkeypatch.setenv("DHELLAM_CP_GATHER_SIM", "1")
+    run_ranks(_worker, world, name, par, n_mb, B, seq, ov)
+
+
 def _pp_bubble_worker(rank, world):
     from dhellam_b200.config import ParallelConfig, TrainConfig, preset
     from dhellam_b200.data import make_microbatch, synthetic_tokens

@@ -204,3 +204,61 @@ def test_tp_engine_fused_matches_unfused(tmp_path):
             assert abs(x - y) / abs(y) < 1e-2, (policy, ra["losses"], rb["losses"])
         assert _rel(ra["g_ln"], rb["g_ln"]) < 5e-2, policy
         assert _rel(ra["g_qkv"], rb["g_qkv"]) < 5e-2, policy
+
+
+def _cp_worker(rank, world, ring, out_path, tp=1):
+    """Context parallelism on GPUs: ``ring`` = library point-to-point ring, else the peer-memory gather form."""
+    os.environ["DHELLAM_CP_RING"] = "1" if ring else "0"
+    from dhellam_b200 import kernels as K
+    from dhellam_b200.config import ModelConfig, ParallelConfig, TrainConfig
+    from dhellam_b200.data import make_microbatch, synthetic_tokens
+    from dhellam_b200.models.sharding import random_full_head, random_full_layer
+    from dhellam_b200.trainer import Trainer
+    cfg = ModelConfig(name="t-llama", num_layers=2, hidden_size=1024, ffn_hidden_size=2048, num_attention_heads=8,
+                      num_query_groups=4, head_dim=128, vocab_size=4096, seq_length=1024, rope_theta=500000.0)
+    train = TrainConfig(micro_batch_size=2, global_batch_size=4, dtype="bf16", clip_grad=0.0)
+    cp = world // tp
+    tr = Trainer(cfg, ParallelConfig(cp=cp, tp=tp), train, device=torch.device("cuda", rank))
+    assert (tr.env.fused_cp is not None) == (cp > 1 and not ring)
+    for i in range(cfg.num_layers):
+        tr.model.load_full_layer_weights(i, random_full_layer(cfg, i, 3))
+    tr.model.load_full_head_weights(random_full_head(cfg, 3))
+    samples = [synthetic_tokens(cfg, 2, 40 + i) for i in range(2)]
+    mbs = [make_microbatch(cfg, tr.ps, s, i, 40 + i, tr.device) for i, s in enumerate(samples)]
+    tr.optimizer.zero_grad()
+    losses = tr.engine.run_step(mbs)
+    tr.optimizer.reduce_gradients()
+    torch.cuda.synchronize()
+    assert K.read_status().code == 0
+    if rank == 0:
+        torch.save({"losses": [float(l) for l in losses],
+                    "g_qkv": tr.model.dctb[0].column_attn_weight_first.main_grad.cpu(),
+                    "g_ln": tr.model.dctb[0].ln_attn_weight_first.main_grad.cpu()}, out_path)
+
+
+def test_context_parallel_gather_over_peer_memory_matches_ring_and_single_gpu(tmp_path):
+    """cp = 2 on two GPUs: the peer-memory gather form (push K|V chunks, one causal call per query chunk, in-switch
+    reduction of dK|dV) against the library ring and against one GPU without context parallelism."""
+    _need(2)
+    paths = {k: str(tmp_path / f"{k}.pt") for k in ("single", "ring", "gather")}
+    run_gpu_ranks(_cp_worker, 1, True, paths["single"])
+    run_gpu_ranks(_cp_worker, 2, True, paths["ring"])
+    run_gpu_ranks(_cp_worker, 2, False, paths["gather"])
+    ref = torch.load(paths["single"])
+    for k in ("ring", "gather"):
+        got = torch.load(paths[k])
+        for x, y in zip(got["losses"], ref["losses"]):
+            assert abs(x - y) / abs(y) < 1e-2, (k, got["losses"], ref["losses"])
+        assert _rel(got["g_qkv"], ref["g_qkv"]) < 5e-2, (k, _rel(got["g_qkv"], ref["g_qkv"]))
+        assert _rel(got["g_ln"], ref["g_ln"]) < 5e-2, k
+
+
+def test_context_parallel_with_tensor_parallel_on_four_gpus(tmp_path):
+    """tp = 2 x cp = 2 (the layout of the long-context configuration, scaled down) against one GPU."""
+    _need(4)
+    a, b = str(tmp_path / "single.pt"), str(tmp_path / "tp2cp2.pt")
+    run_gpu_ranks(_cp_worker, 1, True, a)
+    run_gpu_ranks(_cp_worker, 4, False, b, 2)
+    ref, got = torch.load(a), torch.load(b)
+    for x, y in zip(got["losses"], ref["losses"]):
+        assert abs(x - y) / abs(y) < 1e-2, (got["losses"], ref["losses"])
