@@ -55,6 +55,7 @@ class Env:
         self.training = True
         self.fused = fused
         self.fused_tp = fused is not None and ps.tp > 1
+        self.moe_dev = None           # DeviceMoE: device-resident expert exchange (set by the trainer on GPUs)
         self.fused_cp = None          # FusedCP: peer-memory key/value exchange of context parallelism (set by the trainer)
         self.cur_stream = None
         self.exposed = None           # ExposedTimer of the engine's executor (set by the engine)

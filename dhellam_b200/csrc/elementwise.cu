@@ -237,9 +237,11 @@ __global__ void __launch_bounds__(NT) norm_bwd_kernel(const __nv_bfloat16* __res
 // ============================================================================ activations
 __device__ __forceinline__ float sigmoidf_(float x) { return 1.f / (1.f + __expf(-x)); }
 
+// `rows_dev` (nullable): the number of rows in use lives in device memory (ragged expert batches); rows is then the capacity.
 __global__ void __launch_bounds__(NT) swiglu_fwd_kernel(const __nv_bfloat16* __restrict__ y, __nv_bfloat16* __restrict__ out,
-                                                        long long rows, int f) {
+                                                        long long rows, int f, const int* __restrict__ rows_dev) {
   const int fv = f >> 3;
+  if (rows_dev != nullptr) rows = min(rows, (long long)*rows_dev);
   const long long total = rows * fv;
   for (long long i = (long long)blockIdx.x * NT + threadIdx.x; i < total; i += (long long)gridDim.x * NT) {
     const long long r = i / fv;
@@ -255,8 +257,10 @@ __global__ void __launch_bounds__(NT) swiglu_fwd_kernel(const __nv_bfloat16* __r
 }
 
 __global__ void __launch_bounds__(NT) swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ dout, const __nv_bfloat16* __restrict__ y,
-                                                        __nv_bfloat16* __restrict__ dy, long long rows, int f) {
+                                                        __nv_bfloat16* __restrict__ dy, long long rows, int f,
+                                                        const int* __restrict__ rows_dev) {
   const int fv = f >> 3;
+  if (rows_dev != nullptr) rows = min(rows, (long long)*rows_dev);
   const long long total = rows * fv;
   for (long long i = (long long)blockIdx.x * NT + threadIdx.x; i < total; i += (long long)gridDim.x * NT) {
     const long long r = i / fv;
@@ -448,14 +452,29 @@ int dh_layernorm_bwd(const void* dy, const void* x, const void* w, const void* m
 int dh_swiglu_fwd(const void* y, void* out, int64_t rows, int f, int sm_budget, cudaStream_t s) {
   DH_REQUIRE(f % 8 == 0, "ffn width must be a multiple of 8");
   if (rows <= 0) return 0;
-  swiglu_fwd_kernel<<<grid_for((rows * (f / 8) + NT - 1) / NT, 8, sm_budget), NT, 0, s>>>((const __nv_bfloat16*)y, (__nv_bfloat16*)out, rows, f);
+  swiglu_fwd_kernel<<<grid_for((rows * (f / 8) + NT - 1) / NT, 8, sm_budget), NT, 0, s>>>((const __nv_bfloat16*)y, (__nv_bfloat16*)out, rows, f, nullptr);
   return launch_rc("dh_swiglu_fwd");
+}
+// Ragged form: `rows` is the capacity, the number of rows in use is read from device memory (*rows_dev).
+int dh_swiglu_fwd_n(const void* y, void* out, int64_t rows, const void* rows_dev, int f, int sm_budget, cudaStream_t s) {
+  DH_REQUIRE(f % 8 == 0, "ffn width must be a multiple of 8");
+  if (rows <= 0) return 0;
+  swiglu_fwd_kernel<<<grid_for((rows * (f / 8) + NT - 1) / NT, 8, sm_budget), NT, 0, s>>>((const __nv_bfloat16*)y, (__nv_bfloat16*)out, rows, f,
+                                                                                         (const int*)rows_dev);
+  return launch_rc("dh_swiglu_fwd_n");
+}
+int dh_swiglu_bwd_n(const void* dout, const void* y, void* dy, int64_t rows, const void* rows_dev, int f, int sm_budget, cudaStream_t s) {
+  DH_REQUIRE(f % 8 == 0, "ffn width must be a multiple of 8");
+  if (rows <= 0) return 0;
+  swiglu_bwd_kernel<<<grid_for((rows * (f / 8) + NT - 1) / NT, 8, sm_budget), NT, 0, s>>>((const __nv_bfloat16*)dout, (const __nv_bfloat16*)y,
+                                                                                         (__nv_bfloat16*)dy, rows, f, (const int*)rows_dev);
+  return launch_rc("dh_swiglu_bwd_n");
 }
 int dh_swiglu_bwd(const void* dout, const void* y, void* dy, int64_t rows, int f, int sm_budget, cudaStream_t s) {
   DH_REQUIRE(f % 8 == 0, "ffn width must be a multiple of 8");
   if (rows <= 0) return 0;
   swiglu_bwd_kernel<<<grid_for((rows * (f / 8) + NT - 1) / NT, 8, sm_budget), NT, 0, s>>>((const __nv_bfloat16*)dout, (const __nv_bfloat16*)y,
-                                                                                         (__nv_bfloat16*)dy, rows, f);
+                                                                                         (__nv_bfloat16*)dy, rows, f, nullptr);
   return launch_rc("dh_swiglu_bwd");
 }
 int dh_gelu_fwd(const void* x, void* out, int64_t n, int sm_budget, cudaStream_t s) {

@@ -366,6 +366,13 @@ struct PairParams {
   int perm_mode, perm_world, perm_rank;
   long long wait_budget;               // cycles for the barriers inside the CTA
   DeviceStatus* status;
+  // grouped (ragged) form for mixture-of-experts layers: `groups` experts share one launch.
+  //   group_mode 1  rows grouped: A and D rows are expert-major with region starts group_offs[e] (multiples of 256,
+  //                 device memory: the sizes never reach the host); B is the stack of the experts' weights
+  //   group_mode 2  contraction grouped (weight gradients): D is the stack of per-expert [M, N] outputs, the
+  //                 contraction of expert e runs over rows [group_offs[e], group_offs[e+1]) of A and B
+  int group_mode, groups;
+  const int* group_offs;
   // collective carried by the communication warps (COMM form of the kernel only):
   // 0 none, 1 = push this rank's shard of the gathered A operand, 2 = reduce this rank's rows of the partial products
   int comm_kind;
@@ -386,19 +393,60 @@ __device__ __forceinline__ int perm_tile_m(int i, const PairParams& p) {
   return ((p.perm_rank + 1 + r) % p.perm_world) * per + j;
 }
 
-// Work item -> (tile row, tile column, first k-block, end k-block).
-__device__ __forceinline__ void item_coords(int item, const PairParams& p, int num_tiles, int num_kb, int& tm, int& tn, int& kb0, int& kb1) {
+// Work item -> (tile row, tile column, first k-block, end k-block) plus, in the grouped forms, the expert.
+struct Item {
+  int tm, tn, kb0, kb1;
+  int b_off;            // added to B's outer coordinate (expert's weight inside the stack)
+  int d_row_off;        // added to D's row coordinate (expert's output inside the stack)
+};
+
+__device__ __forceinline__ int num_items_of(const PairParams& p, int& num_tiles) {
+  if (p.group_mode == 1) {
+    num_tiles = (p.group_offs[p.groups] / TILE_M) * p.tiles_n;       // rows in use are known on the device only
+    return num_tiles;
+  }
+  if (p.group_mode == 2) {
+    num_tiles = p.groups * p.tiles_m * p.tiles_n;
+    return num_tiles;
+  }
+  num_tiles = p.tiles_m * p.tiles_n;
+  return num_tiles * p.split_k;
+}
+
+__device__ __forceinline__ Item item_coords(int item, const PairParams& p, int num_tiles, int num_kb) {
+  Item it;
+  it.b_off = 0;
+  it.d_row_off = 0;
+  if (p.group_mode == 2) {
+    const int per = p.tiles_m * p.tiles_n;
+    const int e = item / per;
+    const int t = item - e * per;
+    it.tm = t % p.tiles_m;
+    it.tn = t / p.tiles_m;
+    it.kb0 = p.group_offs[e] / BK;
+    it.kb1 = p.group_offs[e + 1] / BK;
+    it.d_row_off = e * p.M;
+    return it;
+  }
+  const int tiles_m = p.group_mode == 1 ? num_tiles / p.tiles_n : p.tiles_m;
   const int ks = item / num_tiles;
   const int t = item - ks * num_tiles;
   const int band = p.group_m * p.tiles_n;
   const int g = t / band;
   const int first_m = g * p.group_m;
-  const int rows = min(p.group_m, p.tiles_m - first_m);
+  const int rows = min(p.group_m, tiles_m - first_m);
   const int r = t - g * band;
-  tm = perm_tile_m(first_m + (r % rows), p);
-  tn = r / rows;
-  kb0 = ks * p.kb_per_split;
-  kb1 = min(num_kb, kb0 + p.kb_per_split);
+  it.tm = perm_tile_m(first_m + (r % rows), p);
+  it.tn = r / rows;
+  it.kb0 = ks * p.kb_per_split;
+  it.kb1 = min(num_kb, it.kb0 + p.kb_per_split);
+  if (p.group_mode == 1) {
+    const int row = it.tm * TILE_M;
+    int e = 0;
+    while (e + 1 < p.groups && row >= p.group_offs[e + 1]) ++e;
+    it.b_off = e;                                  // expert index; scaled by the caller (B's major decides by what)
+  }
+  return it;
 }
 
 __device__ __forceinline__ bool wait_block_counter(const uint32_t* c, uint32_t want, volatile int* abort_flag, DeviceStatus* st, int where) {
@@ -436,8 +484,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   const uint32_t rank = cluster_ctarank();          // 0 = leader
   const int pair_id = blockIdx.x >> 1;
   const int num_pairs = gridDim.x >> 1;
-  const int num_tiles = p.tiles_m * p.tiles_n;      // tiles of 256 x 256
-  const int num_items = num_tiles * p.split_k;
+  int num_tiles;                                    // tiles of 256 x 256
+  const int num_items = num_items_of(p, num_tiles);
   const int num_kb = (p.K + BK - 1) / BK;
 
   if (threadIdx.x == 0) {
@@ -474,10 +522,13 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       bool ok = true;
       int ready_block = -1;
       for (int it = pair_id; it < num_items && ok; it += num_pairs) {
-        int tm, tn, kb0, kb1;
-        item_coords(it, p, num_tiles, num_kb, tm, tn, kb0, kb1);
+        const Item im = item_coords(it, p, num_tiles, num_kb);
+        const int tm = im.tm, tn = im.tn, kb0 = im.kb0, kb1 = im.kb1;
         const int m0 = tm * TILE_M + (int)rank * BM;
         const int n0 = tn * BN + (int)rank * BN_HALF;
+        // grouped rows: B is the stack of the experts' weights ([groups * N, K] K-major, or [groups * K, N] MN-major)
+        const int bn_off = (p.group_mode == 1 && !B_MN) ? im.b_off * p.N : 0;
+        const int bk_off = (p.group_mode == 1 && B_MN) ? im.b_off * p.K : 0;
         if (p.wait_count != nullptr) {
           const int blk = m0 / BM;
           if (blk != ready_block && m0 < p.M) {
@@ -501,9 +552,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           }
           if (B_MN) {
 #pragma unroll
-            for (int j = 0; j < BN_HALF / 64; ++j) tma_load_2d_2sm(b_dst + j * (BK * 128), &tmap_b, full_leader, n0 + 64 * j, k0);
+            for (int j = 0; j < BN_HALF / 64; ++j) tma_load_2d_2sm(b_dst + j * (BK * 128), &tmap_b, full_leader, n0 + 64 * j, k0 + bk_off);
           } else {
-            tma_load_2d_2sm(b_dst, &tmap_b, full_leader, k0, n0);
+            tma_load_2d_2sm(b_dst, &tmap_b, full_leader, k0, n0 + bn_off);
           }
           if (++s == p.stages) { s = 0; ph ^= 1; }
         }
@@ -520,8 +571,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       uint32_t acc_ph = 0;
       bool ok = true;
       for (int it = pair_id; it < num_items && ok; it += num_pairs) {
-        int tm, tn, kb0, kb1;
-        item_coords(it, p, num_tiles, num_kb, tm, tn, kb0, kb1);
+        const Item im = item_coords(it, p, num_tiles, num_kb);
+        const int kb0 = im.kb0, kb1 = im.kb1;
+        if (kb0 >= kb1) continue;                       // an expert without rows: nothing to add (all roles skip the item)
         if (!mbar_wait<true>(&ctl->acc_empty[acc], acc_ph ^ 1, abort_flag, p.status, 210, p.wait_budget)) { ok = false; break; }
         tc_fence_after();
         const uint32_t tmem_acc = tmem_base + acc * ACC_COLS;
@@ -571,8 +623,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     uint32_t cc = 0;                                // running chunk count -> staging tile parity
     bool ok = true;
     for (int it = pair_id; it < num_items && ok; it += num_pairs) {
-      int tm, tn, kb0, kb1;
-      item_coords(it, p, num_tiles, num_kb, tm, tn, kb0, kb1);
+      const Item im = item_coords(it, p, num_tiles, num_kb);
+      const int tm = im.tm, tn = im.tn;
+      if (im.kb0 >= im.kb1) continue;
       if (!mbar_wait(&ctl->acc_full[acc], acc_ph, abort_flag, p.status, 310, p.wait_budget)) { ok = false; break; }
       tc_fence_after();
       const int row0 = tm * TILE_M + (int)rank * BM + quarter * 32;     // first of this warp's 32 output rows
@@ -608,8 +661,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           fence_proxy_async_smem();
           __syncwarp();
           if (lane == 0) {
-            if (p.reduce_add) tma_reduce_add_2d(&tmap_d, tile, col0, row0);
-            else tma_store_2d(&tmap_d, tile, col0, row0);
+            if (p.reduce_add) tma_reduce_add_2d(&tmap_d, tile, col0, row0 + im.d_row_off);
+            else tma_store_2d(&tmap_d, tile, col0, row0 + im.d_row_off);
             tma_store_commit();
           }
           ++cc;
@@ -959,4 +1012,70 @@ extern "C" int dh_gemm_rs_bf16(const void* a, int64_t lda, const void* b, int64_
   sy.comm_kind = 2;
   sy.reduce = &job;
   return dh::gemm::gemm_impl(a, lda, 0, b, ldb, b_mn_major, part_ptrs[rank], N, 0, 0, M, N, K, sm_budget, sy, stream);
+}
+
+// Grouped (ragged) GEMM over the experts of a mixture-of-experts layer in ONE launch; the per-expert row ranges
+// `offs` ([groups + 1] int32, multiples of 256) live in device memory and are never read by the host.
+//   group_mode 1 (rows grouped):  D[rows, N] = A[rows, K] * op(B_e) for the rows of expert e.
+//       A is [capacity, K] K-major, D is [capacity, N] bf16 (capacity = M);
+//       b_mn_major = 0: B is the stack [groups * N, K] (forward: y = x W_e^T);
+//       b_mn_major = 1: B is the stack [groups * K, N] (data gradient: dx = dy W_e).
+//   group_mode 2 (contraction grouped, weight gradients):  D_e[M, N] += A_e^T B_e with A [capacity, M] and
+//       B [capacity, N] both MN-major and the contraction of expert e over rows [offs[e], offs[e+1]);
+//       D is the stack [groups * M, N] fp32, added in place.  M must be a multiple of 256.
+extern "C" int dh_gemm_grouped_bf16(const void* a, int64_t lda, const void* b, int64_t ldb, int b_mn_major, void* d, int64_t ldd, int M,
+                                    int N, int K, int groups, int group_mode, const void* offs, int capacity, int sm_budget,
+                                    cudaStream_t stream) {
+  using namespace dh;
+  using namespace dh::gemm;
+  using namespace dh::gemm::pair;
+  if (groups < 1 || (group_mode != 1 && group_mode != 2) || offs == nullptr || capacity <= 0 || capacity % TILE_M != 0) {
+    set_last_error("dh_gemm_grouped_bf16: bad arguments (groups %d, mode %d, capacity %d)", groups, group_mode, capacity);
+    return (int)cudaErrorInvalidValue;
+  }
+  const bool wgrad = group_mode == 2;
+  if (wgrad && (M % TILE_M != 0)) { set_last_error("dh_gemm_grouped_bf16: grouped weight gradients need M %% 256 == 0 (M=%d)", M); return (int)cudaErrorInvalidValue; }
+  const int elem = wgrad ? 4 : 2;
+  if ((ldd % (wgrad ? 4 : 8)) != 0 || (reinterpret_cast<uintptr_t>(d) & 15) != 0) { set_last_error("dh_gemm_grouped_bf16: output alignment"); return (int)cudaErrorInvalidValue; }
+  const CUtensorMap *ta, *tb;
+  if (!wgrad) {
+    ta = get_tmap_2d(a, 2, (uint64_t)K, (uint64_t)capacity, (uint64_t)lda * 2, BK, BM, true);
+    tb = b_mn_major ? get_tmap_2d(b, 2, (uint64_t)N, (uint64_t)groups * K, (uint64_t)ldb * 2, 64, BK, true)
+                    : get_tmap_2d(b, 2, (uint64_t)K, (uint64_t)groups * N, (uint64_t)ldb * 2, BK, BN_HALF, true);
+  } else {
+    ta = get_tmap_2d(a, 2, (uint64_t)M, (uint64_t)capacity, (uint64_t)lda * 2, 64, BK, true);
+    tb = get_tmap_2d(b, 2, (uint64_t)N, (uint64_t)capacity, (uint64_t)ldb * 2, 64, BK, true);
+  }
+  if (!ta || !tb) return (int)cudaErrorInvalidValue;
+  CUtensorMap td;
+  const uint64_t d_rows = wgrad ? (uint64_t)groups * M : (uint64_t)capacity;
+  if (!encode_tmap_2d_into(&td, d, elem, (uint64_t)N, d_rows, (uint64_t)ldd * elem, wgrad ? 32 : 64, 32, true)) return (int)cudaErrorInvalidValue;
+  static int stages = 0;
+  if (stages == 0) {
+    const char* e = getenv("DHELLAM_GEMM_STAGES");
+    stages = e ? atoi(e) : RING;
+    if (stages < 2 || stages > RING) stages = RING;
+  }
+  PairParams p;
+  memset(&p, 0, sizeof(p));
+  p.M = wgrad ? M : capacity;
+  p.N = N;
+  p.K = wgrad ? capacity : K;
+  p.tiles_m = wgrad ? M / TILE_M : capacity / TILE_M;
+  p.tiles_n = (N + BN - 1) / BN;
+  p.stages = stages;
+  p.group_m = 8;
+  p.split_k = 1;
+  p.kb_per_split = (p.K + BK - 1) / BK;
+  p.reduce_add = wgrad ? 1 : 0;
+  p.group_mode = group_mode;
+  p.groups = groups;
+  p.group_offs = reinterpret_cast<const int*>(offs);
+  p.wait_budget = (long long)DH_WAIT_BUDGET_CYCLES;
+  p.status = reinterpret_cast<DeviceStatus*>(dh_status_device_ptr());
+  const int sms = dh_sm_count();
+  const int budget = (sm_budget <= 0 || sm_budget > sms) ? sms : sm_budget;
+  const int pairs = budget / 2 < 1 ? 1 : budget / 2;
+  if (wgrad) return launch_pair<true, true, true>(ta, tb, &td, p, pairs, stream);
+  return b_mn_major ? launch_pair<false, true, false>(ta, tb, &td, p, pairs, stream) : launch_pair<false, false, false>(ta, tb, &td, p, pairs, stream);
 }

@@ -67,7 +67,11 @@ class Trainer:
             # key/value exchange of context parallelism over peer memory instead of the library ring
             from .ops.fused_comm import FusedCP
             self.env.fused_cp = FusedCP(self.ps, cfg, train, self.device)
-        elif self.device.type == "cpu" and self.ps.cp > 1 and os.environ.get("DHELLAM_CP_GATHER_SIM", "0") == "1":
+        if cfg.is_moe and self.device.type == "cuda" and _K.backend() == "native" and os.environ.get("DHELLAM_MOE_HOST", "0") != "1":
+            # token dispatch / combine and the grouped expert GEMMs without the host in the loop
+            from .ops.moe_native import DeviceMoE
+            self.env.moe_dev = DeviceMoE(self.ps, cfg, train, self.device, train.micro_batch_size * cfg.seq_length // max(self.ps.cp, 1))
+        if self.device.type == "cpu" and self.ps.cp > 1 and os.environ.get("DHELLAM_CP_GATHER_SIM", "0") == "1":
             from .ops.fused_comm import SimulatedCP           # the gather form on library collectives (tests on CPU ranks)
             self.env.fused_cp = SimulatedCP(self.ps, cfg, train, self.device)
         if strategy is None and train.schedule_config:
@@ -145,6 +149,7 @@ class Trainer:
         if self.env is not None:
             self.env.fused = None
             self.env.fused_cp = None
+            self.env.moe_dev = None
         self.engine = self.optimizer = self.model = self.env = None
 
     def tokens_per_step(self) -> int:

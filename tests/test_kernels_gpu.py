@@ -278,3 +278,70 @@ def test_communication_wait_entry_point_gives_up_after_its_budget():
     K.check(fn(counters.data_ptr(), 16, 3, 2_000_000, K.stream_ptr(None)), "dh_wait_counters")
     assert K.read_status().code == 0
     assert float(torch.ones(4, device=DEV).sum()) == 4.0
+
+
+def test_device_resident_moe_exchange_and_grouped_gemms():
+    """Plan -> dispatch -> grouped expert GEMMs -> combine on one GPU (ep = 1) against plain PyTorch: the
+    routing sizes never reach the host on the device path, the reference below sorts on the host."""
+    from types import SimpleNamespace
+    from dhellam_b200.ops.moe_native import DeviceMoE
+    E, k, h, f, T = 4, 2, 512, 256, 300
+    cfg = SimpleNamespace(num_experts=E, moe_top_k=k, hidden_size=h)
+    ps = SimpleNamespace(ep=1, ep_rank=0, ep_group=None)
+    dev = DeviceMoE(ps, cfg, None, torch.device(DEV), T)
+    x = bf(T, h)
+    logits = torch.randn(T, E, device=DEV)
+    topi = logits.topk(k, dim=-1).indices.to(torch.int32).contiguous()
+    gates = torch.softmax(torch.randn(T, k, device=DEV), -1).contiguous()
+    plan = dev.plan(topi)
+    slot, _ = dev.dispatch(plan, x, "xe", record=True)
+    xe = dev.landed("xe", slot)
+    torch.cuda.synchronize()
+    offs, rows_e = plan.offs.cpu().tolist(), plan.rows_e.cpu().tolist()
+    flat = topi.reshape(-1).cpu()
+    assert int(plan.overflow) == 0 and all(o % 256 == 0 for o in offs)
+    for e in range(E):
+        idx = torch.nonzero(flat == e).squeeze(1)              # stable order of the copies of expert e
+        assert rows_e[e] == idx.numel()
+        got = xe[offs[e]:offs[e] + rows_e[e]].cpu()
+        assert torch.equal(got, x.cpu()[idx // k]), e
+        assert float(xe[offs[e] + rows_e[e]:offs[e + 1]].abs().max() if offs[e + 1] > offs[e] + rows_e[e] else 0.0) == 0.0
+    w1 = bf(E, 2 * f, h, scale=0.05)
+    w2 = bf(E, h, f, scale=0.05)
+    z = dev.grouped_nt(xe, w1, plan)
+    a = dev.swiglu_fwd(z, plan)
+    y, yslot = dev.output_buffer("y")
+    dev.grouped_nt(a, w2, plan, out=y)
+    dev.publish("y", yslot)
+    out, copies = dev.combine(plan, "y", yslot, gates=gates, keep_copies=True)
+    torch.cuda.synchronize()
+    # reference: per token, per choice
+    xf = x.float()
+    ref = torch.zeros(T, h, device=DEV)
+    for j in range(k):
+        for e in range(E):
+            m = topi[:, j] == e
+            if m.any():
+                zz = (xf[m] @ w1[e].float().t()).to(torch.bfloat16).float()
+                aa = (torch.nn.functional.silu(zz[:, :f]) * zz[:, f:]).to(torch.bfloat16).float()
+                yy = (aa @ w2[e].float().t()).to(torch.bfloat16).float()
+                ref[m] += gates[m, j:j + 1] * yy
+    assert rel(out, ref) < 1e-2, rel(out, ref)
+    # backward products on the same plan
+    d_y = torch.zeros_like(y)
+    for e in range(E):
+        d_y[offs[e]:offs[e] + rows_e[e]] = bf(rows_e[e], h)
+    d_a = dev.grouped_nn(d_y, w2, plan)
+    g2 = torch.ones(E, h, f, device=DEV)
+    dev.grouped_tn_acc(d_y, a, g2, plan)
+    torch.cuda.synchronize()
+    for e in range(E):
+        lo, hi = offs[e], offs[e] + rows_e[e]
+        assert rel(d_a[lo:hi], d_y[lo:hi].float() @ w2[e].float()) < 5e-3
+        assert rel(g2[e], 1 + d_y[lo:hi].float().t() @ a[lo:hi].float()) < 1e-3
+    # the pull without gates is the plain sum over a token's copies
+    s2, sslot = dev.output_buffer("dxe")
+    s2.copy_(y)
+    dev.publish("dxe", sslot)
+    summed, _ = dev.combine(plan, "dxe", sslot)
+    assert rel(summed, copies.float().view(T, k, h).sum(1)) < 1e-2

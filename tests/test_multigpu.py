@@ -262,3 +262,44 @@ def test_context_parallel_with_tensor_parallel_on_four_gpus(tmp_path):
     ref, got = torch.load(a), torch.load(b)
     for x, y in zip(got["losses"], ref["losses"]):
         assert abs(x - y) / abs(y) < 1e-2, (got["losses"], ref["losses"])
+
+
+def _moe_worker(rank, world, out_path):
+    from dhellam_b200 import kernels as K
+    from dhellam_b200.config import ModelConfig, ParallelConfig, TrainConfig
+    from dhellam_b200.data import make_microbatch, synthetic_tokens
+    from dhellam_b200.models.sharding import random_full_head, random_full_layer
+    from dhellam_b200.trainer import Trainer
+    cfg = ModelConfig(name="t-moe", num_layers=2, hidden_size=512, ffn_hidden_size=512, num_attention_heads=4,
+                      num_query_groups=2, head_dim=128, vocab_size=2048, seq_length=256, num_experts=4, moe_top_k=2,
+                      moe_aux_loss_coeff=0.0)
+    train = TrainConfig(micro_batch_size=2, global_batch_size=2 * world, dtype="bf16", clip_grad=0.0)
+    tr = Trainer(cfg, ParallelConfig(dp=world, ep=world), train, device=torch.device("cuda", rank))
+    assert tr.env.moe_dev is not None and tr.env.moe_dev.ep == world
+    for i in range(cfg.num_layers):
+        tr.model.load_full_layer_weights(i, random_full_layer(cfg, i, 3))
+    tr.model.load_full_head_weights(random_full_head(cfg, 3))
+    # every data-parallel rank gets its own micro-batch; the single-GPU run sees both in turn
+    samples = [synthetic_tokens(cfg, 2, 40 + r) for r in range(2)]
+    if world == 1:
+        mbs = [make_microbatch(cfg, tr.ps, s, i, 40 + i, tr.device) for i, s in enumerate(samples)]
+    else:
+        mbs = [make_microbatch(cfg, tr.ps, samples[rank], 0, 40 + rank, tr.device)]
+    tr.optimizer.zero_grad()
+    losses = tr.engine.run_step(mbs)
+    torch.cuda.synchronize()
+    assert K.read_status().code == 0
+    torch.save({"losses": [float(l) for l in losses]}, out_path + f".{rank}")
+
+
+def test_expert_parallel_device_exchange_matches_single_gpu(tmp_path):
+    """ep = 2 over peer memory (device-side plan, push dispatch, grouped expert GEMMs, pull combine): each rank's
+    micro-batch loss equals the loss of the same micro-batch on one GPU with all experts local."""
+    _need(2)
+    a, b = str(tmp_path / "one"), str(tmp_path / "two")
+    run_gpu_ranks(_moe_worker, 1, a)
+    run_gpu_ranks(_moe_worker, 2, b)
+    ref = torch.load(a + ".0")["losses"]
+    got = [torch.load(b + ".0")["losses"][0], torch.load(b + ".1")["losses"][0]]
+    for x, y in zip(got, ref):
+        assert abs(x - y) / abs(y) < 1e-2, (got, ref)
