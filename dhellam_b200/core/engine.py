@@ -162,6 +162,12 @@ class DoubleStrandEngine:
             else:
                 x, g = self._inbox["next"]
         self._inbox = {"next": [None, None], "prev": [None, None]}
+        if st.cuda:
+            evs, self._inbox_events = getattr(self, "_inbox_events", [None, None]), [None, None]
+            if evs[0] is not None:
+                st.s1.wait_event(evs[0])              # the forward strand waits for its activation only
+            if evs[1] is not None:
+                st.s2.wait_event(evs[1])              # the backward strand for its gradient only
         if fb and st.cuda and b in self.fwd_done:
             st.s2.wait_event(self.fwd_done[b])
 
@@ -238,9 +244,13 @@ class DoubleStrandEngine:
         st = self.streams
         mb0 = mbs[0]
         shape = (mb0.tokens.numel() // ps.tp, self.cfg.hidden_size)
-        if st.cuda:
-            st.s3.wait_stream(st.s1)
-            st.s3.wait_stream(st.s2)
+        # One group per strand.  The forward strand's activation is ready when the last forward op of the sweep
+        # has run, which in the paired schedule is well before the last backward op: its transfer overlaps the
+        # rest of the backward strand.  The receiving side lets each strand of the next tick wait for its own
+        # tensor only.
+        last = {0: self.program.names("fwd")[-1], 1: self.program.names("bwd")[-1]}
+        from_next, from_prev = [None, None], [None, None]
+        events = [None, None]
         self._set_stream("S3")
         t0 = None
         if self.time_pp:
@@ -249,12 +259,26 @@ class DoubleStrandEngine:
                 t0.record(st.s3)
             else:
                 t0 = time.perf_counter()
-        with self._on("S3"):
-            for tns in list(send_next) + list(send_prev):
-                if tns is not None and tns.is_cuda:
-                    tns.record_stream(st.s3)
-            from_next, from_prev = PP.exchange(ps, send_next, send_prev, recv_next, recv_prev, shape, self.env.dtype,
-                                               self.env.device)
+        for slot in (0, 1):
+            sending = [t for t in (send_next[slot], send_prev[slot]) if t is not None]
+            if not sending and not (recv_next[slot] or recv_prev[slot]):
+                continue
+            if st.cuda:
+                rec = self.executor._events.get(last[slot]) if sending else None
+                if rec is not None:
+                    st.s3.wait_event(rec[0])            # the op that produced this strand's tensor
+                elif sending:
+                    st.s3.wait_stream(st.s1 if slot == 0 else st.s2)
+                for tns in sending:
+                    if tns.is_cuda:
+                        tns.record_stream(st.s3)
+            with self._on("S3"):
+                fn, fp = PP.exchange(ps, send_next, send_prev, recv_next, recv_prev, shape, self.env.dtype, self.env.device,
+                                     slots=(slot,))
+            from_next[slot], from_prev[slot] = fn[slot], fp[slot]
+            if st.cuda:
+                events[slot] = torch.cuda.Event()
+                events[slot].record(st.s3)
         if t0 is not None:
             if st.cuda:
                 t1 = torch.cuda.Event(enable_timing=True)
@@ -262,10 +286,8 @@ class DoubleStrandEngine:
                 self._pp_spans.append((t0, t1))
             else:
                 self._pp_spans.append((t0, time.perf_counter()))
-        if st.cuda:
-            st.s1.wait_stream(st.s3)
-            st.s2.wait_stream(st.s3)
         self._inbox = {"next": from_next, "prev": from_prev}
+        self._inbox_events = events
 
     def measure_exposed(self, on: bool):
         """Switches the exposed-communication measurement on or off (see ``ExposedTimer``)."""

@@ -9,6 +9,11 @@ layer's contiguous slice of the flat buffer on the communication stream, under t
 the backward pass.  Because of the fold, layers become final in two interleaved descending
 orders (second-half layers during down sweeps, first-half layers during up sweeps); each
 (block pair, half) is one bucket.
+
+With the distributed optimizer (every rank owns a contiguous 1/dp slice of the flat buffer) a
+bucket is not all-reduced but reduce-scattered: every piece of the bucket is reduced straight to
+the rank whose optimizer shard it falls into (``shard_bounds``), half the bytes of an all-reduce,
+and still under the backward pass.
 """
 from __future__ import annotations
 
@@ -35,6 +40,26 @@ class OverlappedGradReducer:
                 self.buckets[idx] = (min(o for o, _ in offs), max(e for _, e in offs))
         self.handles: List = []
         self.done: set = set()
+        # [lo, hi) of every group rank's optimizer shard; None = replicated optimizer (all-reduce)
+        self.shard_bounds = None
+
+    def set_shards(self, bounds):
+        """``bounds[r] = (lo, hi)`` of group rank ``r``'s slice of the flat buffer (distributed optimizer)."""
+        self.shard_bounds = list(bounds)
+
+    def _reduce(self, lo: int, hi: int, async_op: bool):
+        """Reduces ``flat_grad[lo:hi]`` over the group: to everybody, or piecewise to the owners."""
+        g = self.model.flat_grad
+        out = []
+        if self.shard_bounds is None:
+            out.append(dist.all_reduce(g[lo:hi], group=self.group, async_op=async_op))
+            return out
+        ranks = dist.get_process_group_ranks(self.group)
+        for r, (slo, shi) in enumerate(self.shard_bounds):
+            a, b = max(lo, slo), min(hi, shi)
+            if a < b:
+                out.append(dist.reduce(g[a:b], dst=ranks[r], group=self.group, async_op=async_op))
+        return out
 
     def active(self) -> bool:
         return self.size > 1 and not (self.model.cfg.is_moe and self.ps.ep > 1)
@@ -47,19 +72,19 @@ class OverlappedGradReducer:
         if not self.active() or layer_index in self.done:
             return
         lo, hi = self.buckets[layer_index]
-        g = self.model.flat_grad[lo:hi]
         st = self.streams
         if st is not None and st.cuda:
             st.s3.wait_stream(producer_stream if producer_stream is not None else st.s2)
             with torch.cuda.stream(st.s3):
-                self.handles.append(dist.all_reduce(g, group=self.group, async_op=True))
+                self.handles.extend(self._reduce(lo, hi, True))
         else:
-            dist.all_reduce(g, group=self.group)
+            self._reduce(lo, hi, False)
         self.done.add(layer_index)
 
     def finish(self):
         """Reduces what is left (head block, padding) and waits for the overlapped buckets.
-        Returns True if the whole flat buffer now holds the SUM over the group."""
+        Returns True if the flat buffer (this rank's shard of it, with the distributed optimizer) now holds
+        the SUM over the group."""
         if not self.active():
             return False
         for h in self.handles:
@@ -69,6 +94,6 @@ class OverlappedGradReducer:
         pos = 0
         for lo, hi in covered + [(g.numel(), g.numel())]:
             if lo > pos:
-                dist.all_reduce(g[pos:lo], group=self.group)
+                self._reduce(pos, lo, False)
             pos = max(pos, hi)
         return True

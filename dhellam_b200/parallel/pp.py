@@ -18,12 +18,17 @@ import torch.distributed as dist
 
 
 def exchange(ps, send_next: Sequence[Optional[torch.Tensor]], send_prev: Sequence[Optional[torch.Tensor]],
-             recv_next: Sequence[bool], recv_prev: Sequence[bool], shape, dtype, device):
-    """Posts all sends/receives of one tick boundary and waits for them.
+             recv_next: Sequence[bool], recv_prev: Sequence[bool], shape, dtype, device, slots: Sequence[int] = (0, 1)):
+    """Posts the sends/receives of one tick boundary for the strands in ``slots`` (0 = forward
+    activation, 1 = backward gradient) as ONE group and waits for them (on GPUs the wait only
+    orders the current stream).
 
     ``send_*`` are lists (forward activation, backward gradient) with ``None`` for an
     absent strand; ``recv_*`` say which of the two to expect from that neighbour.
-    Returns ``(from_next, from_prev)`` lists with tensors or ``None``.
+    Returns ``(from_next, from_prev)`` lists with tensors or ``None``.  The engine calls this
+    once per strand: the forward strand's tensor leaves as soon as it exists, while the (longer)
+    backward strand of the same tick is still computing, and each strand of the next tick waits
+    for its own tensor only.
     """
     ops = []
     from_next: List[Optional[torch.Tensor]] = [None, None]
@@ -31,13 +36,13 @@ def exchange(ps, send_next: Sequence[Optional[torch.Tensor]], send_prev: Sequenc
     nxt, prv = ps.pp_next(), ps.pp_prev()
     # A fixed global order (slot 0 then slot 1; prev-direction then next-direction) keeps
     # the pairing of sends and receives identical on both sides.
-    for i in range(2):
+    for i in slots:
         if send_prev[i] is not None:
             ops.append(dist.P2POp(dist.isend, send_prev[i].contiguous(), prv, ps.pp_group))
         if recv_next[i]:
             from_next[i] = torch.empty(shape, dtype=dtype, device=device)
             ops.append(dist.P2POp(dist.irecv, from_next[i], nxt, ps.pp_group))
-    for i in range(2):
+    for i in slots:
         if send_next[i] is not None:
             ops.append(dist.P2POp(dist.isend, send_next[i].contiguous(), nxt, ps.pp_group))
         if recv_prev[i]:

@@ -101,9 +101,13 @@ class Trainer:
             # row-block-wise reduce-scatter: the reduction kernel may start once its GEMM has been launched
             self.engine.executor.pipeline = fused.rs_blocks and fused.policy == "split"
         self.optimizer = MixedPrecisionAdam(self.model, train, self.ps, distributed=distributed_optimizer)
-        if self.ps.dp * self.ps.cp > 1 and not distributed_optimizer:
+        if self.ps.dp * self.ps.cp > 1:
             from .parallel.dp import OverlappedGradReducer
             reducer = OverlappedGradReducer(self.model, self.ps, self.engine.streams)
+            if self.optimizer.distributed:
+                # gradient reduce-scatter into the optimizer shards, bucket by bucket under the backward pass
+                n, sh, gs = self.model.flat_param.numel(), self.optimizer.shard, self.optimizer.gsize
+                reducer.set_shards([(min(r * sh, n), min(r * sh + sh, n)) for r in range(gs)])
             self.engine.grad_reducer = reducer
             self.optimizer.grad_reducer = reducer
         GLOBAL_VARIABLES["loss_scale_func"] = self.optimizer.scale_loss

@@ -303,3 +303,53 @@ def test_expert_parallel_device_exchange_matches_single_gpu(tmp_path):
     got = [torch.load(b + ".0")["losses"][0], torch.load(b + ".1")["losses"][0]]
     for x, y in zip(got, ref):
         assert abs(x - y) / abs(y) < 1e-2, (got, ref)
+
+
+def _train_worker(rank, world, par, dist_opt, out_path):
+    """Two optimizer steps of a small Llama under the given parallel layout; every rank sees the same global batch."""
+    from dhellam_b200 import kernels as K
+    from dhellam_b200.config import ModelConfig, ParallelConfig, TrainConfig
+    from dhellam_b200.models.sharding import random_full_head, random_full_layer
+    from dhellam_b200.trainer import Trainer
+    cfg = ModelConfig(name="t-llama", num_layers=4, hidden_size=512, ffn_hidden_size=1024, num_attention_heads=4,
+                      num_query_groups=2, head_dim=128, vocab_size=2048, seq_length=256, rope_theta=500000.0)
+    train = TrainConfig(micro_batch_size=1, global_batch_size=4, dtype="bf16", lr=1e-3, weight_decay=0.0, clip_grad=1.0)
+    tr = Trainer(cfg, ParallelConfig(**par), train, device=torch.device("cuda", rank), distributed_optimizer=dist_opt)
+    from dhellam_b200.data import make_microbatch, synthetic_tokens
+    for i in range(cfg.num_layers):
+        tr.model.load_full_layer_weights(i, random_full_layer(cfg, i, 3))       # a stage keeps only the layers it owns
+    if tr.model.dchb is not None:
+        tr.model.load_full_head_weights(random_full_head(cfg, 3))
+    o = tr.optimizer
+    o.master.copy_(tr.model.flat_param[o.lo:o.hi].float())
+    tr.engine.time_pp = par.get("pp", 1) > 1
+    losses = []
+    dp, r = tr.ps.dp, tr.ps.dp_rank
+    for step in range(2):
+        # the same four samples per step whatever the layout; a data-parallel rank takes its share of them
+        mine = [j for j in range(4) if j * dp // 4 == r]
+        mbs = [make_microbatch(cfg, tr.ps, synthetic_tokens(cfg, 1, 900 + 10 * step + j), i, 900 + 10 * step + j, tr.device)
+               for i, j in enumerate(mine)]
+        l = tr.train_step(mbs)
+        losses.append(float(l) if l is not None else None)
+    torch.cuda.synchronize()
+    assert K.read_status().code == 0
+    if tr.engine.time_pp:
+        assert tr.engine.pp_bubble_ms() > 0.0
+    if losses[0] is not None and tr.ps.dp_rank == 0 and tr.ps.tp_rank == 0:
+        torch.save({"losses": losses}, out_path)
+
+
+@pytest.mark.parametrize("par,dist_opt", [(dict(pp=2), False), (dict(dp=2), True), (dict(dp=2), False)],
+                         ids=["pp2", "dp2-distributed-optimizer", "dp2"])
+def test_pipeline_and_data_parallel_training_on_gpus_match_one_gpu(tmp_path, par, dist_opt):
+    """pp = 2 (folded 1F1B, per-strand overlapped exchange) and dp = 2 (bucketed gradient reduction under the
+    backward pass; with the distributed optimizer a reduce-scatter into the optimizer shards) on two GPUs
+    against the same two optimizer steps on one GPU."""
+    _need(2)
+    a, b = str(tmp_path / "one.pt"), str(tmp_path / "two.pt")
+    run_gpu_ranks(_train_worker, 1, {}, False, a)
+    run_gpu_ranks(_train_worker, 2, par, dist_opt, b)
+    ref, got = torch.load(a)["losses"], torch.load(b)["losses"]
+    for x, y in zip(got, ref):
+        assert abs(x - y) / abs(y) < 2e-2, (got, ref)
