@@ -135,6 +135,10 @@ class FusedTP:
         self.rs_blocks = os.environ.get("DHELLAM_RS_BLOCKS", "1") != "0"
         self.total_sig = {t: [0, 0] for t in RS_TAGS}      # block-counter value reached so far, per (tag, slot)
         self._sig_arrays = {}
+        # The strategy search replays single ops out of their layer context (a consumer without its push, a
+        # reduction without its GEMM).  In lenient mode such a call works on the slot's last contents with the
+        # counter value already reached, so it measures the kernel without waiting; training never sets it.
+        self.lenient = False
 
     def split(self, M: int, N: int, Kd: int) -> bool:
         """Whether the collective beside the GEMM ``[M, Kd] x [Kd, N]`` runs as its own kernel."""
@@ -248,6 +252,9 @@ class FusedTP:
         self._pending.setdefault(tag, collections.deque()).append((slot, self.total_ag[tag][slot], M, Kd, ev))
 
     def gather_wait(self, tag: str):
+        if self.lenient and not self._pending.get(tag):
+            slot = (self.calls_ag[tag] - 1) & 1 if self.calls_ag[tag] else 0
+            return self._stage_view(tag, slot, self.rows, self.width)
         slot, target, M, Kd, ev = self._pending[tag].popleft()     # oldest first: a weight gradient may trail by one layer
         s = torch.cuda.current_stream(self.device)
         ctx = self.exposed.span(s) if (self.exposed is not None and self.exposed.enabled) else contextlib.nullcontext()
@@ -267,6 +274,9 @@ class FusedTP:
         if not self.ag_inkernel or measuring:
             return self.gather_wait(tag), None
         from .gemm import GemmSync
+        if self.lenient and not self._pending.get(tag):
+            slot = (self.calls_ag[tag] - 1) & 1 if self.calls_ag[tag] else 0
+            return self._stage_view(tag, slot, self.rows, self.width), None
         slot, target, M, Kd, ev = self._pending[tag].popleft()
         sync = GemmSync(wait_count=self.ptrs[self.rank] + self.off_agc[tag][slot], wait_target=target, perm_mode=1,
                         world=self.world, rank=self.rank)
@@ -308,6 +318,9 @@ class FusedTP:
 
     def rs_reduce(self, tag: str):
         """Runs on the current stream, which must already wait for the GEMM that filled the buffer."""
+        if self.lenient and tag not in self._split_pending:
+            slot = (self.calls_split[tag] - 1) & 1 if self.calls_split[tag] else 0
+            self._split_pending[tag] = (slot, 0, self.rows, self.width, self.total_sig[tag][slot])
         slot, use, M, N, block_target = self._split_pending.pop(tag)
         out = torch.empty((M // self.world, N), dtype=torch.bfloat16, device=self.device)
         s = torch.cuda.current_stream(self.device)

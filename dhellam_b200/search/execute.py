@@ -26,6 +26,9 @@ from .harness import LayerHarness
 def time_strategy(h: LayerHarness, strategy: Strategy, repeat: int = 10):
     """Returns ``(sequential ms, paired ms)`` for one block pair."""
     ex = Executor(h.program, strategy, h.streams)
+    if h.env.fused is not None:
+        ex.pipeline = h.env.fused.rs_blocks and h.env.fused.policy == "split"
+        h.env.exposed = ex.exposed
     name0_f, name0_b = next(iter(h.program.fwd)), next(iter(h.program.bwd))
     vf, af = h.snap[name0_f]
     vb, ab = h.snap[name0_b]
@@ -33,6 +36,7 @@ def time_strategy(h: LayerHarness, strategy: Strategy, repeat: int = 10):
     def runs():
         if h.env.fused is not None:
             h.env.fused._pending.clear()
+            h.env.fused._split_pending.clear()
         return (LayerRun(h.first, dict(af), h.mb, h.env, dict(vf), 0), LayerRun(h.first, dict(ab), h.mb, h.env, dict(vb), 0))
 
     def sequential():

@@ -29,6 +29,8 @@ class LayerHarness:
         one_pair = ModelConfig(**{**cfg.__dict__, "num_layers": 2 * ps.pp})
         self.model = DSLLM(one_pair, ps, train, device=self.device)
         self.env = Env(one_pair, ps, train, self.device, self.model.dtype, fused=fused)
+        if fused is not None:
+            fused.lenient = True           # ops are replayed out of context: never wait for a collective that is not part of the group
         self.program = build_layer_program(one_pair, cp=ps.cp)
         self.streams = StreamSet(self.device if self.device.type == "cuda" else None)
         self.env.streams = self.streams
@@ -75,6 +77,7 @@ class LayerHarness:
             fused = self.env.fused
             if fused is not None:
                 fused._pending.clear()
+                fused._split_pending.clear()
             state["run"] = LayerRun(self.first, dict(acts), self.mb, self.env, dict(v), 0)
 
         comp, comm = [], []

@@ -353,3 +353,11 @@ def test_pipeline_and_data_parallel_training_on_gpus_match_one_gpu(tmp_path, par
     ref, got = torch.load(a)["losses"], torch.load(b)["losses"]
     for x, y in zip(got, ref):
         assert abs(x - y) / abs(y) < 2e-2, (got, ref)
+
+
+def test_fused_collectives_at_world_8_with_headline_rows():
+    """All eight GPUs of a box, 16384 rows x 8192 columns (the per-micro-batch activation of the headline run):
+    one-kernel all-gather->GEMM and GEMM->reduce-scatter, the stand-alone push / row-block reduction with in-kernel
+    waits and signals, with and without the NVSwitch multicast alias, against the NCCL + GEMM composition."""
+    _need(8)
+    run_gpu_ranks(_fused_worker, 8, 16384, 8192, 1024, 1, timeout=600)
