@@ -5,9 +5,12 @@
 //   warp 0     TMA producer: Q once, then K_j / V_j tiles through 2-stage rings
 //   warp 1     MMA issuer:   S_j = Q K_j^T and O_j = P_j V_j with tcgen05.mma, S and O tiles
 //                            double-buffered in TMEM (4 x 128 columns = all 512)
-//   warps 2-5  softmax:      thread = query row; two passes over S_j in TMEM (row max, then
-//                            exp2 / row sum / bf16 P_j into swizzled shared memory), running
-//                            output kept in registers and rescaled once per block
+//   warps 2-9  softmax:      two warps per TMEM lane quarter; both own the same 32 query rows, each
+//                            takes 64 of the 128 score columns and 64 of the 128 output columns: two
+//                            passes over its part of S_j in TMEM (row max, exchanged inside the pair
+//                            through shared memory; then exp2 / row sum / bf16 P_j into swizzled
+//                            shared memory), running output kept in registers (64 per thread) and
+//                            rescaled once per block
 //   S_{j+1} and P_{j-1} V_{j-1} run on the tensor cores while the softmax warps work on S_j.
 //
 // Backward is two kernels that share delta = rowsum(dO * O):
@@ -77,10 +80,12 @@ struct FwdCtl {
   uint64_t s_full[2], p_ready[2], o_full[2];
   uint32_t tmem_base;
   int abort_flag;
+  float xch[2 * 128];            // row maximum / row sum exchange between the two softmax warps of a row
 };
-constexpr int FWD_SMEM = TILE_BYTES * 7 + 1024 + 256;   // Q, K x2, V x2, P x2
+constexpr int FWD_THREADS = 320;                         // TMA warp + MMA warp + 8 softmax warps
+constexpr int FWD_SMEM = TILE_BYTES * 7 + 1024 + 1280;  // Q, K x2, V x2, P x2, control
 
-__global__ void __launch_bounds__(THREADS, 1)
+__global__ void __launch_bounds__(FWD_THREADS, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ CUtensorMap tk, const __grid_constant__ CUtensorMap tv,
                 __nv_bfloat16* __restrict__ out, float* __restrict__ lse, const Geometry g) {
   extern __shared__ uint8_t smem_raw[];
@@ -108,7 +113,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
     for (int i = 0; i < 2; ++i) {
       mbar_init(&ctl->k_full[i], 1); mbar_init(&ctl->k_empty[i], 1);
       mbar_init(&ctl->v_full[i], 1); mbar_init(&ctl->v_empty[i], 1);
-      mbar_init(&ctl->s_full[i], 1); mbar_init(&ctl->p_ready[i], 4); mbar_init(&ctl->o_full[i], 1);
+      mbar_init(&ctl->s_full[i], 1); mbar_init(&ctl->p_ready[i], 8); mbar_init(&ctl->o_full[i], 1);
     }
     ctl->abort_flag = 0;
     mbar_fence_init();
@@ -176,31 +181,40 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
     }
     __syncwarp();
   } else {
+    // Eight softmax warps: two per TMEM lane quarter.  Both warps of a pair own the same 32 query rows;
+    // warp half `hf` handles score columns [64 hf, 64 hf + 64) of every key block and head-dim columns
+    // [64 hf, 64 hf + 64) of the running output.  The row maximum is exchanged through shared memory
+    // (one named barrier per pair), the row sums are added once at the end.  Two warps per scheduler hide
+    // the TMEM round trips that a single warp per scheduler exposes.  A warp whose wait gives up keeps
+    // walking the loop (every later wait returns at once through the CTA's abort flag), so the pair's
+    // barriers always match.
     const int quarter = warp & 3;
+    const int hf = (warp - 2) >> 2;
     const int r = quarter * 32 + lane;               // row inside the tile
     const int qi = qb * BQ + r;                      // global query index
     const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
     const float sl2 = g.scale * LOG2E;
+    float* xch = ctl->xch;                           // [2][128] exchange between the two warps of a pair
+    auto pair_sync = [&]() { asm volatile("bar.sync %0, 64;" ::"r"(1 + quarter) : "memory"); };
     float m = -FLT_MAX, l = 0.f;
-    float o[D];
+    float o[64];
 #pragma unroll
-    for (int i = 0; i < D; ++i) o[i] = 0.f;
+    for (int i = 0; i < 64; ++i) o[i] = 0.f;
     bool ok = nblk > 0;
-    for (int j = 0; j < nblk && ok; ++j) {
+    for (int j = 0; j < nblk; ++j) {
       const int s = j & 1;
       const uint32_t ph = (j >> 1) & 1;
-      if (!mbar_wait(&ctl->s_full[s], ph, abort_flag, g.status, 420)) { ok = false; break; }
+      if (ok && !mbar_wait(&ctl->s_full[s], ph, abort_flag, g.status, 420)) ok = false;
       tc_fence_after();
-      const uint32_t ts = tmem + s * 128 + lane_base;
-      const int key0 = j * BKV;
-      // which keys of this block may this row see
+      const uint32_t ts = tmem + s * 128 + lane_base + hf * 64;
+      const int key0 = j * BKV + hf * 64;            // first key of this warp's columns
       int limit = g.Sk - key0;                                        // keys beyond Sk are padding
       if (g.causal) limit = min(limit, qi + off - key0 + 1);
-      const bool full_block = limit >= BKV;
-      // pass 1: row maximum
+      const bool full_block = limit >= 64;
+      // pass 1: row maximum over this warp's 64 columns, then over the pair
       float bm = -FLT_MAX;
 #pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
+      for (int c = 0; c < 2; ++c) {
         uint32_t v[32];
         tmem_ld32(ts + c * 32, v);
         tmem_ld_wait();
@@ -212,14 +226,18 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
           for (int i = 0; i < 32; ++i) if (c * 32 + i < limit) bm = fmaxf(bm, __uint_as_float(v[i]));
         }
       }
+      xch[hf * 128 + r] = bm;
+      pair_sync();
+      bm = fmaxf(bm, xch[(hf ^ 1) * 128 + r]);
+      pair_sync();                                   // the partner has read before the next block overwrites
       const float m_new = fmaxf(m, bm);
       const float alpha = (m == -FLT_MAX) ? 0.f : exp2f((m - m_new) * sl2);
       const float mb = (m_new == -FLT_MAX) ? 0.f : m_new * sl2;
-      // pass 2: probabilities -> shared memory (bf16, swizzled), row sum
+      // pass 2: probabilities -> shared memory (bf16, swizzled), partial row sum
       float rs = 0.f;
       uint8_t* pdst = sP + s * TILE_BYTES;
 #pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
+      for (int c = 0; c < 2; ++c) {
         uint32_t v[32];
         tmem_ld32(ts + c * 32, v);
         tmem_ld_wait();
@@ -238,7 +256,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
           u.y = pack_bf16x2(p[q4 * 8 + 2], p[q4 * 8 + 3]);
           u.z = pack_bf16x2(p[q4 * 8 + 4], p[q4 * 8 + 5]);
           u.w = pack_bf16x2(p[q4 * 8 + 6], p[q4 * 8 + 7]);
-          *reinterpret_cast<uint4*>(pdst + swz_off(r, c * 4 + q4)) = u;
+          *reinterpret_cast<uint4*>(pdst + swz_off(r, hf * 8 + c * 4 + q4)) = u;
         }
       }
       l = l * alpha + rs;
@@ -247,14 +265,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
       fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) mbar_arrive(&ctl->p_ready[s]);
-      // fold in the previous block's P V (relative to the previous maximum), then rescale
+      // fold in the previous block's P V (relative to the previous maximum), then rescale: this warp's 64 head-dim columns
       if (j > 0) {
         const int sp = (j - 1) & 1;
-        if (!mbar_wait(&ctl->o_full[sp], ((j - 1) >> 1) & 1, abort_flag, g.status, 421)) { ok = false; break; }
+        if (ok && !mbar_wait(&ctl->o_full[sp], ((j - 1) >> 1) & 1, abort_flag, g.status, 421)) ok = false;
         tc_fence_after();
-        const uint32_t to = tmem + 256 + sp * 128 + lane_base;
+        const uint32_t to = tmem + 256 + sp * 128 + lane_base + hf * 64;
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
+        for (int c = 0; c < 2; ++c) {
           uint32_t v[32];
           tmem_ld32(to + c * 32, v);
           tmem_ld_wait();
@@ -264,15 +282,20 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
         tc_fence_before();
       }
     }
-    if (ok && nblk > 0) {
+    // the row sum of the whole row = the two halves' partial sums (same running maximum in both)
+    xch[hf * 128 + r] = l;
+    pair_sync();
+    l += xch[(hf ^ 1) * 128 + r];
+    if (nblk > 0) {
       const int sp = (nblk - 1) & 1;
-      if (mbar_wait(&ctl->o_full[sp], ((nblk - 1) >> 1) & 1, abort_flag, g.status, 422)) {
+      if (ok && !mbar_wait(&ctl->o_full[sp], ((nblk - 1) >> 1) & 1, abort_flag, g.status, 422)) ok = false;
+      if (ok) {
         tc_fence_after();
-        const uint32_t to = tmem + 256 + sp * 128 + lane_base;
+        const uint32_t to = tmem + 256 + sp * 128 + lane_base + hf * 64;
         const float inv = l > 0.f ? 1.f / l : 0.f;
-        __nv_bfloat16* orow = out + (long long)qi * g.o_s + (long long)b * g.o_b + (long long)hq * g.o_h;
+        __nv_bfloat16* orow = out + (long long)qi * g.o_s + (long long)b * g.o_b + (long long)hq * g.o_h + hf * 64;
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
+        for (int c = 0; c < 2; ++c) {
           uint32_t v[32];
           tmem_ld32(to + c * 32, v);
           tmem_ld_wait();
@@ -289,12 +312,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
             }
           }
         }
-        if (qi < g.Sq) lse[((long long)b * g.Hq + hq) * g.Sq + qi] = (l > 0.f) ? m * g.scale + logf(l) : -INFINITY;
+        if (hf == 0 && qi < g.Sq) lse[((long long)b * g.Hq + hq) * g.Sq + qi] = (l > 0.f) ? m * g.scale + logf(l) : -INFINITY;
       }
-    } else if (nblk == 0 && qi < g.Sq) {
-      __nv_bfloat16* orow = out + (long long)qi * g.o_s + (long long)b * g.o_b + (long long)hq * g.o_h;
-      for (int i = 0; i < D / 8; ++i) reinterpret_cast<uint4*>(orow)[i] = make_uint4(0, 0, 0, 0);
-      lse[((long long)b * g.Hq + hq) * g.Sq + qi] = -INFINITY;
+    } else if (qi < g.Sq) {
+      __nv_bfloat16* orow = out + (long long)qi * g.o_s + (long long)b * g.o_b + (long long)hq * g.o_h + hf * 64;
+      for (int i = 0; i < 64 / 8; ++i) reinterpret_cast<uint4*>(orow)[i] = make_uint4(0, 0, 0, 0);
+      if (hf == 0) lse[((long long)b * g.Hq + hq) * g.Sq + qi] = -INFINITY;
     }
   }
   tc_fence_before();
@@ -1093,7 +1116,7 @@ int dh_attn_fwd(const void* q, const void* k, const void* v, void* out, void* ls
   g.o_h = D; g.o_b = (long long)Hq * D; g.o_s = (long long)B * Hq * D;
   g.status = reinterpret_cast<DeviceStatus*>(dh_status_device_ptr());
   dim3 grid((Sq + BQ - 1) / BQ, Hq, B);
-  attn_fwd_kernel<<<grid, THREADS, FWD_SMEM, stream>>>(*tq, *tk, *tv, (__nv_bfloat16*)out, (float*)lse, g);
+  attn_fwd_kernel<<<grid, FWD_THREADS, FWD_SMEM, stream>>>(*tq, *tk, *tv, (__nv_bfloat16*)out, (float*)lse, g);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) set_last_error("dh_attn_fwd launch failed: %s", cudaGetErrorString(e));
   return (int)e;

@@ -201,5 +201,14 @@ __host__ __device__ inline int slices_for(int blocks, int width, int groups) {
   return s;
 }
 
+// Column slices per row block for the reduction: at least one per thread group, so that every group works on
+// the row block that has just become complete instead of one group owning it (the last block to complete would
+// otherwise be reduced by a single group after the producers have finished).
+__host__ __device__ inline int reduce_slices_for(int width, int groups) {
+  int s = 1;
+  while (s < groups && (width / (s * 2)) % 8 == 0 && width / (s * 2) >= 64 && s < 256) s *= 2;
+  return s;
+}
+
 }  // namespace comm
 }  // namespace dh

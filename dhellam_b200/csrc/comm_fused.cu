@@ -251,7 +251,7 @@ int dh_reduce_blocks(void* const* part_ptrs, const void* part_mc, const void* re
   p.rows = rows;
   p.in_block0 = in_block0;
   p.blocks = (rows + ROW_BLOCK - 1) / ROW_BLOCK;
-  p.slices = dh::comm::slices_for(p.blocks, N, ctas);
+  p.slices = dh::comm::reduce_slices_for(N, ctas);
   p.target = target;
   rs_reduce_blocks_kernel<<<ctas, threads, 0, stream>>>(p, reinterpret_cast<DeviceStatus*>(dh_status_device_ptr()));
   cudaError_t e = cudaGetLastError();
@@ -277,7 +277,7 @@ int dh_rs_reduce_blocks(void* const* part_ptrs, const void* part_mc, const void*
   ReduceJob p;
   const int blocks = (M / (world > 0 ? world : 1) + ROW_BLOCK - 1) / ROW_BLOCK;
   int rc = dh_fill_reduce_job(p, "dh_rs_reduce_blocks", part_ptrs, part_mc, ready, out, M, N, rank, world, target,
-                              dh::comm::slices_for(blocks, N, ctas));
+                              dh::comm::reduce_slices_for(N, ctas));
   if (rc) return rc;
   rs_reduce_blocks_kernel<<<ctas, threads, 0, stream>>>(p, reinterpret_cast<DeviceStatus*>(dh_status_device_ptr()));
   cudaError_t e = cudaGetLastError();

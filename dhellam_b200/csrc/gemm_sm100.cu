@@ -474,10 +474,12 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                  const __grid_constant__ CUtensorMap tmap_d, const PairParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  // layout: A ring | B ring | epilogue staging | control, sized for the ring depth in use (p.stages), so that a
+  // shallower ring really leaves shared memory to small kernels that share the SM
   uint8_t* sA = smem;
-  uint8_t* sB = smem + RING * A2_STAGE_BYTES;
-  uint8_t* sEpi = smem + RING * STAGE2_BYTES;
-  Control2* ctl = reinterpret_cast<Control2*>(smem + RING * STAGE2_BYTES + EPI_BYTES);
+  uint8_t* sB = smem + p.stages * A2_STAGE_BYTES;
+  uint8_t* sEpi = smem + p.stages * STAGE2_BYTES;
+  Control2* ctl = reinterpret_cast<Control2*>(smem + p.stages * STAGE2_BYTES + EPI_BYTES);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -621,6 +623,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     int acc = 0;
     uint32_t acc_ph = 0;
     uint32_t cc = 0;                                // running chunk count -> staging tile parity
+    int pending_blk = -1;                           // row block whose completion signal is still owed (lane 0)
     bool ok = true;
     for (int it = pair_id; it < num_items && ok; it += num_pairs) {
       const Item im = item_coords(it, p, num_tiles, num_kb);
@@ -630,10 +633,12 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       tc_fence_after();
       const int row0 = tm * TILE_M + (int)rank * BM + quarter * 32;     // first of this warp's 32 output rows
       const uint32_t taddr = tmem_base + acc * ACC_COLS + ((uint32_t)(quarter * 32) << 16);
+      int chunks_done = 0;
 #pragma unroll 1
       for (int c = 0; c < NCH; ++c) {
         const int col0 = tn * BN + c * CH_COLS;
         if (col0 >= p.N) break;                     // uniform across the warp
+        ++chunks_done;
         uint32_t r[OUT_F32 ? 32 : 64];
         tmem_ld32(taddr + c * CH_COLS, *reinterpret_cast<uint32_t(*)[32]>(&r[0]));
         if (!OUT_F32) tmem_ld32(taddr + c * CH_COLS + 32, *reinterpret_cast<uint32_t(*)[32]>(&r[32]));
@@ -673,19 +678,31 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(&ctl->acc_empty[acc], 0);
       if (p.sig[0] != nullptr && row0 < p.M) {
-        // this warp's 32 rows of the tile are in memory -> tell the rank that owns the row block
+        // Tell the rank that owns the row block that this warp's 32 rows of a tile are in memory.  The signal of
+        // tile i is sent after the stores of tile i + 1 have been issued: waiting for "all but the newest NCH
+        // groups" then completes tile i without stalling on the stores just issued.
         if (lane == 0) {
-          tma_store_wait<0>();
-          fence_proxy_async_all();
-          asm volatile("fence.acq_rel.sys;" ::: "memory");
-          const int blk = row0 / BM;
-          red_add_release_sys(p.sig[blk / p.sig_bpr] + (blk % p.sig_bpr), 1u);
+          if (pending_blk >= 0) {
+            if (chunks_done == NCH) tma_store_wait<NCH>();
+            else tma_store_wait<0>();
+            fence_proxy_async_all();
+            asm volatile("fence.acq_rel.sys;" ::: "memory");
+            red_add_release_sys(p.sig[pending_blk / p.sig_bpr] + (pending_blk % p.sig_bpr), 1u);
+          }
+          pending_blk = row0 / BM;
         }
         __syncwarp();
       }
       if (++acc == NUM_ACC) { acc = 0; acc_ph ^= 1; }
     }
-    if (lane == 0) tma_store_wait<0>();             // shared memory must outlive the bulk stores
+    if (lane == 0) {
+      tma_store_wait<0>();                          // shared memory must outlive the bulk stores
+      if (pending_blk >= 0) {
+        fence_proxy_async_all();
+        asm volatile("fence.acq_rel.sys;" ::: "memory");
+        red_add_release_sys(p.sig[pending_blk / p.sig_bpr] + (pending_blk % p.sig_bpr), 1u);
+      }
+    }
     __syncwarp();
   }
 
@@ -716,7 +733,7 @@ static int launch_pair(const CUtensorMap* ta, const CUtensorMap* tb, const CUten
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(2 * pairs);
   cfg.blockDim = dim3(COMM ? THREADS + COMM_THREADS : THREADS);
-  cfg.dynamicSmemBytes = SMEM2_BYTES;
+  cfg.dynamicSmemBytes = SMEM2_BYTES - (RING - p.stages) * STAGE2_BYTES;
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -842,7 +859,11 @@ static int gemm_impl(const void* a, int64_t lda, int a_mn_major, const void* b, 
     p.M = M; p.N = N; p.K = K;
     p.tiles_m = (M + TILE_M - 1) / TILE_M;
     p.tiles_n = (N + BN - 1) / BN;
-    p.stages = pair_stages;
+    // A GEMM that other resident kernels wait on (row-block signals) or that waits on them must never be kept off
+    // an SM by those kernels' CTAs: with a static tile assignment a CTA pair that cannot become resident leaves
+    // its tiles undone while the kernels that hold its shared memory spin on exactly those tiles.  One ring stage
+    // less leaves 32 KB per SM, room for every small CTA that can share it.
+    p.stages = hooks && pair_stages == RING ? RING - 1 : pair_stages;
     p.group_m = pair_group;
     p.status = status;
     const int num_tiles = p.tiles_m * p.tiles_n;
@@ -1001,7 +1022,7 @@ extern "C" int dh_gemm_rs_bf16(const void* a, int64_t lda, const void* b, int64_
   const int blocks = M / world / 128;
   dh::comm::ReduceJob job;
   int rc = dh_fill_reduce_job(job, "dh_gemm_rs_bf16", part_ptrs, part_mc, ready_ptrs[rank], out, M, N, rank, world, target,
-                              dh::comm::slices_for(blocks, N, dh_sm_count()));
+                              dh::comm::reduce_slices_for(N, dh_sm_count()));
   if (rc) return rc;
   dh::gemm::SyncArgs sy;
   sy.sig_ptrs = ready_ptrs;

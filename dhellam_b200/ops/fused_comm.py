@@ -132,7 +132,7 @@ class FusedTP:
         # (not with two compute streams: a GEMM that spins on arrival counters holds every SM's shared memory, so the
         #  other strand's GEMM, whose output some peer's push may be waiting for, could never start)
         self.ag_inkernel = os.environ.get("DHELLAM_AG_INKERNEL", "1") != "0" and getattr(train, "compute_streams", 1) < 2
-        self.rs_blocks = os.environ.get("DHELLAM_RS_BLOCKS", "1") != "0"
+        self.rs_blocks = os.environ.get("DHELLAM_RS_BLOCKS", "1") != "0" and getattr(train, "compute_streams", 1) < 2
         self.total_sig = {t: [0, 0] for t in RS_TAGS}      # block-counter value reached so far, per (tag, slot)
         self._sig_arrays = {}
         # The strategy search replays single ops out of their layer context (a consumer without its push, a
