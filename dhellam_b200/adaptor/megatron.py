@@ -93,6 +93,7 @@ def _add_megatron_args(parser):
     t.add_argument("--hysteresis", type=int, default=2)
     t.add_argument("--min-loss-scale", type=float, default=1.0)
     t.add_argument("--label-smoothing-factor", type=float, default=0.0)
+    t.add_argument("--deterministic-mode", action="store_true", help="fixed-order reductions: two runs give bitwise equal results")
     t.add_argument("--use-distributed-optimizer", action="store_true")
     t.add_argument("--seed", type=int, default=1234)
     t.add_argument("--no-fused-comm", action="store_true", help="library collectives instead of in-kernel ones")
@@ -164,7 +165,7 @@ def configs_from_args(args, world_size: int):
         loss_scale=args.loss_scale if args.loss_scale is not None else 1.0,
         dynamic_loss_scale=bool(args.fp16) and args.loss_scale is None, initial_loss_scale=args.initial_loss_scale,
         loss_scale_window=args.loss_scale_window, hysteresis=args.hysteresis, min_loss_scale=args.min_loss_scale,
-        label_smoothing=args.label_smoothing_factor)
+        label_smoothing=args.label_smoothing_factor, deterministic=args.deterministic_mode)
     return cfg, pcfg, train
 
 

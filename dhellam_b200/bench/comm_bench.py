@@ -37,6 +37,7 @@ def _time(fn, iters, warmup, device, group):
         dist.barrier(group=group)
         torch.cuda.synchronize()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda._sleep(1_000_000)          # the host enqueues fn() behind a short spin kernel: device time only
         e0.record()
         fn()
         e1.record()

@@ -38,6 +38,10 @@ def time_ms(fn, iters, warmup, flush):
             flush.fill_(1.0)
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         torch.cuda.synchronize()
+        # a short spin kernel in front of the first event: the host enqueues fn()'s launches while it runs, so the
+        # events bracket device time only and not the host's launch path (which would otherwise sit inside the
+        # bracket for every kernel shorter than its own launch sequence)
+        torch.cuda._sleep(1_000_000)
         e0.record()
         fn()
         e1.record()

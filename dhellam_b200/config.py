@@ -143,6 +143,7 @@ class TrainConfig:
     # (dhellam/core/dstb.py:1043-1059) and its device-wide synchronisation after every block (:1266)
     reference_schedule: bool = False
     sync_per_block: bool = False
+    deterministic: bool = False          # Megatron's --deterministic-mode: fixed-order reductions, bitwise repeatable runs
 
     def num_microbatches(self, dp: int) -> int:
         assert self.global_batch_size % (self.micro_batch_size * dp) == 0, "global batch must divide by micro-batch x dp"

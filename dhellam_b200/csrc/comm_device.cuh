@@ -193,11 +193,14 @@ __device__ __forceinline__ bool reduce_rows(const ReduceJob& p, int group, int n
   return true;
 }
 
-// Column slices per row block such that (row blocks x slices) work items keep about `groups` thread groups
-// busy.  A pure function of its arguments, so every rank and the host agree on the counter increments.
+// Column slices per row block of a push: (row blocks x slices) work items over `groups` thread groups, taken
+// block by block, so that at most about four row blocks are in flight at a time and the first blocks of the
+// shard arrive early (a consumer that waits per row block starts long before the last block has been sent;
+// one whole block per group would deliver them all at once, at the end).  A pure function of its arguments,
+// so every rank and the host agree on the counter increments.
 __host__ __device__ inline int slices_for(int blocks, int width, int groups) {
   int s = 1;
-  while (blocks * s < groups && (width / (s * 2)) % 8 == 0 && width / (s * 2) >= 64 && s < 64) s *= 2;
+  while ((blocks * s < groups || s * 4 < groups) && (width / (s * 2)) % 8 == 0 && width / (s * 2) >= 64 && s < 64) s *= 2;
   return s;
 }
 

@@ -147,7 +147,7 @@ __global__ void __launch_bounds__(NT) norm_bwd_kernel(const __nv_bfloat16* __res
                                                       const __nv_bfloat16* __restrict__ w, const float* __restrict__ mu_in,
                                                       const float* __restrict__ rstd_in, const __nv_bfloat16* __restrict__ res,
                                                       __nv_bfloat16* __restrict__ dx, float* __restrict__ dw, float* __restrict__ db,
-                                                      int rows, int h) {
+                                                      int rows, int h, float* __restrict__ partial) {
   __shared__ float red[64];
   const int nvec = h >> 3;
   float accw[VPT][8], accb[VPT][8];
@@ -208,6 +208,25 @@ __global__ void __launch_bounds__(NT) norm_bwd_kernel(const __nv_bfloat16* __res
       }
     }
   }
+  if (partial != nullptr) {
+    // reproducible form: every CTA stores its partial sums (rows [0, grid) weight, rows [grid, 2 grid) bias);
+    // norm_dw_finish_kernel adds them up in CTA order
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const int c = threadIdx.x + i * NT;
+      if (c < nvec) {
+        float4* pw = reinterpret_cast<float4*>(partial + (size_t)blockIdx.x * h + c * 8);
+        pw[0] = make_float4(accw[i][0], accw[i][1], accw[i][2], accw[i][3]);
+        pw[1] = make_float4(accw[i][4], accw[i][5], accw[i][6], accw[i][7]);
+        if (MODE == 1 && db != nullptr) {
+          float4* pb = reinterpret_cast<float4*>(partial + ((size_t)gridDim.x + blockIdx.x) * h + c * 8);
+          pb[0] = make_float4(accb[i][0], accb[i][1], accb[i][2], accb[i][3]);
+          pb[1] = make_float4(accb[i][4], accb[i][5], accb[i][6], accb[i][7]);
+        }
+      }
+    }
+    return;
+  }
   // gradient buffers are views into one flat buffer: 16-byte alignment is usual, not guaranteed
   const bool vec_ok = ((reinterpret_cast<uintptr_t>(dw) | (MODE == 1 && db != nullptr ? reinterpret_cast<uintptr_t>(db) : 0)) & 15) == 0;
 #pragma unroll
@@ -231,6 +250,20 @@ __global__ void __launch_bounds__(NT) norm_bwd_kernel(const __nv_bfloat16* __res
         }
       }
     }
+  }
+}
+
+// Adds `parts` partial rows of length h, in row order, to the gradient (same result for every run).
+__global__ void __launch_bounds__(NT) norm_dw_finish_kernel(const float* __restrict__ partial, int parts, int h, float* __restrict__ dw,
+                                                            float* __restrict__ db) {
+  const int c = blockIdx.x * NT + threadIdx.x;
+  if (c >= h) return;
+  float a = 0.f, b = 0.f;
+  for (int p = 0; p < parts; ++p) a += partial[(size_t)p * h + c];
+  dw[c] += a;
+  if (db != nullptr) {
+    for (int p = 0; p < parts; ++p) b += partial[((size_t)parts + p) * h + c];
+    db[c] += b;
   }
 }
 
@@ -429,8 +462,34 @@ int dh_rmsnorm_bwd(const void* dy, const void* x, const void* w, const void* rst
   if (rows <= 0) return 0;
   DH_VPT_DISPATCH(h, norm_bwd_kernel, 0, grid_for(rows, 2, sm_budget), (const __nv_bfloat16*)dy, (const __nv_bfloat16*)x,
                   (const __nv_bfloat16*)w, nullptr, (const float*)rstd, (const __nv_bfloat16*)res, (__nv_bfloat16*)dx, (float*)dw, nullptr,
-                  rows, h);
+                  rows, h, nullptr);
   return launch_rc("dh_rmsnorm_bwd");
+}
+// Number of CTAs the norm backward launches = rows of fp32 partial sums (x h, x 2 with a bias) its reproducible form needs.
+int dh_norm_bwd_grid(int rows, int sm_budget) { return grid_for(rows, 2, sm_budget); }
+// Reproducible forms: the weight (and bias) gradient is summed over CTAs in a fixed order through `partial`
+// (fp32 [grid, h], [2 grid, h] for layer norm) instead of order-dependent reductions into memory.
+int dh_rmsnorm_bwd_det(const void* dy, const void* x, const void* w, const void* rstd, const void* res, void* dx, void* dw, void* partial,
+                       int rows, int h, int sm_budget, cudaStream_t s) {
+  DH_REQUIRE(h % 8 == 0 && h <= NT * MAXV * 8, "hidden size must be a multiple of 8 and at most 16384");
+  DH_REQUIRE(partial != nullptr && (reinterpret_cast<uintptr_t>(partial) & 15) == 0, "partial sums need a 16-byte aligned buffer");
+  if (rows <= 0) return 0;
+  const int grid = grid_for(rows, 2, sm_budget);
+  DH_VPT_DISPATCH(h, norm_bwd_kernel, 0, grid, (const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, nullptr,
+                  (const float*)rstd, (const __nv_bfloat16*)res, (__nv_bfloat16*)dx, (float*)dw, nullptr, rows, h, (float*)partial);
+  norm_dw_finish_kernel<<<(h + NT - 1) / NT, NT, 0, s>>>((const float*)partial, grid, h, (float*)dw, nullptr);
+  return launch_rc("dh_rmsnorm_bwd_det");
+}
+int dh_layernorm_bwd_det(const void* dy, const void* x, const void* w, const void* mu, const void* rstd, const void* res, void* dx, void* dw,
+                         void* db, void* partial, int rows, int h, int sm_budget, cudaStream_t s) {
+  DH_REQUIRE(h % 8 == 0 && h <= NT * MAXV * 8, "hidden size must be a multiple of 8 and at most 16384");
+  DH_REQUIRE(partial != nullptr && (reinterpret_cast<uintptr_t>(partial) & 15) == 0, "partial sums need a 16-byte aligned buffer");
+  if (rows <= 0) return 0;
+  const int grid = grid_for(rows, 2, sm_budget);
+  DH_VPT_DISPATCH(h, norm_bwd_kernel, 1, grid, (const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (const float*)mu,
+                  (const float*)rstd, (const __nv_bfloat16*)res, (__nv_bfloat16*)dx, (float*)dw, (float*)db, rows, h, (float*)partial);
+  norm_dw_finish_kernel<<<(h + NT - 1) / NT, NT, 0, s>>>((const float*)partial, grid, h, (float*)dw, (float*)db);
+  return launch_rc("dh_layernorm_bwd_det");
 }
 int dh_layernorm_fwd(const void* x, const void* w, const void* b, void* y, void* mu, void* rstd, int rows, int h, float eps, int sm_budget,
                      cudaStream_t s) {
@@ -446,7 +505,7 @@ int dh_layernorm_bwd(const void* dy, const void* x, const void* w, const void* m
   if (rows <= 0) return 0;
   DH_VPT_DISPATCH(h, norm_bwd_kernel, 1, grid_for(rows, 2, sm_budget), (const __nv_bfloat16*)dy, (const __nv_bfloat16*)x,
                   (const __nv_bfloat16*)w, (const float*)mu, (const float*)rstd, (const __nv_bfloat16*)res, (__nv_bfloat16*)dx, (float*)dw,
-                  (float*)db, rows, h);
+                  (float*)db, rows, h, nullptr);
   return launch_rc("dh_layernorm_bwd");
 }
 int dh_swiglu_fwd(const void* y, void* out, int64_t rows, int f, int sm_budget, cudaStream_t s) {

@@ -85,6 +85,33 @@ __global__ void __launch_bounds__(HT) embedding_bwd_kernel(const __nv_bfloat16* 
   }
 }
 
+// Reproducible form: `order` is a stable sort of the token positions by token id and `sorted_tok` the ids in that
+// order; the CTA that meets the first position of a token adds all of that token's rows in sorted order and
+// writes the row of the gradient once (no two CTAs touch the same row, nothing depends on timing).
+__global__ void __launch_bounds__(HT) embedding_bwd_sorted_kernel(const __nv_bfloat16* __restrict__ dout, const long long* __restrict__ order,
+                                                                  const int* __restrict__ sorted_tok, float* __restrict__ grad, int T, int h,
+                                                                  int Vl, int v0) {
+  const int nvec = h >> 3;
+  for (int i = blockIdx.x; i < T; i += gridDim.x) {
+    const int tk = sorted_tok[i];
+    if (i > 0 && sorted_tok[i - 1] == tk) continue;          // not the first position of this token
+    const int loc = tk - v0;
+    if (loc < 0 || loc >= Vl) continue;
+    float* dst = grad + (size_t)loc * h;
+    for (int c = threadIdx.x; c < nvec; c += HT) {
+      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      for (int j = i; j < T && sorted_tok[j] == tk; ++j) {
+        float v[8];
+        h_unpack8(ld_nc_v4(reinterpret_cast<const uint4*>(dout + (size_t)order[j] * h) + c), v);
+#pragma unroll
+        for (int q = 0; q < 8; ++q) acc[q] += v[q];
+      }
+#pragma unroll
+      for (int q = 0; q < 8; ++q) dst[c * 8 + q] += acc[q];
+    }
+  }
+}
+
 // ============================================================================ cross entropy
 // One CTA per token row; online (max, sum-exp) in a single pass over the vocabulary shard.
 template <bool F32>
@@ -322,6 +349,42 @@ __global__ void __launch_bounds__(HT) sumsq_kernel(const float* __restrict__ x, 
   }
 }
 
+// Reproducible form of the sum of squares: CTA b stores its sum in scratch[b]; the last CTA to finish (a counter
+// behind the partial sums) adds them in index order to *out and resets the counter for the next call.
+__global__ void __launch_bounds__(HT) sumsq_det_kernel(const float* __restrict__ x, float* __restrict__ out, long long n,
+                                                       float* __restrict__ scratch, unsigned int* __restrict__ counter) {
+  __shared__ float red[32];
+  __shared__ unsigned int last;
+  float s = 0.f;
+  const long long n4 = n >> 2;
+  for (long long i = (long long)blockIdx.x * HT + threadIdx.x; i < n4; i += (long long)gridDim.x * HT) {
+    const float4 v = reinterpret_cast<const float4*>(x)[i];
+    s += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+  }
+  for (long long i = (n4 << 2) + (long long)blockIdx.x * HT + threadIdx.x; i < n; i += (long long)gridDim.x * HT) s += x[i] * x[i];
+  s = hwarp_sum(s);
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+  if (l == 0) red[w] = s;
+  __syncthreads();
+  if (w == 0) {
+    float r = l < (HT >> 5) ? red[l] : 0.f;
+    r = hwarp_sum(r);
+    if (l == 0) {
+      scratch[blockIdx.x] = r;
+      __threadfence();
+      last = atomicAdd(counter, 1u) == gridDim.x - 1 ? 1u : 0u;
+    }
+  }
+  __syncthreads();
+  if (last && threadIdx.x == 0) {
+    __threadfence();
+    float tot = 0.f;
+    for (unsigned int b = 0; b < gridDim.x; ++b) tot += reinterpret_cast<volatile float*>(scratch)[b];
+    *out += tot;
+    *counter = 0u;
+  }
+}
+
 }  // namespace dh
 
 using namespace dh;
@@ -347,6 +410,15 @@ int dh_embedding_bwd(const void* dout, const void* tok, void* grad, int T, int h
   if (T <= 0) return 0;
   embedding_bwd_kernel<<<h_grid(T, 8, sm_budget), HT, 0, s>>>((const __nv_bfloat16*)dout, (const int*)tok, (float*)grad, T, h, Vl, v0);
   return h_rc("dh_embedding_bwd");
+}
+// Reproducible embedding gradient.  order: int64 [T], a stable sort of the positions by token id; sorted_tok: int32 [T].
+int dh_embedding_bwd_sorted(const void* dout, const void* order, const void* sorted_tok, void* grad, int T, int h, int Vl, int v0,
+                            int sm_budget, cudaStream_t s) {
+  DH_REQ(h % 8 == 0, "hidden size must be a multiple of 8");
+  if (T <= 0) return 0;
+  embedding_bwd_sorted_kernel<<<h_grid(T, 8, sm_budget), HT, 0, s>>>((const __nv_bfloat16*)dout, (const long long*)order, (const int*)sorted_tok,
+                                                                     (float*)grad, T, h, Vl, v0);
+  return h_rc("dh_embedding_bwd_sorted");
 }
 int dh_ce_stats(const void* logits, const void* labels, void* stats, int T, int Vl, int64_t ld, int v0, int is_f32, int sm_budget,
                 cudaStream_t s) {
@@ -389,6 +461,18 @@ int dh_sum_squares(const void* x, void* out, int64_t n, cudaStream_t s) {
   if (n <= 0) return 0;
   sumsq_kernel<<<h_grid((n / 4 + HT - 1) / HT, 8, 0), HT, 0, s>>>((const float*)x, (float*)out, n);
   return h_rc("dh_sum_squares");
+}
+// Reproducible form.  scratch: fp32 [dh_sum_squares_scratch()] whose LAST element is a counter that must be zero
+// before the first call (the kernel leaves it zero); calls that share a scratch must be ordered on one stream.
+int dh_sum_squares_scratch() { return dh_sm_count() * 8 + 1; }
+int dh_sum_squares_det(const void* x, void* out, int64_t n, void* scratch, cudaStream_t s) {
+  DH_REQ((reinterpret_cast<uintptr_t>(x) & 15) == 0, "input must be 16-byte aligned");
+  DH_REQ(scratch != nullptr, "scratch buffer missing");
+  if (n <= 0) return 0;
+  const int grid = h_grid((n / 4 + HT - 1) / HT, 8, 0);
+  float* sc = (float*)scratch;
+  sumsq_det_kernel<<<grid, HT, 0, s>>>((const float*)x, (float*)out, n, sc, reinterpret_cast<unsigned int*>(sc + dh_sm_count() * 8));
+  return h_rc("dh_sum_squares_det");
 }
 
 }  // extern "C"

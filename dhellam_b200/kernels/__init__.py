@@ -61,6 +61,35 @@ def use_library(t) -> bool:
     return t.is_cuda and _BACKEND == "library"
 
 
+# Reproducible mode: every reduction whose order would depend on timing (norm weight gradients, the embedding
+# gradient, the gradient norm, K-split weight-gradient GEMMs) takes a fixed-order form, so that two runs of
+# the same program on the same GPU give bitwise equal results.  Costs a few small extra launches per layer.
+_DETERMINISTIC = os.environ.get("DHELLAM_DETERMINISTIC", "0") == "1"
+_DET_SCRATCH = {}
+
+
+def set_deterministic(on: bool = True):
+    global _DETERMINISTIC
+    _DETERMINISTIC = bool(on)
+    if available() and _BACKEND == "native":
+        proto("dh_gemm_set_splitk", [c_int], None)(1 if on else -1)
+
+
+def deterministic() -> bool:
+    return _DETERMINISTIC
+
+
+def det_scratch(device, floats: int, zero_tail: bool = False):
+    """A per-device fp32 scratch of at least ``floats`` elements for the fixed-order reductions (grown on demand;
+    the users run on one stream, in order).  ``zero_tail`` scratch starts zeroed and is kept separately."""
+    key = (torch.device(device).index, zero_tail)
+    buf = _DET_SCRATCH.get(key)
+    if buf is None or buf.numel() < floats:
+        buf = (torch.zeros if zero_tail else torch.empty)(floats, dtype=torch.float32, device=device)
+        _DET_SCRATCH[key] = buf
+    return buf
+
+
 def lib_path() -> Path:
     return _LIB_PATH
 

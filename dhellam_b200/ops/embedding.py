@@ -46,6 +46,15 @@ def embedding_bwd(dout, tokens, main_grad, vocab_start: int = 0, sm_budget: int 
         rows = torch.nonzero(own).squeeze(1)
         main_grad.index_add_(0, loc[rows], dout.reshape(T, h)[rows].to(main_grad.dtype))
         return main_grad
+    if K.deterministic():
+        # fixed summation order: positions sorted by token id (stable), one CTA per distinct token
+        flat = tokens.reshape(-1)
+        sorted_tok, order = torch.sort(flat, stable=True)
+        sorted_tok = sorted_tok.to(torch.int32).contiguous()
+        fn = K.proto("dh_embedding_bwd_sorted", [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p])
+        K.check(fn(dout.data_ptr(), order.contiguous().data_ptr(), sorted_tok.data_ptr(), main_grad.data_ptr(), T, h, Vl, vocab_start,
+                   sm_budget, K.stream_ptr(stream)), "dh_embedding_bwd_sorted")
+        return main_grad
     fn = K.proto("dh_embedding_bwd", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p])
     K.check(fn(dout.data_ptr(), tokens.data_ptr(), main_grad.data_ptr(), T, h, Vl, vocab_start, sm_budget,
                K.stream_ptr(stream)), "dh_embedding_bwd")

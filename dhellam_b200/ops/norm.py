@@ -90,6 +90,14 @@ def rmsnorm_bwd(dy, x, weight, rstd, weight_main_grad=None, residual_grad=None, 
     if weight_main_grad is None:
         weight_main_grad = torch.zeros(h, dtype=torch.float32, device=x.device)
         ret = weight_main_grad
+    if K.deterministic():
+        grid = K.proto("dh_norm_bwd_grid", [c_int, c_int])(rows, sm_budget)
+        partial = K.det_scratch(x.device, grid * h)
+        fn = K.proto("dh_rmsnorm_bwd_det", [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                                            c_int, c_void_p])
+        K.check(fn(dy.data_ptr(), x.data_ptr(), weight.data_ptr(), rstd.data_ptr(), K.ptr(residual_grad), dx.data_ptr(),
+                   weight_main_grad.data_ptr(), partial.data_ptr(), rows, h, sm_budget, K.stream_ptr(stream)), "dh_rmsnorm_bwd_det")
+        return dx, ret
     fn = K.proto("dh_rmsnorm_bwd", [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
                                     c_int, c_void_p])
     K.check(fn(dy.data_ptr(), x.data_ptr(), weight.data_ptr(), rstd.data_ptr(), K.ptr(residual_grad), dx.data_ptr(),
@@ -134,6 +142,15 @@ def layernorm_bwd(dy, x, weight, mu, rstd, weight_main_grad=None, bias_main_grad
         weight_main_grad = rw = torch.zeros(h, dtype=torch.float32, device=x.device)
     if bias_main_grad is None:
         bias_main_grad = rb = torch.zeros(h, dtype=torch.float32, device=x.device)
+    if K.deterministic():
+        grid = K.proto("dh_norm_bwd_grid", [c_int, c_int])(rows, sm_budget)
+        partial = K.det_scratch(x.device, 2 * grid * h)
+        fn = K.proto("dh_layernorm_bwd_det", [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                              c_void_p, c_void_p, c_int, c_int, c_int, c_void_p])
+        K.check(fn(dy.data_ptr(), x.data_ptr(), weight.data_ptr(), mu.data_ptr(), rstd.data_ptr(), K.ptr(residual_grad),
+                   dx.data_ptr(), weight_main_grad.data_ptr(), bias_main_grad.data_ptr(), partial.data_ptr(), rows, h, sm_budget,
+                   K.stream_ptr(stream)), "dh_layernorm_bwd_det")
+        return dx, rw, rb
     fn = K.proto("dh_layernorm_bwd", [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                       c_void_p, c_int, c_int, c_int, c_void_p])
     K.check(fn(dy.data_ptr(), x.data_ptr(), weight.data_ptr(), mu.data_ptr(), rstd.data_ptr(), K.ptr(residual_grad),

@@ -54,6 +54,12 @@ def sum_squares(t, stream=None):
     if not t.is_cuda:
         return (t.float() ** 2).sum().reshape(1)
     out = torch.zeros(1, dtype=torch.float32, device=t.device)
+    if K.deterministic():
+        n = K.proto("dh_sum_squares_scratch", [])()
+        scratch = K.det_scratch(t.device, n, zero_tail=True)
+        fn = K.proto("dh_sum_squares_det", [c_void_p, c_void_p, c_int64, c_void_p, c_void_p])
+        K.check(fn(t.data_ptr(), out.data_ptr(), t.numel(), scratch.data_ptr(), K.stream_ptr(stream)), "dh_sum_squares_det")
+        return out
     fn = K.proto("dh_sum_squares", [c_void_p, c_void_p, c_int64, c_void_p])
     K.check(fn(t.data_ptr(), out.data_ptr(), t.numel(), K.stream_ptr(stream)), "dh_sum_squares")
     return out

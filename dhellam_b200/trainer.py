@@ -61,6 +61,8 @@ class Trainer:
             # so that path keeps the single-CTA tiles.
             from .ops.gemm import set_gemm_mode
             set_gemm_mode(1)
+        if train.deterministic:
+            _K.set_deterministic(True)
         self.env = Env(cfg, self.ps, train, self.device, self.model.dtype, fused=fused)
         if train.fused_comm and self.device.type == "cuda" and self.ps.cp > 1 and _K.backend() == "native" \
                 and os.environ.get("DHELLAM_CP_RING", "0") != "1":

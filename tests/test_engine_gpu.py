@@ -116,3 +116,34 @@ def test_library_backend_composition_matches_native_and_frees_memory():
         K.set_backend("native")
     for a, b in zip(out["native"], out["library"]):
         assert abs(a - b) / abs(a) < 2e-2, out
+
+
+@pytest.mark.parametrize("family", ["llama", "gpt"])
+def test_deterministic_mode_gives_bitwise_equal_runs(family):
+    """Two trainers with the same seed, weights and data, three optimizer steps each (gradient clipping on,
+    repeated tokens in the batch): every loss and every parameter is bitwise equal."""
+    from dhellam_b200 import kernels as K
+    from dhellam_b200.config import ParallelConfig, TrainConfig
+    from dhellam_b200.data import synthetic_step_batches
+    from dhellam_b200.parallel import state as PS
+    from dhellam_b200.trainer import Trainer
+    cfg = _cfgs(family)
+    runs = []
+    try:
+        for _ in range(2):
+            PS.set_state(None)
+            train = TrainConfig(micro_batch_size=2, global_batch_size=4, dtype="bf16", lr=1e-3, clip_grad=1.0, seed=77, deterministic=True)
+            tr = Trainer(cfg, ParallelConfig(), train, device="cuda")
+            assert K.deterministic()
+            losses = []
+            for step in range(3):
+                mbs = synthetic_step_batches(cfg, train, tr.ps, step, "cuda")
+                losses.append(float(tr.train_step(mbs)))
+            torch.cuda.synchronize()
+            runs.append((losses, {n: p.detach().clone() for n, p in tr.model.named_parameters()}))
+            tr.close()
+    finally:
+        K.set_deterministic(False)
+    assert runs[0][0] == runs[1][0], (runs[0][0], runs[1][0])
+    for n, p in runs[0][1].items():
+        assert torch.equal(p, runs[1][1][n]), n

@@ -86,3 +86,34 @@ def test_noalloc_attention_backward_rejects_oversized_problem():
     rc = fn(*([t.data_ptr()] * 9), arr, B, Hq, Hk, Sq, Sq, d, 1, 0.088, torch.cuda.current_stream().cuda_stream)
     assert rc != 0
     assert "scratch" in lib.dh_last_error_string().decode()
+
+
+def test_noalloc_attention_backward_against_fp32_reference_at_1024():
+    """The same entry point against a plain fp32 attention backward (autograd over an explicit softmax),
+    1024 positions, causal, four query heads per KV head."""
+    from dhellam_b200 import kernels as K
+    from dhellam_b200.ops.attention import attn_fwd
+    lib = K.lib()
+    torch.manual_seed(11)
+    Sq, B, Hq, Hk, d = 1024, 2, 8, 2, 128
+    scale = 1.0 / math.sqrt(d)
+    q = torch.randn(Sq, B, Hq, d, device="cuda").to(torch.bfloat16)
+    k = torch.randn(Sq, B, Hk, d, device="cuda").to(torch.bfloat16)
+    v = torch.randn(Sq, B, Hk, d, device="cuda").to(torch.bfloat16)
+    dout = torch.randn(Sq, B, Hq, d, device="cuda").to(torch.bfloat16)
+    out, lse = attn_fwd(q, k, v, True, scale)
+    rc, dq, dk, dv = _call_noalloc(lib, dout, q, k, v, out, lse, True, scale)
+    assert rc == 0, lib.dh_last_error_string().decode()
+    qf, kf, vf = (t.float().requires_grad_() for t in (q, k, v))
+    g = Hq // Hk
+    kk = kf.repeat_interleave(g, dim=2)
+    vv = vf.repeat_interleave(g, dim=2)
+    s = torch.einsum("sbhd,tbhd->bhst", qf, kk) * scale
+    mask = torch.ones(Sq, Sq, device="cuda", dtype=torch.bool).tril()
+    p = torch.softmax(s.masked_fill(~mask, float("-inf")), dim=-1)
+    o = torch.einsum("bhst,tbhd->sbhd", p, vv)
+    o.backward(dout.float())
+    assert _rel(out, o.detach()) < 1e-2
+    assert _rel(dq, qf.grad) < 1.5e-2
+    assert _rel(dk, kf.grad) < 1.5e-2
+    assert _rel(dv, vf.grad) < 1.5e-2
