@@ -129,6 +129,7 @@ AB_ARMS = {
     "nccl": ({}, True),
     "spread": ({"DHELLAM_COMM_SPREAD": "1"}, False),                      # one small communication CTA per SM
     "legacy-split": ({"DHELLAM_RS_BLOCKS": "0", "DHELLAM_AG_INKERNEL": "0"}, False),   # whole-buffer waits, no tile-granular overlap
+    "ctas32": ({"DHELLAM_PUSH_CTAS": "32", "DHELLAM_RS_CTAS": "32"}, False),   # twice the communication CTAs of the 8-GPU default
     "whole-rs": ({"DHELLAM_RS_BLOCKS": "0"}, False),                      # tile-granular all-gather side only
     "whole-ag": ({"DHELLAM_AG_INKERNEL": "0"}, False),                    # tile-granular reduce-scatter side only
 }

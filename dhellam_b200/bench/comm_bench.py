@@ -54,6 +54,8 @@ def main(argv=None):
     ap.add_argument("--width", type=int, default=8192)
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--emulate-tp8", action="store_true", help="GEMM shapes of one rank of an 8-way split (short K, narrow N) whatever "
+                    "the number of ranks: shows the cost of the row-block signals where the main loop is short")
     a = ap.parse_args(argv)
     from ..config import ModelConfig, ParallelConfig, TrainConfig
     from ..ops import comm as C
@@ -107,8 +109,10 @@ def main(argv=None):
     full = torch.randn(rows, h, device=dev).to(torch.bfloat16)
     ag_bytes = (world - 1) / world * rows * h * 2            # bytes one GPU receives (= sends through the switch multicast)
     n_c, n_l = 1280 * 8 // world if world <= 8 else 1280, h  # column-parallel output width per rank (QKV), row-parallel output width
+    if a.emulate_tp8:
+        n_c = 1280
     w_c = (torch.randn(n_c, h, device=dev) * 0.02).to(torch.bfloat16)
-    k_l = 1024 * 8 // world
+    k_l = 1024 if a.emulate_tp8 else 1024 * 8 // world
     a_l = torch.randn(rows, k_l, device=dev).to(torch.bfloat16)
     w_l = (torch.randn(h, k_l, device=dev) * 0.02).to(torch.bfloat16)
     fl_c, fl_l = 2.0 * rows * n_c * h, 2.0 * rows * h * k_l

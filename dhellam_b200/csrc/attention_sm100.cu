@@ -57,6 +57,7 @@ struct Geometry {
   float scale;
   long long o_s, o_b, o_h;        // output strides (elements)
   DeviceStatus* status;
+  int x0, p0, ny;                 // SM budget: this launch covers tile columns from x0 and (head, batch) pairs from p0; ny = heads
 };
 
 // K-major operand descriptor for step kk (16 elements of the contraction) of a tile stored
@@ -98,8 +99,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int nqb = (g.Sq + BQ - 1) / BQ;
-  const int qb = nqb - 1 - (int)blockIdx.x;       // heaviest (latest) query blocks first
-  const int hq = blockIdx.y, b = blockIdx.z;
+  const int qb = nqb - 1 - (g.x0 + (int)blockIdx.x);       // heaviest (latest) query blocks first
+  const int pyz = g.p0 + (int)blockIdx.y + (int)blockIdx.z * (int)gridDim.y;
+  const int hq = pyz % g.ny, b = pyz / g.ny;
   const int hk = hq / (g.Hq / g.Hk);
   const int off = g.Sk - g.Sq;                    // key j visible to query i iff j <= i + off
   int nblk = (g.Sk + BKV - 1) / BKV;
@@ -362,6 +364,7 @@ struct BwdGeometry {
   int hs;
   float* part;
   DeviceStatus* status;
+  int x0, p0, ny;                 // as in Geometry; ny = Hk * hs
 };
 
 __global__ void __launch_bounds__(BWD_THREADS, 1)
@@ -379,7 +382,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ 
   BwdCtl* ctl = reinterpret_cast<BwdCtl*>(smem + 6 * TILE_BYTES);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int kb = blockIdx.x, hk = blockIdx.y / g.hs, hpart = blockIdx.y % g.hs, b = blockIdx.z;
+  const int pyz = g.p0 + (int)blockIdx.y + (int)blockIdx.z * (int)gridDim.y;
+  const int by = pyz % g.ny;
+  const int kb = g.x0 + (int)blockIdx.x, hk = by / g.hs, hpart = by % g.hs, b = pyz / g.ny;
   const int group = g.Hq / g.Hk;
   const int gpp = group / g.hs;                 // query heads handled by this CTA
   const int hq0 = hk * group + hpart * gpp;
@@ -627,7 +632,9 @@ attn_bwd_t_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant_
   BwdTCtl* ctl = reinterpret_cast<BwdTCtl*>(sDS + 2 * PT_TILE);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int kb = blockIdx.x, hk = blockIdx.y / g.hs, hpart = blockIdx.y % g.hs, b = blockIdx.z;
+  const int pyz = g.p0 + (int)blockIdx.y + (int)blockIdx.z * (int)gridDim.y;
+  const int by = pyz % g.ny;
+  const int kb = g.x0 + (int)blockIdx.x, hk = by / g.hs, hpart = by % g.hs, b = pyz / g.ny;
   const int group = g.Hq / g.Hk;
   const int gpp = group / g.hs;
   const int hq0 = hk * group + hpart * gpp;
@@ -908,6 +915,7 @@ struct DqGeometry {
   float scale;
   long long dq_s, dq_b, dq_h;
   DeviceStatus* status;
+  int x0, p0, ny;                 // as in Geometry; ny = Hq
 };
 
 __global__ void __launch_bounds__(BWD_THREADS, 1)
@@ -925,8 +933,9 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int nqb = (g.Sq + BQ - 1) / BQ;
-  const int qb = nqb - 1 - (int)blockIdx.x;
-  const int hq = blockIdx.y, b = blockIdx.z;
+  const int qb = nqb - 1 - (g.x0 + (int)blockIdx.x);
+  const int pyz = g.p0 + (int)blockIdx.y + (int)blockIdx.z * (int)gridDim.y;
+  const int hq = pyz % g.ny, b = pyz / g.ny;
   const int hk = hq / (g.Hq / g.Hk);
   const int off = g.Sk - g.Sq;
   int nblk = (g.Sk + BKV - 1) / BKV;
@@ -1089,6 +1098,27 @@ using namespace dh::attn;
 // dK/dV kernel choice of dh_attn_bwd: -1 = read DHELLAM_ATTN_BWD_T on first use, 0 = attn_bwd_kernel, 1 = attn_bwd_t_kernel
 static int g_bwd_mode = -1;
 
+// SM budget for kernels whose grid is one CTA per tile (one CTA per SM by shared memory): the (X, Y, Z) grid is cut
+// into launches of at most `budget` CTAs, which the stream runs one after the other, so at most `budget` SMs are in
+// use at any time.  launch(grid, x0, p0) starts tile columns x0.. and flattened (y, z) pairs p0..
+template <class F>
+static void launch_in_waves(int X, int Y, int Z, int sm_budget, F&& launch) {
+  const int sms = dh_sm_count();
+  const int budget = (sm_budget <= 0 || sm_budget >= sms) ? 0 : sm_budget;
+  const long long pairs = (long long)Y * Z;
+  if (budget == 0 || (long long)X * pairs <= budget) {
+    launch(dim3(X, Y, Z), 0, 0);
+    return;
+  }
+  if (X >= budget) {
+    for (long long p = 0; p < pairs; ++p)
+      for (int x0 = 0; x0 < X; x0 += budget) launch(dim3(X - x0 < budget ? X - x0 : budget, 1, 1), x0, (int)p);
+  } else {
+    const int np = budget / X;
+    for (long long p0 = 0; p0 < pairs; p0 += np) launch(dim3(X, (unsigned)(pairs - p0 < np ? pairs - p0 : np), 1), 0, (int)p0);
+  }
+}
+
 extern "C" {
 
 void dh_attn_set_bwd_mode(int mode) { g_bwd_mode = mode; }
@@ -1096,7 +1126,6 @@ void dh_attn_set_bwd_mode(int mode) { g_bwd_mode = mode; }
 int dh_attn_fwd(const void* q, const void* k, const void* v, void* out, void* lse, int64_t q_s, int64_t q_b, int64_t q_h, int64_t k_s,
                 int64_t k_b, int64_t k_h, int64_t v_s, int64_t v_b, int64_t v_h, int B, int Hq, int Hk, int Sq, int Sk, int d, int causal,
                 float scale, int sm_budget, cudaStream_t stream) {
-  (void)sm_budget;
   if (d != D) { set_last_error("dh_attn_fwd: head size %d is not supported (128 only)", d); return (int)cudaErrorInvalidValue; }
   if (Hq % Hk != 0) { set_last_error("dh_attn_fwd: query heads must be a multiple of KV heads"); return (int)cudaErrorInvalidValue; }
   if (B <= 0 || Sq <= 0 || Sk <= 0) return 0;
@@ -1115,8 +1144,11 @@ int dh_attn_fwd(const void* q, const void* k, const void* v, void* out, void* ls
   g.B = B; g.Hq = Hq; g.Hk = Hk; g.Sq = Sq; g.Sk = Sk; g.causal = causal; g.scale = scale;
   g.o_h = D; g.o_b = (long long)Hq * D; g.o_s = (long long)B * Hq * D;
   g.status = reinterpret_cast<DeviceStatus*>(dh_status_device_ptr());
-  dim3 grid((Sq + BQ - 1) / BQ, Hq, B);
-  attn_fwd_kernel<<<grid, FWD_THREADS, FWD_SMEM, stream>>>(*tq, *tk, *tv, (__nv_bfloat16*)out, (float*)lse, g);
+  g.ny = Hq;
+  launch_in_waves((Sq + BQ - 1) / BQ, Hq, B, sm_budget, [&](dim3 grid, int x0, int p0) {
+    g.x0 = x0; g.p0 = p0;
+    attn_fwd_kernel<<<grid, FWD_THREADS, FWD_SMEM, stream>>>(*tq, *tk, *tv, (__nv_bfloat16*)out, (float*)lse, g);
+  });
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) set_last_error("dh_attn_fwd launch failed: %s", cudaGetErrorString(e));
   return (int)e;
@@ -1153,7 +1185,6 @@ int64_t dh_attn_bwd_scratch_bytes(int B, int Hq, int Hk, int Sq, int Sk) {
 int dh_attn_bwd(const void* dout, const void* q, const void* k, const void* v, const void* out, const void* lse, void* dq, void* dk,
                 void* dv, void* scratch, const int64_t* strides /* 8 tensors x (s,b,h): do,q,k,v,o,dq,dk,dv */, int B, int Hq, int Hk,
                 int Sq, int Sk, int d, int causal, float scale, int sm_budget, cudaStream_t stream) {
-  (void)sm_budget;
   if (d != D) { set_last_error("dh_attn_bwd: head size %d is not supported (128 only)", d); return (int)cudaErrorInvalidValue; }
   if (Hq % Hk != 0) { set_last_error("dh_attn_bwd: query heads must be a multiple of KV heads"); return (int)cudaErrorInvalidValue; }
   if (B <= 0 || Sq <= 0 || Sk <= 0) return 0;
@@ -1188,6 +1219,7 @@ int dh_attn_bwd(const void* dout, const void* q, const void* k, const void* v, c
   g.status = st;
   g.hs = bwd_head_split(B, Hq, Hk, Sk);
   g.part = g.hs > 1 ? reinterpret_cast<float*>(reinterpret_cast<char*>(scratch) + ((int64_t)rows * 4 + 255) / 256 * 256) : nullptr;
+  g.x0 = 0; g.p0 = 0; g.ny = Hk * g.hs;
   // DHELLAM_ATTN_BWD_T=1 (or dh_attn_set_bwd_mode(1)) selects the pipelined (transposed-score) form of the dK/dV kernel
   if (g_bwd_mode < 0) {
     const char* ev = getenv("DHELLAM_ATTN_BWD_T");
@@ -1204,12 +1236,17 @@ int dh_attn_bwd(const void* dout, const void* q, const void* k, const void* v, c
       if (e2 != cudaSuccess) { set_last_error("dh_attn_bwd: shared memory opt-in failed: %s", cudaGetErrorString(e2)); return (int)e2; }
       configured_t = true;
     }
-    attn_bwd_t_kernel<<<dim3((Sk + BKV - 1) / BKV, Hk * g.hs, B), BWD_THREADS, BWDT_SMEM, stream>>>(*tq64, *tk, *tv, *tdo64, (const float*)lse,
-                                                                                                  delta, (__nv_bfloat16*)dk,
-                                                                                                  (__nv_bfloat16*)dv, g);
+    launch_in_waves((Sk + BKV - 1) / BKV, Hk * g.hs, B, sm_budget, [&](dim3 grid, int x0, int p0) {
+      g.x0 = x0; g.p0 = p0;
+      attn_bwd_t_kernel<<<grid, BWD_THREADS, BWDT_SMEM, stream>>>(*tq64, *tk, *tv, *tdo64, (const float*)lse, delta, (__nv_bfloat16*)dk,
+                                                                  (__nv_bfloat16*)dv, g);
+    });
   } else {
-    attn_bwd_kernel<<<dim3((Sk + BKV - 1) / BKV, Hk * g.hs, B), BWD_THREADS, BWD_SMEM, stream>>>(*tq, *tk, *tv, *tdo, (const float*)lse, delta,
-                                                                                               (__nv_bfloat16*)dk, (__nv_bfloat16*)dv, g);
+    launch_in_waves((Sk + BKV - 1) / BKV, Hk * g.hs, B, sm_budget, [&](dim3 grid, int x0, int p0) {
+      g.x0 = x0; g.p0 = p0;
+      attn_bwd_kernel<<<grid, BWD_THREADS, BWD_SMEM, stream>>>(*tq, *tk, *tv, *tdo, (const float*)lse, delta, (__nv_bfloat16*)dk,
+                                                               (__nv_bfloat16*)dv, g);
+    });
   }
   if (g.hs > 1) {
     const long long n = 2LL * Sk * B * Hk * (D / 8);
@@ -1220,8 +1257,11 @@ int dh_attn_bwd(const void* dout, const void* q, const void* k, const void* v, c
   gq.B = B; gq.Hq = Hq; gq.Hk = Hk; gq.Sq = Sq; gq.Sk = Sk; gq.causal = causal; gq.scale = scale;
   gq.dq_s = sdq[0]; gq.dq_b = sdq[1]; gq.dq_h = sdq[2];
   gq.status = st;
-  attn_bwd_dq_kernel<<<dim3((Sq + BQ - 1) / BQ, Hq, B), BWD_THREADS, DQ_SMEM, stream>>>(*tq, *tk, *tv, *tdo, (const float*)lse, delta,
-                                                                                      (__nv_bfloat16*)dq, gq);
+  gq.ny = Hq;
+  launch_in_waves((Sq + BQ - 1) / BQ, Hq, B, sm_budget, [&](dim3 grid, int x0, int p0) {
+    gq.x0 = x0; gq.p0 = p0;
+    attn_bwd_dq_kernel<<<grid, BWD_THREADS, DQ_SMEM, stream>>>(*tq, *tk, *tv, *tdo, (const float*)lse, delta, (__nv_bfloat16*)dq, gq);
+  });
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) set_last_error("dh_attn_bwd launch failed: %s", cudaGetErrorString(e));
   return (int)e;
@@ -1302,12 +1342,14 @@ extern "C" int dh_attn_bwd_noalloc(const void* dout, const void* q, const void* 
   g.status = nullptr;
   g.hs = 1;              // the built-in scratch holds delta only: no head split here
   g.part = nullptr;
+  g.x0 = 0; g.p0 = 0; g.ny = Hk;
   attn_bwd_kernel<<<dim3((Sk + BKV - 1) / BKV, Hk, B), BWD_THREADS, BWD_SMEM, stream>>>(tq, tk, tv, tdo, (const float*)lse, delta,
                                                                                       (__nv_bfloat16*)dk, (__nv_bfloat16*)dv, g);
   DqGeometry gq;
   gq.B = B; gq.Hq = Hq; gq.Hk = Hk; gq.Sq = Sq; gq.Sk = Sk; gq.causal = causal; gq.scale = scale;
   gq.dq_s = sdq[0]; gq.dq_b = sdq[1]; gq.dq_h = sdq[2];
   gq.status = nullptr;
+  gq.x0 = 0; gq.p0 = 0; gq.ny = Hq;
   attn_bwd_dq_kernel<<<dim3((Sq + BQ - 1) / BQ, Hq, B), BWD_THREADS, DQ_SMEM, stream>>>(tq, tk, tv, tdo, (const float*)lse, delta,
                                                                                       (__nv_bfloat16*)dq, gq);
   e = cudaGetLastError();

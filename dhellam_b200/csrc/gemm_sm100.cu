@@ -348,7 +348,9 @@ struct __align__(8) Control2 {
   uint32_t tmem_base;
   int abort_flag;
   int comm_flag;
+  uint32_t epi_done[4];            // tiles whose stores are complete, per epilogue warp (read by the signal warp)
 };
+constexpr int SIGNAL_THREADS = 32;                 // one more warp when the GEMM signals finished row blocks
 constexpr int COMM_THREADS = 64;                   // two communication warps per CTA in the COMM form of the kernel
 constexpr int SMEM2_BYTES = RING * STAGE2_BYTES + EPI_BYTES + 1024 + 256;
 
@@ -365,6 +367,7 @@ struct PairParams {
   int sig_bpr;                         // 128-row blocks per owner
   int perm_mode, perm_world, perm_rank;
   long long wait_budget;               // cycles for the barriers inside the CTA
+  unsigned start_id;                   // != 0: announce "every CTA of this launch is resident" (g_start_flag = start_id)
   DeviceStatus* status;
   // grouped (ragged) form for mixture-of-experts layers: `groups` experts share one launch.
   //   group_mode 1  rows grouped: A and D rows are expert-major with region starts group_offs[e] (multiples of 256,
@@ -379,6 +382,13 @@ struct PairParams {
   comm::PushJob push;
   comm::ReduceJob reduce;
 };
+
+// "Every CTA of launch `id` is resident": a kernel on another stream that spins on this GEMM's row-block signals
+// must not start before that, because with a static tile assignment a CTA pair that finds no room on its SMs
+// (taken by the spinning kernel's CTAs) would leave exactly the tiles undone that the spinning kernel waits for.
+// The consumer's stream runs a one-CTA wait on g_start_flag >= id in front of its kernel.
+__device__ unsigned g_start_count = 0;
+__device__ unsigned g_start_flag = 0;
 
 __device__ __forceinline__ int perm_tile_m(int i, const PairParams& p) {
   if (p.perm_mode == 0) return i;
@@ -469,7 +479,7 @@ __device__ __forceinline__ bool wait_block_counter(const uint32_t* c, uint32_t w
 // row-block-wise reduction of the partial products this GEMM and its peers signal), spread evenly over all
 // SMs, so that compute and transfer are ONE kernel and no SM carries more communication work than another.
 template <bool A_MN, bool B_MN, bool OUT_F32, bool COMM>
-__global__ void __launch_bounds__(COMM ? THREADS + COMM_THREADS : THREADS, 1)
+__global__ void __launch_bounds__((COMM ? THREADS + COMM_THREADS : THREADS) + SIGNAL_THREADS, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                  const __grid_constant__ CUtensorMap tmap_d, const PairParams p) {
   extern __shared__ uint8_t smem_raw[];
@@ -501,6 +511,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     }
     ctl->abort_flag = 0;
     ctl->comm_flag = 1;
+    for (int q = 0; q < 4; ++q) ctl->epi_done[q] = 0;
     mbar_fence_init();
   }
   if (warp == 1) {
@@ -513,6 +524,13 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   tc_fence_after();
   const uint32_t tmem_base = ctl->tmem_base;
   volatile int* abort_flag = &ctl->abort_flag;
+  if (p.start_id != 0 && threadIdx.x == 0) {
+    if (atomicAdd(&g_start_count, 1u) + 1u == gridDim.x) {       // the last CTA to become resident
+      atomicExch(&g_start_count, 0u);
+      __threadfence();
+      atomicMax(&g_start_flag, p.start_id);
+    }
+  }
 
   if (warp == 0) {
     // ------------------------------ TMA producer (both CTAs) ------------------
@@ -605,6 +623,41 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       }
     }
     __syncwarp();
+  } else if (warp == (COMM ? 8 : 6)) {
+    // ------------------------------ signal warp (both CTAs; launched only with row-block signals) -----------
+    // Tells the rank that owns a row block that this CTA's 128 rows of a tile are in memory.  The system-scope
+    // fence and the remote reduction take microseconds; here they delay nobody: the epilogue warps only publish
+    // "stores of tile k complete" in shared memory and go on.
+    if (lane == 0 && p.sig[0] != nullptr) {
+      uint32_t k = 0;
+      bool ok = true;
+      for (int it = pair_id; it < num_items && ok; it += num_pairs) {
+        const Item im = item_coords(it, p, num_tiles, num_kb);
+        if (im.kb0 >= im.kb1) continue;
+        ++k;
+        const long long t0 = clock64();
+        for (int q = 0; q < 4 && ok; ++q) {
+          while (ld_acquire_cta_u32(&ctl->epi_done[q]) < k) {
+            __nanosleep(64);
+            if (*abort_flag) { ok = false; break; }
+            if (clock64() - t0 > p.wait_budget) {
+              *abort_flag = 1;
+              report_error(p.status, ERR_FLAG_TIMEOUT, 330, (int)k);
+              ok = false;
+              break;
+            }
+          }
+        }
+        if (!ok) break;
+        const int m0 = im.tm * TILE_M + (int)rank * BM;
+        if (m0 < p.M) {
+          const int blk = m0 / BM;
+          asm volatile("fence.acq_rel.sys;" ::: "memory");
+          red_add_release_sys(p.sig[blk / p.sig_bpr] + (blk % p.sig_bpr), 1u);
+        }
+      }
+    }
+    __syncwarp();
   } else if (COMM && warp >= 6) {
     // ------------------------------ communication warps (both CTAs) -----------
     const int tid = (int)threadIdx.x - THREADS;
@@ -623,7 +676,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     int acc = 0;
     uint32_t acc_ph = 0;
     uint32_t cc = 0;                                // running chunk count -> staging tile parity
-    int pending_blk = -1;                           // row block whose completion signal is still owed (lane 0)
+    bool owed = false;                              // a tile's completion has not been published yet (lane 0)
+    uint32_t published = 0;
     bool ok = true;
     for (int it = pair_id; it < num_items && ok; it += num_pairs) {
       const Item im = item_coords(it, p, num_tiles, num_kb);
@@ -677,19 +731,17 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(&ctl->acc_empty[acc], 0);
-      if (p.sig[0] != nullptr && row0 < p.M) {
-        // Tell the rank that owns the row block that this warp's 32 rows of a tile are in memory.  The signal of
-        // tile i is sent after the stores of tile i + 1 have been issued: waiting for "all but the newest NCH
-        // groups" then completes tile i without stalling on the stores just issued.
+      if (p.sig[0] != nullptr) {
+        // Publish "the stores of the PREVIOUS tile are complete" to the signal warp: after the stores of this tile
+        // have been issued, waiting for all but the newest NCH groups completes the previous tile without stalling.
         if (lane == 0) {
-          if (pending_blk >= 0) {
+          if (owed) {
             if (chunks_done == NCH) tma_store_wait<NCH>();
             else tma_store_wait<0>();
             fence_proxy_async_all();
-            asm volatile("fence.acq_rel.sys;" ::: "memory");
-            red_add_release_sys(p.sig[pending_blk / p.sig_bpr] + (pending_blk % p.sig_bpr), 1u);
+            st_release_cta_u32(&ctl->epi_done[quarter], ++published);
           }
-          pending_blk = row0 / BM;
+          owed = true;
         }
         __syncwarp();
       }
@@ -697,10 +749,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     }
     if (lane == 0) {
       tma_store_wait<0>();                          // shared memory must outlive the bulk stores
-      if (pending_blk >= 0) {
+      if (owed) {
         fence_proxy_async_all();
-        asm volatile("fence.acq_rel.sys;" ::: "memory");
-        red_add_release_sys(p.sig[pending_blk / p.sig_bpr] + (pending_blk % p.sig_bpr), 1u);
+        st_release_cta_u32(&ctl->epi_done[quarter], ++published);
       }
     }
     __syncwarp();
@@ -732,7 +783,7 @@ static int launch_pair(const CUtensorMap* ta, const CUtensorMap* tb, const CUten
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(2 * pairs);
-  cfg.blockDim = dim3(COMM ? THREADS + COMM_THREADS : THREADS);
+  cfg.blockDim = dim3((COMM ? THREADS + COMM_THREADS : THREADS) + (p.sig[0] != nullptr ? SIGNAL_THREADS : 0));
   cfg.dynamicSmemBytes = SMEM2_BYTES - (RING - p.stages) * STAGE2_BYTES;
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
@@ -808,6 +859,7 @@ struct SyncArgs {
   int sig_bpr = 0;
   int perm_mode = 0, world = 1, rank = 0;
   int comm_kind = 0;                       // collective carried by the kernel's own communication warps
+  unsigned start_id = 0;                   // announce residency under this id (0 = no announcement)
   const comm::PushJob* push = nullptr;
   const comm::ReduceJob* reduce = nullptr;
 };
@@ -888,6 +940,7 @@ static int gemm_impl(const void* a, int64_t lda, int a_mn_major, const void* b, 
     }
     // barriers inside the CTA sit downstream of a peer wait, so they must outlast it
     p.wait_budget = (p.wait_count != nullptr) ? 2 * PEER_WAIT_CYCLES : (long long)DH_WAIT_BUDGET_CYCLES;
+    p.start_id = sy.start_id;
     const int num_items = num_tiles * p.split_k;
     if (sy.comm_kind == 0 && pairs > num_items) pairs = num_items;     // the communication warps use every CTA of the budget
     CUtensorMap td;
@@ -962,6 +1015,8 @@ extern "C" int dh_gemm_bf16(const void* a, int64_t lda, int a_mn_major, const vo
 //                             its counter on the owning rank (sig_ptrs[owner][block within the owner's shard])
 //   perm_mode                 0 natural row order, 1 own shard first then the others block by block, 2 block by
 //                             block over all owners
+static unsigned g_start_ids[64];             // per device: id of the newest signalling GEMM launched
+
 extern "C" int dh_gemm_bf16_sync(const void* a, int64_t lda, int a_mn_major, const void* b, int64_t ldb, int b_mn_major, void* d,
                                  int64_t ldd, int d_fp32, int accumulate, int M, int N, int K, int sm_budget, const void* wait_count,
                                  unsigned wait_target, void* const* sig_ptrs, int sig_bpr, int perm_mode, int world, int rank,
@@ -974,7 +1029,26 @@ extern "C" int dh_gemm_bf16_sync(const void* a, int64_t lda, int a_mn_major, con
   sy.perm_mode = perm_mode;
   sy.world = world;
   sy.rank = rank;
+  if (sig_ptrs != nullptr) {
+    // a GEMM whose row-block signals another kernel may spin on: announce when all of its CTAs are resident
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64) sy.start_id = ++g_start_ids[dev];
+  }
   return dh::gemm::gemm_impl(a, lda, a_mn_major, b, ldb, b_mn_major, d, ldd, d_fp32, accumulate, M, N, K, sm_budget, sy, stream);
+}
+
+// Device address of the word that holds the id of the newest signalling GEMM whose CTAs are all resident, and the id
+// that the most recent dh_gemm_bf16_sync call with row-block signals on this device announced (0: none yet).
+extern "C" const void* dh_gemm_start_flag_ptr() {
+  void* ptr = nullptr;
+  cudaGetSymbolAddress(&ptr, dh::gemm::pair::g_start_flag);
+  return ptr;
+}
+extern "C" unsigned dh_gemm_last_start_id() {
+  int dev = 0;
+  cudaGetDevice(&dev);
+  return (dev >= 0 && dev < 64) ? g_start_ids[dev] : 0u;
 }
 
 int dh_fill_push_job(dh::comm::PushJob& p, const char* who, const void* shard, void* const* stage_ptrs, void* const* count_ptrs,

@@ -103,6 +103,8 @@ class FusedTP:
             except Exception:
                 mc = 0
         self.mc_ptr = mc
+        e = os.environ.get("DHELLAM_MULTIMEM_PUSH", "")
+        self.mc_push = (e != "0") if e else self.world >= 4
         self.buf[cnt_base:cnt_end].zero_()
         torch.cuda.synchronize(self.device)
         dist.barrier(group=group)                 # nobody pushes before every rank's counters are zero
@@ -113,6 +115,8 @@ class FusedTP:
         self._pending = {}
         self.calls_split = {t: 0 for t in RS_TAGS}
         self._split_pending = {}
+        self._split_sync = {}
+        self._start_flag = None
         # "split" (default): every collective is its own small kernel on the communication stream
         # (multimem push / in-switch reduction) and the GEMM stays a plain local GEMM, so that the
         # schedule hides the transfer behind the other strand's kernels; "fused": every collective
@@ -154,6 +158,13 @@ class FusedTP:
 
     def _mc(self, off):
         return (self.mc_ptr + off) if self.mc_ptr else 0
+
+    def _mc_push(self, off):
+        """Multicast alias for the all-gather push, or 0 for per-peer stores.  A multicast store also returns the
+        sender's own rows through the switch, so a GPU receives world/(world-1) times the bytes of per-peer stores:
+        twice as many on 2 GPUs (measured there: 0.64 ms multicast, 0.53 ms per-peer for 134 MB), 1.14x on 8,
+        where one store instead of seven is worth it."""
+        return (self.mc_ptr + off) if (self.mc_ptr and self.mc_push) else 0
 
     def _stage_view(self, tag, slot, M, Kd):
         off = self.off_stage[tag][slot]
@@ -202,7 +213,7 @@ class FusedTP:
         fn = K.proto("dh_ag_gemm_bf16", [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_void_p, c_int64, c_int,
                                           c_int, c_int, c_int, c_int, c_int, c_uint, c_int, c_void_p])
         K.check(fn(shard.data_ptr(), self._ptr_array(self.off_stage[tag][slot]), self._ptr_array(self.off_agc[tag][slot]),
-                   self._mc(self.off_stage[tag][slot]), w.data_ptr(), w.stride(0), int(transpose_w), out.data_ptr(), out.stride(0),
+                   self._mc_push(self.off_stage[tag][slot]), w.data_ptr(), w.stride(0), int(transpose_w), out.data_ptr(), out.stride(0),
                    M, N, Kd, self.rank, self.world, slices, before, int(sm_budget), s.cuda_stream), "dh_ag_gemm_bf16")
         self._done(s)
         return out, self._stage_view(tag, slot, M, Kd)
@@ -218,7 +229,7 @@ class FusedTP:
         out = torch.empty((M // self.world, N), dtype=torch.bfloat16, device=self.device)
         slot = self.calls_split[tag] & 1
         self.calls_split[tag] += 1
-        self.total_sig[tag][slot] += self.world * 4 * ((N + 255) // 256)
+        self.total_sig[tag][slot] += self.world * ((N + 255) // 256)      # every rank: one signal per tile column
         target = self.total_sig[tag][slot]
         off = self.off_split[tag][slot]
         s = self._chain()
@@ -245,7 +256,7 @@ class FusedTP:
             shard.record_stream(s)
         fn = K.proto("dh_ag_push", [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p])
         K.check(fn(shard.data_ptr(), self._ptr_array(self.off_stage[tag][slot]), self._ptr_array(self.off_agc[tag][slot]),
-                   self._mc(self.off_stage[tag][slot]), M, Kd, self.rank, self.world, self.push_ctas, self.comm_threads, slices,
+                   self._mc_push(self.off_stage[tag][slot]), M, Kd, self.rank, self.world, self.push_ctas, self.comm_threads, slices,
                    s.cuda_stream), "dh_ag_push")
         ev = torch.cuda.Event()
         ev.record(s)
@@ -307,14 +318,15 @@ class FusedTP:
         from .gemm import GemmSync
         slot, use, _, _, _ = self._split_pending[tag]
         tiles_n = (N + 255) // 256
-        self.total_sig[tag][slot] += self.world * 4 * tiles_n       # every rank: 4 epilogue warps per tile column
+        self.total_sig[tag][slot] += self.world * tiles_n           # every rank: one signal per tile column
         target = self.total_sig[tag][slot]
         key = (tag, slot)
         if key not in self._sig_arrays:
             self._sig_arrays[key] = self._ptr_array(self.off_rsflag[tag][slot])
+        sync = GemmSync(sig_ptrs=self._sig_arrays[key], sig_bpr=M // self.world // 128, perm_mode=2, world=self.world, rank=self.rank)
         self._split_pending[tag] = (slot, use, M, N, target)
-        return buf, GemmSync(sig_ptrs=self._sig_arrays[key], sig_bpr=M // self.world // 128, perm_mode=2, world=self.world,
-                             rank=self.rank)
+        self._split_sync[tag] = sync
+        return buf, sync
 
     def rs_reduce(self, tag: str):
         """Runs on the current stream, which must already wait for the GEMM that filled the buffer."""
@@ -325,6 +337,15 @@ class FusedTP:
         out = torch.empty((M // self.world, N), dtype=torch.bfloat16, device=self.device)
         s = torch.cuda.current_stream(self.device)
         if block_target is not None:
+            sync = self._split_sync.pop(tag, None)
+            if sync is not None and sync.start_id:
+                # The reduction spins on the GEMM's row-block signals and may be launched while that GEMM has not
+                # started: a one-CTA wait in front of it holds this stream until every CTA of the GEMM is resident,
+                # so the spinning CTAs can never keep a CTA pair of the GEMM (static tile assignment) off its SMs.
+                if self._start_flag is None:
+                    self._start_flag = K.proto("dh_gemm_start_flag_ptr", [], c_void_p)()
+                wfn = K.proto("dh_wait_counters", [c_void_p, c_int, c_uint, c_int64, c_void_p])
+                K.check(wfn(self._start_flag, 1, sync.start_id, 0, s.cuda_stream), "dh_wait_counters")
             fn = K.proto("dh_rs_reduce_blocks", [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_uint, c_int, c_int,
                                                   c_void_p])
             off = self.off_split[tag][slot]

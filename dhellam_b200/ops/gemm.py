@@ -16,6 +16,8 @@ from __future__ import annotations
 
 from ctypes import c_int, c_int64, c_uint, c_void_p
 
+import ctypes
+
 import torch
 
 from .. import kernels as K
@@ -40,6 +42,7 @@ class GemmSync:
         self.wait_count, self.wait_target = wait_count, wait_target
         self.sig_ptrs, self.sig_bpr = sig_ptrs, sig_bpr
         self.perm_mode, self.world, self.rank = perm_mode, world, rank
+        self.start_id = 0          # set by the launch: id under which the kernel announces "all CTAs resident"
 
 
 def _native(*ts) -> bool:
@@ -65,6 +68,8 @@ def _launch(a, a_mn, b, b_mn, d, accumulate, M, N, Kdim, sm_budget, stream, sync
                 int(sync.wait_target), sync.sig_ptrs, int(sync.sig_bpr), int(sync.perm_mode), int(sync.world), int(sync.rank),
                 K.stream_ptr(stream))
         K.check(rc, "dh_gemm_bf16_sync")
+        if sync.sig_ptrs is not None:
+            sync.start_id = K.proto("dh_gemm_last_start_id", [], ctypes.c_uint)()
         return
     fn = K.proto("dh_gemm_bf16", _GEMM_ARGS)
     rc = fn(a.data_ptr(), a.stride(0), int(a_mn), b.data_ptr(), b.stride(0), int(b_mn), d.data_ptr(), d.stride(0),

@@ -251,6 +251,27 @@ def test_attention_forward_backward(Sq, Sk, B, Hq, Hk, causal, attn_bwd_mode):
     assert rel(dv, dvr) < 2e-2, ("dv", rel(dv, dvr))
 
 
+@pytest.mark.parametrize("budget", [1, 5, 24, 100])
+def test_attention_sm_budget_gives_identical_results(budget):
+    """With an SM budget the attention kernels run as consecutive launches of at most that many CTAs
+    (tile columns split when one head alone has more tiles than the budget, else whole (head, batch)
+    pairs per launch); every tile computes exactly what it computes without a budget."""
+    from dhellam_b200.ops.attention import attn_bwd, attn_fwd
+    Sq, B, Hq, Hk, d = 1024, 2, 4, 2, 128
+    qkv = bf(Sq, B, Hq + 2 * Hk, d)
+    q, k, v = qkv[:, :, :Hq], qkv[:, :, Hq:Hq + Hk], qkv[:, :, Hq + Hk:]
+    do = bf(Sq, B, Hq, d)
+    scale = 1.0 / math.sqrt(d)
+    o0, l0 = attn_fwd(q, k, v, True, scale)
+    g0 = attn_bwd(do, q, k, v, o0, l0, True, scale)
+    o1, l1 = attn_fwd(q, k, v, True, scale, sm_budget=budget)
+    g1 = attn_bwd(do, q, k, v, o1, l1, True, scale, sm_budget=budget)
+    torch.cuda.synchronize()
+    assert torch.equal(o0, o1) and torch.equal(l0, l1)
+    for a, b in zip(g0, g1):
+        assert torch.equal(a, b)
+
+
 def test_bounded_wait_reports_timeout_without_hanging():
     """A flag that nobody sets: the device-side wait gives up after its (short) budget and
     the host reads the status word; the context stays usable."""
