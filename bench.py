@@ -414,6 +414,13 @@ def main():
                                       "direction": "vs_composition = native tokens/s / composition tokens/s"}
         if ab:
             out["ab"] = ab
+        if args.pp > 1:
+            # the folded two-strand schedule fills and drains like 1F1B: (stages - 1) of (micro-batches + stages - 1) slots idle
+            tp_ = args.tp or max(N // (args.cp * args.pp * max(args.ep, 1)), 1)
+            n_mb = args.global_batch // max(mbs * (N // (tp_ * args.cp * args.pp)), 1)
+            out["pp_bubble"] = {"stages": args.pp, "micro_batches": n_mb,
+                                "ideal_frac": round((args.pp - 1) / (n_mb + args.pp - 1), 4),
+                                "what": "share of a stage's time slots that are empty in the fill and drain phases (from the schedule, not measured)"}
         if args.layers:
             out["config"]["note"] = "layer count overridden: not the headline configuration"
         print(json.dumps(out))

@@ -131,6 +131,17 @@ def main(argv=None):
     emit("gemm_col_parallel_alone", _time(lambda: gemm_nt(full, w_c), a.iters, a.warmup, dev, ps.tp_group), 0, fl_c, link,
          note="[%d, %d] x [%d, %d]^T, no collective" % (rows, h, n_c, h))
 
+    def into_symmetric():
+        gemm_nt(a_l, w_l, out=fused.partial_buffer("head_bwd", rows, h))
+    emit("gemm_row_parallel_into_symmetric", _time(into_symmetric, a.iters, a.warmup, dev, ps.tp_group), 0, fl_l, link,
+         note="the same GEMM writing into the symmetric partial buffer, no signals, usual tile order")
+
+    def owner_order_only():
+        from ..ops.gemm import GemmSync
+        gemm_nt(a_l, w_l, out=fused.partial_buffer("head_bwd", rows, h), sync=GemmSync(perm_mode=2, world=world, rank=rank))
+    emit("gemm_row_parallel_owner_order", _time(owner_order_only, a.iters, a.warmup, dev, ps.tp_group), 0, fl_l, link,
+         note="the same with the row-block-by-owner tile order and the 5-deep ring, still no signals")
+
     def signalling_gemm():
         part, sync = fused.partial_produce("attn_c_bwd", rows, h)
         gemm_nt(a_l, w_l, out=part, sync=sync)
