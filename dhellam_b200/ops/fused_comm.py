@@ -1,34 +1,38 @@
-"""Tensor-parallel collectives fused into the GEMM kernels over NVLink peer memory.
+"""Tensor-parallel (and context-parallel) collectives over NVLink peer memory.
 
-``FusedTP`` owns the symmetric memory of one tensor-parallel group and launches the kernels
-of ``csrc/comm_fused.cu``:
+``FusedTP`` owns the symmetric memory of one tensor-parallel group and launches the kernels of
+``csrc/comm_fused.cu`` and the collective forms of the GEMM in ``csrc/gemm_sm100.cu``:
 
-* ``ag_gemm(shard, w, tag)`` = ``all_gather(shard) @ op(w)``; the gathered operand stays in
-  the local staging buffer of ``tag`` and is returned as a view (valid until the second next
-  call with the same tag), replacing ``allgather_* + gemm_*`` of the reference
-  (dhellam/core/dstb.py:412-425 + :80-107);
-* ``gemm_rs(a, w)`` = ``reduce_scatter(a @ op(w))``, replacing ``gemm_* + reduce_scatter``
-  (dstb.py:407-410);
-* ``gather_start(shard, tag)`` / ``gather_wait(tag)``: the all-gather alone, pushed from a
-  few CTAs on the communication stream while other kernels run; used by the split policy
-  (below) and to re-gather the sequence-parallel input of a column-parallel layer for its
-  weight gradient instead of keeping the gathered activation alive from the forward pass;
-* ``partial_buffer(tag, M, N)`` / ``rs_reduce(tag)``: the reduce-scatter alone: a plain local
-  GEMM writes its partial product into symmetric memory, then a small kernel on the
-  communication stream exchanges completion flags and reduces this rank's rows inside the
-  NVSwitch (``multimem.ld_reduce``) or with peer loads.
+* ``gather_start(shard, tag)`` pushes this rank's rows into every rank's staging buffer from a few CTAs
+  on the communication stream and raises per-128-row-block arrival counters; ``gather_consume(tag)``
+  hands the consuming GEMM the staged operand plus a ``GemmSync`` that makes the kernel wait per row
+  block (own rows first); ``gather_wait(tag)`` is the whole-buffer wait in front of any other consumer.
+  Also used to re-gather the sequence-parallel input of a column-parallel layer for its weight gradient
+  instead of keeping the gathered activation alive from the forward pass.  Replaces ``allgather_*``
+  of the reference (dhellam/core/dstb.py:412-425, dhellam/operators/comm.py:13-33).
+* ``partial_produce(tag, M, N)`` gives the producing GEMM a symmetric partial buffer plus a ``GemmSync``
+  that makes it write row block by row block over all owners and signal each finished block to its owner;
+  ``rs_reduce(tag)`` launches the reduction that follows those signals (in-switch ``multimem.ld_reduce`` or
+  peer loads) and may be launched as soon as the GEMM has been launched.  ``partial_buffer`` /
+  ``rs_reduce`` without signals is the whole-buffer form.  Replaces ``reduce_scatter_*``
+  (dstb.py:407-410, comm.py:35-58).
+* ``ag_gemm(shard, w, tag)`` / ``gemm_rs(a, w, tag)``: the same two pairs as ONE kernel each, with the push /
+  reduction carried by communication warps inside every GEMM CTA (policy ``fused``).
 
 ``split(M, N, K)`` says per call site which form the layer ops use (``DHELLAM_FUSED_POLICY``).
 
-Every staging buffer is double-buffered per tag, with monotonically increasing arrival
-counters.  Kernels that wait for peers inside the kernel (``ag_gemm``, ``gemm_rs``) are
-chained to one another with events so that all ranks run them one at a time in the same
-order; pure pushes do not wait for anybody and are not chained.
+Every staging / partial buffer is double-buffered per tag, with monotonically increasing counters (no resets,
+no host barriers).  Kernels that wait for peers inside the kernel (``ag_gemm``, ``gemm_rs``) are chained to one
+another with events so that all ranks run them one at a time in the same order; pure pushes wait for nobody.
 
-The NVSwitch multicast address of the buffer (``multimem.st``: one store reaches all ranks)
-is used when the platform provides it and ``DHELLAM_MULTIMEM`` is not ``0``; otherwise the
-push stores to every peer in turn.  Peer pointers come from
-``torch.distributed._symmetric_memory`` (one allocation, one rendezvous).
+The NVSwitch multicast address of the buffer is used for the in-switch reduction whenever the platform
+provides it, and for the push on 4 or more GPUs (``DHELLAM_MULTIMEM``, ``DHELLAM_MULTIMEM_PUSH``).  Peer
+pointers come from ``torch.distributed._symmetric_memory`` (one allocation, one rendezvous).
+
+``FusedCP`` is the context-parallel counterpart: key/value chunks pushed into global order in every rank's
+buffer, per-chunk arrival waits, partial dK|dV reduced by the chunk owners (role of the reference's ring,
+dhellam/operators/ring_attn.py:43-201, without its per-step exchanges).  ``SimulatedCP`` runs the same data
+flow on library collectives for the CPU tests.
 """
 from __future__ import annotations
 
@@ -117,13 +121,12 @@ class FusedTP:
         self._split_pending = {}
         self._split_sync = {}
         self._start_flag = None
-        # "split" (default): every collective is its own small kernel on the communication stream
-        # (multimem push / in-switch reduction) and the GEMM stays a plain local GEMM, so that the
-        # schedule hides the transfer behind the other strand's kernels; "fused": every collective
-        # inside its GEMM kernel, overlapped tile by tile with that GEMM only; "auto": split while
-        # both strands are live, fused in the warm-up and cool-down rounds.  Measured on 8 GPUs
-        # (tokens/s, headline model): split 138.9k, auto 134.6k, fused 126.6k; on 2 GPUs the three
-        # are within 1%.
+        # "split" (default): every collective is its own small kernel on the communication stream, beside a
+        # GEMM that waits per row block / signals finished row blocks, so that the schedule hides the transfer
+        # behind the other strand's kernels too; "fused": every collective inside its GEMM kernel (communication
+        # warps), overlapped tile by tile with that GEMM only; "auto": split while both strands are live, fused
+        # in the warm-up and cool-down rounds.  Measured on 8 GPUs (tokens/s, headline model, one process):
+        # split 139.5k, fused 130.8k, library collectives 137.0k; on 2 GPUs split and fused are within 1 %.
         self.policy = os.environ.get("DHELLAM_FUSED_POLICY", "split")
         self.paired = True                # set by the engine before every layer run
         self.rs_ctas = int(os.environ.get("DHELLAM_RS_CTAS", "0")) or (self.sms if spread else max(16, 128 // self.world))
