@@ -29,6 +29,16 @@ def _seed_and_status():
     assert st.code == 0, f"device status {st.code} at {st.where}"
 
 
+@pytest.fixture(params=[False, True], ids=["atomic", "reproducible"])
+def reduction_mode(request):
+    """The kernels with cross-CTA reductions in both forms: order-dependent atomics (default) and the
+    fixed-order forms of the reproducible mode."""
+    from dhellam_b200 import kernels as K
+    K.set_deterministic(request.param)
+    yield request.param
+    K.set_deterministic(False)
+
+
 @pytest.fixture(params=[1, 2], ids=["single_cta", "cta_pair"])
 def gemm_mode(request):
     from dhellam_b200.ops.gemm import set_gemm_mode
@@ -103,7 +113,7 @@ def test_gemm_sm_budget_and_strided_output(gemm_mode):
 
 
 @pytest.mark.parametrize("rows,h", [(64, 256), (300, 4096), (257, 8192), (33, 1024)])
-def test_rmsnorm(rows, h):
+def test_rmsnorm(rows, h, reduction_mode):
     from dhellam_b200.ops.norm import rmsnorm_bwd, rmsnorm_fwd
     x, w, dy, res = bf(rows, h), bf(h) * 0.1 + 1, bf(rows, h), bf(rows, h)
     y, rstd = rmsnorm_fwd(x, w, 1e-5)
@@ -117,7 +127,7 @@ def test_rmsnorm(rows, h):
 
 
 @pytest.mark.parametrize("rows,h", [(64, 256), (129, 5120)])
-def test_layernorm(rows, h):
+def test_layernorm(rows, h, reduction_mode):
     from dhellam_b200.ops.norm import layernorm_bwd, layernorm_fwd
     x, w, b, dy = bf(rows, h) + 0.5, bf(h) * 0.1 + 1, bf(h) * 0.1, bf(rows, h)
     y, mu, rstd = layernorm_fwd(x, w, b, 1e-5)
@@ -163,7 +173,7 @@ def test_rope_roundtrip_and_reference():
     assert rel(back, orig) < 1e-2
 
 
-def test_embedding_and_cross_entropy():
+def test_embedding_and_cross_entropy(reduction_mode):
     from dhellam_b200.ops.embedding import embedding_bwd, embedding_fwd
     from dhellam_b200.ops.loss import ce_combine_stats, ce_local_stats, vocab_parallel_ce_bwd_
     T, h, Vl, v0 = 200, 256, 1000, 500
@@ -189,7 +199,7 @@ def test_embedding_and_cross_entropy():
         assert rel(out, ref) < 1e-2
 
 
-def test_adam_and_sum_squares():
+def test_adam_and_sum_squares(reduction_mode):
     from dhellam_b200.optim.adam import adam_update, sum_squares
     n = 4096 * 3 + 4
     master = torch.randn(n, device=DEV)
