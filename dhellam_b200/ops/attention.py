@@ -146,18 +146,38 @@ def set_attn_bwd_mode(mode: int):
     K.proto("dh_attn_set_bwd_mode", [c_int], None)(int(mode))
 
 
+def _uniform_length(cu):
+    """Common length of the sequences described by cumulative offsets ``cu`` (starting at 0), or 0 if they differ."""
+    if len(cu) < 2 or cu[0] != 0:
+        return 0
+    n = cu[1] - cu[0]
+    return n if n > 0 and all(cu[i + 1] - cu[i] == n for i in range(len(cu) - 1)) else 0
+
+
+def _as_sbhd(t, b, s):
+    """Packed ``[b * s, h, d]`` seen as ``[s, b, h, d]`` (a view; the kernels take strides)."""
+    return t.view(b, s, t.shape[1], t.shape[2]).permute(1, 0, 2, 3)
+
+
 def pymha_varlen_fwd(q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k, p_dropout: float = 0.0,
                      softmax_scale: float | None = None, is_causal: bool = True, return_softmax: bool = False,
                      math_sm_count: int = 0, profiling: bool = False):
     """Packed variable-length attention with the reference's signature
     (csrc/operators/ops.h:18-32): ``q [total_q, h, d]``, ``k, v [total_k, h_k, d]`` and
     cumulative sequence offsets.  Returns ``(out [total_q, h, d], softmax_lse [b, h, max_q])``.
-    Each sequence runs as one strided call of the fixed-length kernel, so no padding copy
-    is made.  Attention dropout is not supported by the sm_100a kernel (``p_dropout`` must be 0)."""
+    A batch of equal-length sequences runs as ONE launch over strided views of the packed tensors; sequences
+    of different lengths run one strided call each, so no padding copy is made.  Attention dropout is not supported by the sm_100a kernel (``p_dropout`` must be 0)."""
     assert p_dropout == 0.0, "attention dropout is not implemented"
     cq = [int(x) for x in cu_seqlens_q.tolist()]
     ck = [int(x) for x in cu_seqlens_k.tolist()]
     b = len(cq) - 1
+    sq, sk = _uniform_length(cq), _uniform_length(ck)
+    if sq and sk and sq == max_seqlen_q:
+        # every sequence has the same length (the reference's own use: a micro-batch of fixed-length samples):
+        # the packed [b * s, h, d] tensors are [s, b, h, d] tensors with other strides, one launch does it all
+        o, lse = attn_fwd(_as_sbhd(q, b, sq), _as_sbhd(k, b, sk), _as_sbhd(v, b, sk), is_causal, softmax_scale,
+                          sm_budget=abs(math_sm_count))
+        return o.permute(1, 0, 2, 3).reshape(q.shape), lse
     out = torch.empty_like(q)
     lse = torch.full((b, q.shape[1], max_seqlen_q), float("-inf"), dtype=torch.float32, device=q.device)
     for i in range(b):
@@ -175,6 +195,15 @@ def pymha_varlen_bwd(dout, q, k, v, out, softmax_lse, cu_seqlens_q, cu_seqlens_k
     cq = [int(x) for x in cu_seqlens_q.tolist()]
     ck = [int(x) for x in cu_seqlens_k.tolist()]
     dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+    b = len(cq) - 1
+    sq, sk = _uniform_length(cq), _uniform_length(ck)
+    if sq and sk and sq == max_seqlen_q and softmax_lse.shape[-1] == sq:
+        a, b_, c = attn_bwd(_as_sbhd(dout, b, sq), _as_sbhd(q, b, sq), _as_sbhd(k, b, sk), _as_sbhd(v, b, sk), _as_sbhd(out, b, sq),
+                            softmax_lse, is_causal, softmax_scale, sm_budget=abs(math_sm_count))
+        dq.copy_(a.permute(1, 0, 2, 3).reshape(q.shape))
+        dk.copy_(b_.permute(1, 0, 2, 3).reshape(k.shape))
+        dv.copy_(c.permute(1, 0, 2, 3).reshape(v.shape))
+        return dq, dk, dv
     for i in range(len(cq) - 1):
         sl_q, sl_k = slice(cq[i], cq[i + 1]), slice(ck[i], ck[i + 1])
         lse_i = softmax_lse[i:i + 1, :, : cq[i + 1] - cq[i]].contiguous()

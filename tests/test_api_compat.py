@@ -38,6 +38,34 @@ def test_varlen_attention_matches_per_sequence_reference():
     assert dq.shape == q.shape and dk.shape == k.shape and torch.isfinite(dv).all()
 
 
+def test_varlen_attention_with_equal_lengths_runs_as_one_call_and_matches_the_per_sequence_path():
+    """A packed batch of equal-length sequences (what the reference passes) takes the single-launch path; the
+    result equals the per-sequence path, which unequal lengths force."""
+    from dhellam_b200 import pymha_varlen_bwd, pymha_varlen_fwd
+    from dhellam_b200.ops import attention as ATT
+    torch.manual_seed(1)
+    b, s, hq, hk, d = 3, 8, 4, 2, 16
+    cu = torch.arange(0, (b + 1) * s, s, dtype=torch.int32)
+    q, k, v = torch.randn(b * s, hq, d), torch.randn(b * s, hk, d), torch.randn(b * s, hk, d)
+    dout = torch.randn(b * s, hq, d)
+    calls = []
+    real = ATT.attn_fwd
+    ATT.attn_fwd = lambda *a, **kw: (calls.append(1), real(*a, **kw))[1]
+    try:
+        out, lse = pymha_varlen_fwd(q, k, v, cu, cu, s, s, 0.0, 0.25, True)
+    finally:
+        ATT.attn_fwd = real
+    assert len(calls) == 1 and out.shape == q.shape and lse.shape == (b, hq, s)
+    dq, dk, dv = pymha_varlen_bwd(dout, q, k, v, out, lse, cu, cu, s, s, 0.0, 0.25, True)
+    for i in range(b):
+        sl = slice(i * s, (i + 1) * s)
+        c1 = torch.tensor([0, s], dtype=torch.int32)
+        o_i, l_i = pymha_varlen_fwd(q[sl], k[sl], v[sl], c1, c1, s + 1, s + 1, 0.0, 0.25, True)     # max != length: loop path
+        assert torch.allclose(out[sl], o_i, atol=1e-5) and torch.allclose(lse[i], l_i[0, :, :s], atol=1e-5)
+        g = pymha_varlen_bwd(dout[sl], q[sl], k[sl], v[sl], o_i, l_i, c1, c1, s + 1, s + 1, 0.0, 0.25, True)
+        assert torch.allclose(dq[sl], g[0], atol=1e-5) and torch.allclose(dk[sl], g[1], atol=1e-5) and torch.allclose(dv[sl], g[2], atol=1e-5)
+
+
 def test_qkv_layout_probe():
     from dhellam_b200 import _get_qkv_layout
     s, b, h, d = 4, 2, 3, 8

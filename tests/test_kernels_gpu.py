@@ -282,6 +282,24 @@ def test_attention_sm_budget_gives_identical_results(budget):
         assert torch.equal(a, b)
 
 
+def test_varlen_api_with_equal_lengths_uses_strided_views_of_the_packed_tensors():
+    """``pymha_varlen_fwd / bwd`` on a packed batch of equal-length sequences (one launch over strided views)
+    against the fixed-length entry points on contiguous [s, b, h, d] copies."""
+    from dhellam_b200.ops.attention import attn_bwd, attn_fwd, pymha_varlen_bwd, pymha_varlen_fwd
+    b, s, hq, hk, d = 3, 256, 4, 2, 128
+    cu = torch.arange(0, (b + 1) * s, s, dtype=torch.int32, device=DEV)
+    q, k, v, do = bf(b * s, hq, d), bf(b * s, hk, d), bf(b * s, hk, d), bf(b * s, hq, d)
+    scale = 1.0 / math.sqrt(d)
+    out, lse = pymha_varlen_fwd(q, k, v, cu, cu, s, s, 0.0, scale, True)
+    dq, dk, dv = pymha_varlen_bwd(do, q, k, v, out, lse, cu, cu, s, s, 0.0, scale, True)
+    sb = lambda t: t.view(b, s, t.shape[1], d).permute(1, 0, 2, 3).contiguous()
+    o2, l2 = attn_fwd(sb(q), sb(k), sb(v), True, scale)
+    g2 = attn_bwd(sb(do), sb(q), sb(k), sb(v), o2, l2, True, scale)
+    assert torch.equal(sb(out), o2) and torch.equal(lse, l2)
+    for a, r in zip((dq, dk, dv), g2):
+        assert rel(sb(a), r) < 1e-3
+
+
 def test_bounded_wait_reports_timeout_without_hanging():
     """A flag that nobody sets: the device-side wait gives up after its (short) budget and
     the host reads the status word; the context stays usable."""
