@@ -261,6 +261,33 @@ def test_attention_forward_backward(Sq, Sk, B, Hq, Hk, causal, attn_bwd_mode):
     assert rel(dv, dvr) < 2e-2, ("dv", rel(dv, dvr))
 
 
+@pytest.mark.parametrize("Sq,Sk,B,Hq,Hk", [(4096, 4096, 1, 8, 1), (1024, 2048, 2, 4, 2), (2048, 2048, 4, 16, 2)])
+def test_attention_large_shapes_against_fp32(Sq, Sk, B, Hq, Hk):
+    """Causal attention at the sizes the training step uses, against plain fp32 PyTorch (explicit softmax and
+    autograd on the GPU): 4096 positions with eight query heads on one KV head (the dK/dV kernel then splits the
+    heads of that KV head over several CTAs), more keys than queries (mask aligned to the last key, the
+    context-parallel case), and a batch that fills the GPU without a head split."""
+    from dhellam_b200.ops.attention import attn_bwd, attn_fwd
+    d = 128
+    scale = 1.0 / math.sqrt(d)
+    q, k, v, do = bf(Sq, B, Hq, d), bf(Sk, B, Hk, d), bf(Sk, B, Hk, d), bf(Sq, B, Hq, d)
+    o, lse = attn_fwd(q, k, v, True, scale)
+    dq, dk, dv = attn_bwd(do, q, k, v, o, lse, True, scale)
+    qf, kf, vf = (t.float().requires_grad_() for t in (q, k, v))
+    g = Hq // Hk
+    sc = torch.einsum("sbhd,tbhd->bhst", qf, kf.repeat_interleave(g, dim=2)) * scale
+    i = torch.arange(Sq, device=DEV).unsqueeze(1)
+    j = torch.arange(Sk, device=DEV).unsqueeze(0)
+    sc = sc.masked_fill(j > i + (Sk - Sq), float("-inf"))
+    ref_lse = torch.logsumexp(sc, dim=-1)
+    oref = torch.einsum("bhst,tbhd->sbhd", torch.softmax(sc, dim=-1), vf.repeat_interleave(g, dim=2))
+    oref.backward(do.float())
+    assert rel(o, oref.detach()) < 1e-2 and rel(lse, ref_lse.detach()) < 1e-3
+    assert rel(dq, qf.grad) < 2e-2, ("dq", rel(dq, qf.grad))
+    assert rel(dk, kf.grad) < 2e-2, ("dk", rel(dk, kf.grad))
+    assert rel(dv, vf.grad) < 2e-2, ("dv", rel(dv, vf.grad))
+
+
 @pytest.mark.parametrize("budget", [1, 5, 24, 100])
 def test_attention_sm_budget_gives_identical_results(budget):
     """With an SM budget the attention kernels run as consecutive launches of at most that many CTAs
