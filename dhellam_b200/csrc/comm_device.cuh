@@ -117,7 +117,8 @@ __device__ __forceinline__ void push_rows(const PushJob& p, int group, int ngrou
     group_sync();
     if (tid == 0) {
       asm volatile("fence.acq_rel.sys;" ::: "memory");
-      for (int j = 0; j < p.world; ++j) red_add_release_sys(p.count[(p.rank - j + p.world) % p.world] + gb, 1u);
+      // one fence, then relaxed reductions: a release reduction per rank would repeat the fence world times
+      for (int j = 0; j < p.world; ++j) red_add_relaxed_sys(p.count[(p.rank - j + p.world) % p.world] + gb, 1u);
     }
   }
 }

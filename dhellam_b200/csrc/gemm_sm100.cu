@@ -629,31 +629,45 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     // fence and the remote reduction take microseconds; here they delay nobody: the epilogue warps only publish
     // "stores of tile k complete" in shared memory and go on.
     if (lane == 0 && p.sig[0] != nullptr) {
-      uint32_t k = 0;
+      // One system-scope fence per BATCH of finished tiles, then one relaxed remote reduction per tile: the fence
+      // (microseconds) is the only part that waits, and a backlog costs one fence, not one per tile.
+      uint32_t done = 0;                            // tiles of this CTA signalled so far
+      int it = pair_id;                             // work item of tile number `done`
       bool ok = true;
-      for (int it = pair_id; it < num_items && ok; it += num_pairs) {
-        const Item im = item_coords(it, p, num_tiles, num_kb);
-        if (im.kb0 >= im.kb1) continue;
-        ++k;
+      while (ok) {
+        while (it < num_items) {                    // skip items without work (no tile, no signal)
+          const Item im = item_coords(it, p, num_tiles, num_kb);
+          if (im.kb0 < im.kb1) break;
+          it += num_pairs;
+        }
+        if (it >= num_items) break;
+        uint32_t ready = done;
         const long long t0 = clock64();
-        for (int q = 0; q < 4 && ok; ++q) {
-          while (ld_acquire_cta_u32(&ctl->epi_done[q]) < k) {
-            __nanosleep(64);
-            if (*abort_flag) { ok = false; break; }
-            if (clock64() - t0 > p.wait_budget) {
-              *abort_flag = 1;
-              report_error(p.status, ERR_FLAG_TIMEOUT, 330, (int)k);
-              ok = false;
-              break;
-            }
+        while (true) {
+          ready = ld_acquire_cta_u32(&ctl->epi_done[0]);
+          for (int q = 1; q < 4; ++q) ready = min(ready, ld_acquire_cta_u32(&ctl->epi_done[q]));
+          if (ready > done) break;
+          __nanosleep(64);
+          if (*abort_flag) { ok = false; break; }
+          if (clock64() - t0 > p.wait_budget) {
+            *abort_flag = 1;
+            report_error(p.status, ERR_FLAG_TIMEOUT, 330, (int)done);
+            ok = false;
+            break;
           }
         }
         if (!ok) break;
-        const int m0 = im.tm * TILE_M + (int)rank * BM;
-        if (m0 < p.M) {
-          const int blk = m0 / BM;
-          asm volatile("fence.acq_rel.sys;" ::: "memory");
-          red_add_release_sys(p.sig[blk / p.sig_bpr] + (blk % p.sig_bpr), 1u);
+        asm volatile("fence.acq_rel.sys;" ::: "memory");
+        while (done < ready && it < num_items) {
+          const Item im = item_coords(it, p, num_tiles, num_kb);
+          it += num_pairs;
+          if (im.kb0 >= im.kb1) continue;
+          const int m0 = im.tm * TILE_M + (int)rank * BM;
+          if (m0 < p.M) {
+            const int blk = m0 / BM;
+            red_add_relaxed_sys(p.sig[blk / p.sig_bpr] + (blk % p.sig_bpr), 1u);
+          }
+          ++done;
         }
       }
     }

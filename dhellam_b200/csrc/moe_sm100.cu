@@ -198,7 +198,7 @@ __global__ void __launch_bounds__(256) moe_dispatch_kernel(const DispatchParams 
     if (done == gridDim.x) {
       *p.done_ctas = 0u;
       asm volatile("fence.acq_rel.sys;" ::: "memory");
-      for (int d = 0; d < p.ep; ++d) red_add_release_sys(p.arrived[d], 1u);
+      for (int d = 0; d < p.ep; ++d) red_add_relaxed_sys(p.arrived[d], 1u);      // released by the fence above
     }
   }
 }

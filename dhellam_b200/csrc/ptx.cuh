@@ -342,6 +342,10 @@ __device__ __forceinline__ uint32_t ld_acquire_cta_u32(const uint32_t* p) {
 __device__ __forceinline__ void st_release_cta_u32(uint32_t* p, uint32_t v) {
   asm volatile("st.release.cta.shared::cta.u32 [%0], %1;" ::"r"((uint32_t)__cvta_generic_to_shared(p)), "r"(v) : "memory");
 }
+// Relaxed system-scope reduction: a release only together with a preceding fence.acq_rel.sys.
+__device__ __forceinline__ void red_add_relaxed_sys(uint32_t* p, uint32_t v) {
+  asm volatile("red.relaxed.sys.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
 __device__ __forceinline__ void red_add_release_sys(uint32_t* p, uint32_t v) {
   asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
