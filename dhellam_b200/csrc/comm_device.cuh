@@ -194,25 +194,18 @@ __device__ __forceinline__ bool reduce_rows(const ReduceJob& p, int group, int n
   return true;
 }
 
-// Column slices per row block of a push: (row blocks x slices) work items over `groups` thread groups, taken
-// block by block, so that at most about four row blocks are in flight at a time and the first blocks of the
-// shard arrive early (a consumer that waits per row block starts long before the last block has been sent;
-// one whole block per group would deliver them all at once, at the end).  A pure function of its arguments,
-// so every rank and the host agree on the counter increments.
+// Column slices per 128-row block: (row blocks x slices) work items are dealt to `groups` thread groups block by
+// block.  Enough slices that only about four row blocks are in flight at a time (the first blocks of a pushed
+// shard arrive early, and every group works on the row block of a reduction that has just become complete), at
+// most 32 (an item then still moves 64 KB per fence / per counter wait at width 8192), and at least one item per
+// group.  A pure function of its arguments, so every rank and the host agree on the counter increments.
 __host__ __device__ inline int slices_for(int blocks, int width, int groups) {
   int s = 1;
-  while ((blocks * s < groups || s * 4 < groups) && (width / (s * 2)) % 8 == 0 && width / (s * 2) >= 64 && s < 64) s *= 2;
+  while ((blocks * s < groups || s * 4 < groups) && s < 32 && (width / (s * 2)) % 8 == 0 && width / (s * 2) >= 64) s *= 2;
   return s;
 }
 
-// Column slices per row block for the reduction: at least one per thread group, so that every group works on
-// the row block that has just become complete instead of one group owning it (the last block to complete would
-// otherwise be reduced by a single group after the producers have finished).
-__host__ __device__ inline int reduce_slices_for(int width, int groups) {
-  int s = 1;
-  while (s < groups && (width / (s * 2)) % 8 == 0 && width / (s * 2) >= 64 && s < 256) s *= 2;
-  return s;
-}
+__host__ __device__ inline int reduce_slices_for(int width, int groups) { return slices_for(1 << 20, width, groups); }
 
 }  // namespace comm
 }  // namespace dh

@@ -63,12 +63,14 @@ class FusedTP:
         self.world, self.rank = ps.tp, ps.tp_rank
         # the shard a rank pushes is 1/tp of the operand: fewer ranks -> more bytes per rank -> more copy CTAs
         self.sms = K.lib().dh_sm_count()
-        # Stand-alone communication kernels: how many CTAs of how many threads.  DHELLAM_COMM_SPREAD=1 launches one
-        # small CTA per SM (64 threads), which loads every SM equally beside a statically scheduled persistent GEMM;
-        # the default is a few 256-thread CTAs.
+        # Stand-alone communication kernels: one CTA of 256 threads per SM.  A persistent GEMM assigns its tiles to
+        # CTAs statically, so a copy kernel that sits on 16 SMs slows those 16 CTAs and with them the whole GEMM
+        # (measured on one GPU beside the FC1-shaped GEMM: +24 % with 16 copy CTAs, +7 % with 148, and the copy
+        # itself runs 3x faster); spread over all SMs nobody is the straggler.  DHELLAM_PUSH_CTAS / DHELLAM_RS_CTAS
+        # override the counts, DHELLAM_COMM_SPREAD=1 selects 64-thread CTAs.
         spread = os.environ.get("DHELLAM_COMM_SPREAD", "0") == "1"
         self.comm_threads = 64 if spread else 256
-        self.push_ctas = push_ctas or int(os.environ.get("DHELLAM_PUSH_CTAS", "0")) or (self.sms if spread else max(16, 96 // self.world))
+        self.push_ctas = push_ctas or int(os.environ.get("DHELLAM_PUSH_CTAS", "0")) or self.sms
         rows = max_rows or train.micro_batch_size * cfg.seq_length // max(ps.cp, 1)
         width = width or cfg.hidden_size
         assert rows % (self.world * 128) == 0, "rows per micro-batch must divide by tp x 128 for the fused kernels"
@@ -129,7 +131,7 @@ class FusedTP:
         # split 139.5k, fused 130.8k, library collectives 137.0k; on 2 GPUs split and fused are within 1 %.
         self.policy = os.environ.get("DHELLAM_FUSED_POLICY", "split")
         self.paired = True                # set by the engine before every layer run
-        self.rs_ctas = int(os.environ.get("DHELLAM_RS_CTAS", "0")) or (self.sms if spread else max(16, 128 // self.world))
+        self.rs_ctas = int(os.environ.get("DHELLAM_RS_CTAS", "0")) or self.sms
         self.exposed = None               # the engine's ExposedTimer (set by the trainer); None = no measurement
         # Tile-granular overlap between a GEMM and the collective beside it (split policy):
         #   DHELLAM_AG_INKERNEL=1  the GEMM that consumes a gathered operand waits per 128-row block inside the kernel
