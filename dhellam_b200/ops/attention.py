@@ -146,6 +146,12 @@ def set_attn_bwd_mode(mode: int):
     K.proto("dh_attn_set_bwd_mode", [c_int], None)(int(mode))
 
 
+def _offsets(cu):
+    """``cu_seqlens`` as a Python list.  A CUDA tensor costs a device synchronisation here; pass a CPU tensor or a
+    list (the offsets are known on the host in every caller of this package) to avoid it."""
+    return [int(x) for x in (cu.tolist() if torch.is_tensor(cu) else cu)]
+
+
 def _uniform_length(cu):
     """Common length of the sequences described by cumulative offsets ``cu`` (starting at 0), or 0 if they differ."""
     if len(cu) < 2 or cu[0] != 0:
@@ -168,8 +174,8 @@ def pymha_varlen_fwd(q, k, v, cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seql
     A batch of equal-length sequences runs as ONE launch over strided views of the packed tensors; sequences
     of different lengths run one strided call each, so no padding copy is made.  Attention dropout is not supported by the sm_100a kernel (``p_dropout`` must be 0)."""
     assert p_dropout == 0.0, "attention dropout is not implemented"
-    cq = [int(x) for x in cu_seqlens_q.tolist()]
-    ck = [int(x) for x in cu_seqlens_k.tolist()]
+    cq = _offsets(cu_seqlens_q)
+    ck = _offsets(cu_seqlens_k)
     b = len(cq) - 1
     sq, sk = _uniform_length(cq), _uniform_length(ck)
     if sq and sk and sq == max_seqlen_q:
@@ -192,8 +198,8 @@ def pymha_varlen_bwd(dout, q, k, v, out, softmax_lse, cu_seqlens_q, cu_seqlens_k
                      softmax_scale: float | None = None, is_causal: bool = True, rng_state=None, deterministic: bool = False,
                      math_sm_count: int = 0, profiling: bool = False, stream_ptr: int = 0):
     """Backward of ``pymha_varlen_fwd`` (csrc/operators/ops.h:34-52).  Returns ``(dq, dk, dv)``."""
-    cq = [int(x) for x in cu_seqlens_q.tolist()]
-    ck = [int(x) for x in cu_seqlens_k.tolist()]
+    cq = _offsets(cu_seqlens_q)
+    ck = _offsets(cu_seqlens_k)
     dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
     b = len(cq) - 1
     sq, sk = _uniform_length(cq), _uniform_length(ck)
