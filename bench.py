@@ -60,7 +60,7 @@ def parse():
     ap.add_argument("--ep", type=int, default=1)
     ap.add_argument("--distributed-optimizer", action="store_true")
     ap.add_argument("--ab", default="", help="comma-separated extra arms measured in the same process after the main one "
-                    "(fused, nccl, spread, ctas16, legacy-split, whole-rs, whole-ag, sched=<strategy file>): each reports tokens/s under the key 'ab'")
+                    "(fused, nccl, spread, cta-per-sm, legacy-split, whole-rs, whole-ag, sched=<strategy file>): each reports tokens/s under the key 'ab'")
     ap.add_argument("--ab-steps", type=int, default=0, help="timed steps of every extra arm (0 = same as --steps)")
     return ap.parse_args()
 
@@ -129,7 +129,7 @@ AB_ARMS = {
     "nccl": ({}, True),
     "spread": ({"DHELLAM_COMM_SPREAD": "1"}, False),                      # one small communication CTA per SM
     "legacy-split": ({"DHELLAM_RS_BLOCKS": "0", "DHELLAM_AG_INKERNEL": "0"}, False),   # whole-buffer waits, no tile-granular overlap
-    "ctas16": ({"DHELLAM_PUSH_CTAS": "16", "DHELLAM_RS_CTAS": "16"}, False),   # communication kernels on 16 SMs instead of one CTA per SM
+    "cta-per-sm": ({"DHELLAM_PUSH_CTAS": "148", "DHELLAM_RS_CTAS": "148"}, False),   # communication kernels on every SM (256 threads)
     "whole-rs": ({"DHELLAM_RS_BLOCKS": "0"}, False),                      # tile-granular all-gather side only
     "whole-ag": ({"DHELLAM_AG_INKERNEL": "0"}, False),                    # tile-granular reduce-scatter side only
 }

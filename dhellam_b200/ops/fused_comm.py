@@ -63,14 +63,18 @@ class FusedTP:
         self.world, self.rank = ps.tp, ps.tp_rank
         # the shard a rank pushes is 1/tp of the operand: fewer ranks -> more bytes per rank -> more copy CTAs
         self.sms = K.lib().dh_sm_count()
-        # Stand-alone communication kernels: one CTA of 256 threads per SM.  A persistent GEMM assigns its tiles to
-        # CTAs statically, so a copy kernel that sits on 16 SMs slows those 16 CTAs and with them the whole GEMM
-        # (measured on one GPU beside the FC1-shaped GEMM: +24 % with 16 copy CTAs, +7 % with 148, and the copy
-        # itself runs 3x faster); spread over all SMs nobody is the straggler.  DHELLAM_PUSH_CTAS / DHELLAM_RS_CTAS
-        # override the counts, DHELLAM_COMM_SPREAD=1 selects 64-thread CTAs.
+        # Stand-alone communication kernels: a few 256-thread CTAs (16 on 8 GPUs).  Two effects pull in opposite
+        # directions.  A persistent GEMM deals its tiles to CTAs statically, so a copy kernel on 16 SMs makes those 16
+        # CTAs the stragglers of the whole GEMM (one GPU, copy beside the FC1-shaped GEMM: +24 % with 16 copy CTAs,
+        # +7 % with one per SM, and the copy itself 3x faster).  But a 256-thread communication CTA (26 K registers)
+        # does not fit on an SM beside a CTA of the attention forward (54 K of the 64 K), so a copy that sits on EVERY
+        # SM keeps the attention kernel of the other strand from starting until it has finished.  Measured in the
+        # training step on 8 GPUs, same call: 16 CTAs 146.4k tokens/s, one CTA per SM 142.2k.  DHELLAM_PUSH_CTAS /
+        # DHELLAM_RS_CTAS set the counts; DHELLAM_COMM_SPREAD=1 selects one 64-thread CTA per SM (7 K registers, fits
+        # beside attention; not yet measured in the step on 8 GPUs).
         spread = os.environ.get("DHELLAM_COMM_SPREAD", "0") == "1"
         self.comm_threads = 64 if spread else 256
-        self.push_ctas = push_ctas or int(os.environ.get("DHELLAM_PUSH_CTAS", "0")) or self.sms
+        self.push_ctas = push_ctas or int(os.environ.get("DHELLAM_PUSH_CTAS", "0")) or (self.sms if spread else max(16, 96 // self.world))
         rows = max_rows or train.micro_batch_size * cfg.seq_length // max(ps.cp, 1)
         width = width or cfg.hidden_size
         assert rows % (self.world * 128) == 0, "rows per micro-batch must divide by tp x 128 for the fused kernels"
@@ -131,7 +135,7 @@ class FusedTP:
         # split 139.5k, fused 130.8k, library collectives 137.0k; on 2 GPUs split and fused are within 1 %.
         self.policy = os.environ.get("DHELLAM_FUSED_POLICY", "split")
         self.paired = True                # set by the engine before every layer run
-        self.rs_ctas = int(os.environ.get("DHELLAM_RS_CTAS", "0")) or self.sms
+        self.rs_ctas = int(os.environ.get("DHELLAM_RS_CTAS", "0")) or (self.sms if spread else max(16, 128 // self.world))
         self.exposed = None               # the engine's ExposedTimer (set by the trainer); None = no measurement
         # Tile-granular overlap between a GEMM and the collective beside it (split policy):
         #   DHELLAM_AG_INKERNEL=1  the GEMM that consumes a gathered operand waits per 128-row block inside the kernel
