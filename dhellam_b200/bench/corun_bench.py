@@ -1,6 +1,7 @@
 """How much does a copy kernel that shares the GPU slow the persistent GEMM, by how the copy is spread over SMs.
 
     python -m dhellam_b200.bench.corun_bench [M N K]
+    python -m dhellam_b200.bench.corun_bench attn            # the attention forward (seq 4096, batch 4, 8 heads) instead of a GEMM
 
 One GPU.  The copy is the all-gather push kernel (``dh_ag_push``) with both "ranks'" buffers in this GPU's
 memory, run on a second stream for the whole duration of the GEMM; the GEMM is timed with CUDA events on
@@ -26,11 +27,21 @@ def main(argv=None):
     argv = sys.argv[1:] if argv is None else argv
     dev = "cuda"
     M, N, Kd = 16384, 7168, 8192
+    attn = bool(argv) and argv[0] == "attn"
     if len(argv) >= 3:
         M, N, Kd = (int(x) for x in argv[:3])
-    a = (torch.randn(M, Kd, device=dev)).to(torch.bfloat16)
-    w = (torch.randn(N, Kd, device=dev) * 0.02).to(torch.bfloat16)
-    out = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
+    if attn:
+        from ..ops.attention import attn_fwd
+        qkv = torch.randn(4096, 4, 10, 128, device=dev).to(torch.bfloat16)
+        q, k, v = qkv[:, :, :8], qkv[:, :, 8:9], qkv[:, :, 9:]
+        work = lambda: attn_fwd(q, k, v, True)
+        label = {"kernel": "attn_fwd", "shape": [4096, 4, 8, 1]}
+    else:
+        a = (torch.randn(M, Kd, device=dev)).to(torch.bfloat16)
+        w = (torch.randn(N, Kd, device=dev) * 0.02).to(torch.bfloat16)
+        out = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
+        work = lambda: gemm_nt(a, w, out=out)
+        label = {"kernel": "gemm_nt", "shape": [M, N, Kd]}
     rows, width = 16384, 8192
     shard = torch.randn(rows // 2, width, device=dev).to(torch.bfloat16)      # "rank 0 of 2": both ranks' buffers are local
     stage0 = torch.empty(rows, width, device=dev, dtype=torch.bfloat16)
@@ -59,7 +70,7 @@ def main(argv=None):
                         K.check(push(shard.data_ptr(), arr1, arr2, None, rows, width, 0, 2, ctas, threads, slices, side.cuda_stream), "push")
                     c1.record()
             e0.record()
-            gemm_nt(a, w, out=out)
+            work()
             e1.record()
             torch.cuda.synchronize()
             ts.append(e0.elapsed_time(e1))
@@ -68,10 +79,10 @@ def main(argv=None):
         return statistics.median(ts[3:]), (statistics.median(tc[3:]) if tc else 0.0)
 
     base, _ = run(0, 0)
-    print(json.dumps({"gemm_alone_ms": round(base, 4), "shape": [M, N, Kd]}))
+    print(json.dumps(dict(label, alone_ms=round(base, 4))))
     for ctas, threads in ((16, 256), (32, 256), (64, 256), (148, 64), (148, 128), (148, 256)):
         t, c = run(ctas, threads)
-        print(json.dumps({"copy_ctas": ctas, "copy_threads": threads, "gemm_ms": round(t, 4), "gemm_slowdown": round(t / base, 3),
+        print(json.dumps({"copy_ctas": ctas, "copy_threads": threads, "kernel_ms": round(t, 4), "slowdown": round(t / base, 3),
                           "copy_ms_per_268MB": round(c, 4)}), flush=True)
     st = K.read_status()
     print(json.dumps({"status": st.code}))

@@ -63,15 +63,14 @@ class FusedTP:
         self.world, self.rank = ps.tp, ps.tp_rank
         # the shard a rank pushes is 1/tp of the operand: fewer ranks -> more bytes per rank -> more copy CTAs
         self.sms = K.lib().dh_sm_count()
-        # Stand-alone communication kernels: a few 256-thread CTAs (16 on 8 GPUs).  Two effects pull in opposite
-        # directions.  A persistent GEMM deals its tiles to CTAs statically, so a copy kernel on 16 SMs makes those 16
-        # CTAs the stragglers of the whole GEMM (one GPU, copy beside the FC1-shaped GEMM: +24 % with 16 copy CTAs,
-        # +7 % with one per SM, and the copy itself 3x faster).  But a 256-thread communication CTA (26 K registers)
-        # does not fit on an SM beside a CTA of the attention forward (54 K of the 64 K), so a copy that sits on EVERY
-        # SM keeps the attention kernel of the other strand from starting until it has finished.  Measured in the
-        # training step on 8 GPUs, same call: 16 CTAs 146.4k tokens/s, one CTA per SM 142.2k.  DHELLAM_PUSH_CTAS /
-        # DHELLAM_RS_CTAS set the counts; DHELLAM_COMM_SPREAD=1 selects one 64-thread CTA per SM (7 K registers, fits
-        # beside attention; not yet measured in the step on 8 GPUs).
+        # Stand-alone communication kernels: a few 256-thread CTAs (16 on 8 GPUs).  Measured alone, more is better: a
+        # persistent GEMM deals its tiles to CTAs statically, so a copy kernel on 16 SMs makes those 16 CTAs the
+        # stragglers of the whole GEMM (one GPU, copy beside the FC1-shaped GEMM: +24 % with 16 copy CTAs, +7 % with
+        # one per SM, and the copy itself 3x faster).  Measured in the training step on 8 GPUs (same call) it is the
+        # other way round: 16 CTAs 146.4k tokens/s, one CTA per SM 142.2k.  Why is not known (the attention forward
+        # beside the same copy loses only 5 % on one GPU, so it is not that kernel being kept off the SMs); the step
+        # decides the default.  DHELLAM_PUSH_CTAS / DHELLAM_RS_CTAS set the counts; DHELLAM_COMM_SPREAD=1 selects one
+        # 64-thread CTA per SM (not yet measured in the step on 8 GPUs).
         spread = os.environ.get("DHELLAM_COMM_SPREAD", "0") == "1"
         self.comm_threads = 64 if spread else 256
         self.push_ctas = push_ctas or int(os.environ.get("DHELLAM_PUSH_CTAS", "0")) or (self.sms if spread else max(16, 96 // self.world))
