@@ -126,6 +126,12 @@ def _add_megatron_args(parser):
     d.add_argument("--tokenizer-type", default=None)
     d.add_argument("--tokenizer-model", default=None)
     d.add_argument("--split", default=None)
+    # accepted so that the reference's launch lines (script/run.sh:108-160) parse unchanged; tokenisation happens before
+    # this engine (it reads token files or synthetic ids), and there is one transformer implementation
+    d.add_argument("--vocab-file", default=None)
+    d.add_argument("--merge-file", default=None)
+    d.add_argument("--data-cache-path", default=None)
+    d.add_argument("--transformer-impl", default="local")
     return parser
 
 

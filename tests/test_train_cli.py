@@ -57,3 +57,30 @@ def test_train_cli_two_ranks_tensor_and_sequence_parallel(tmp_path):
     assert p.returncode == 0, p.stdout[-2000:] + p.stderr[-4000:]
     recs = [json.loads(l) for l in open(tmp_path / "m.jsonl")]
     assert len(recs) == 2 and recs[0]["tokens_per_s"] > 0
+
+
+def test_the_reference_launch_lines_parse_unchanged():
+    """Every flag of the reference's one-click script (script/run.sh:55-160, both model types) is accepted by
+    the Megatron-style parser, so a user of the reference can keep the launch line."""
+    from dhellam_b200.adaptor.megatron import build_parser
+    common = ["--num-layers", "8", "--hidden-size", "8192", "--num-attention-heads", "64", "--seq-length", "8192",
+              "--max-position-embeddings", "8192", "--transformer-impl", "transformer_engine", "--vocab-size", "128256",
+              "--global-batch-size", "16", "--micro-batch-size", "4", "--train-iters", "2", "--weight-decay", "0.1",
+              "--adam-beta1", "0.9", "--adam-beta2", "0.95", "--init-method-std", "0.006", "--clip-grad", "1.0", "--lr", "6.0e-5",
+              "--lr-decay-style", "cosine", "--min-lr", "6.0e-6", "--lr-warmup-fraction", ".001", "--lr-decay-iters", "430000",
+              "--use-mcore-models", "--distributed-backend", "nccl", "--initial-loss-scale", "65536", "--disable-bias-linear",
+              "--fp16", "--use-distributed-optimizer", "--use-flash-attn", "--tensor-model-parallel-size", "8",
+              "--context-parallel-size", "1", "--pipeline-model-parallel-size", "1", "--distributed-timeout-minutes", "2",
+              "--sequence-parallel", "--attention-mask-cuda-init", "--log-throughput", "--timing-log-level", "2",
+              "--log-interval", "1", "--save-interval", "10000", "--eval-interval", "10000", "--eval-iters", "0",
+              "--dhellam", "--schedule-config", "config/best.json"]
+    llama = ["--data-cache-path", "d/cache", "--tokenizer-type", "Llama2Tokenizer", "--tokenizer-model", "d/tokenizer.model",
+             "--data-path", "d/oscar_text_document", "--split", "949,50,1", "--ffn-hidden-size", "28672", "--swiglu",
+             "--group-query-attention", "--num-query-groups", "8"]
+    gpt = ["--data-path", "d/my-gpt2_text_document", "--vocab-file", "d/gpt2-vocab.json", "--merge-file", "d/gpt2-merges.txt",
+           "--split", "949,50,1", "--tokenizer-type", "GPT2BPETokenizer"]
+    parser = build_parser()
+    a = parser.parse_args(common + llama)
+    assert a.tensor_model_parallel_size == 8 and a.sequence_parallel and a.dhellam and a.schedule_config == "config/best.json"
+    b = parser.parse_args(common + gpt)
+    assert b.vocab_file == "d/gpt2-vocab.json" and b.merge_file == "d/gpt2-merges.txt"
