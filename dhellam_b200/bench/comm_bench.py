@@ -1,4 +1,5 @@
-"""Device-timed benchmark of the tensor-parallel communication paths, one JSON line per path.
+"""Device-timed benchmark of the tensor-parallel communication paths, one JSON line per path (the collectives
+of dhellam/operators/comm.py:13-58 alone and beside the GEMMs they feed or follow, dhellam/core/dstb.py:407-425).
 
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
         -m dhellam_b200.bench.comm_bench [--rows 16384] [--width 8192] [--iters 10]

@@ -1,4 +1,5 @@
-"""How much does a copy kernel that shares the GPU slow the persistent GEMM, by how the copy is spread over SMs.
+"""How much does a copy kernel that shares the GPU slow the persistent GEMM, by how the copy is spread over SMs
+(a one-pair version of the reference's pairwise overlap matrix, micro_benchmark/overlap.py:1-227).
 
     python -m dhellam_b200.bench.corun_bench [M N K]
     python -m dhellam_b200.bench.corun_bench attn            # the attention forward (seq 4096, batch 4, 8 heads) instead of a GEMM

@@ -11,6 +11,9 @@
 //                 block (multimem.ld_reduce adds the copies in fp32 inside the switch; plain peer
 //                 loads + fp32 adds without the alias) into the bf16 output shard.
 //
+// Role in the reference: all_gather_into_tensor / reduce_scatter_tensor along the sequence dimension
+// (dhellam/operators/comm.py:13-58) and its chunked prototypes (comm.py:89-143).
+//
 // Both are written for "a group of T threads of one CTA" (a whole 256-thread CTA of a stand-alone
 // kernel, or the 64 threads of the two communication warps of a GEMM CTA); `group_sync` is the
 // barrier of that group.  Work items are (row block, column slice) and are spread over `ngroups`

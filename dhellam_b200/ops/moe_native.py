@@ -1,6 +1,7 @@
 """Device-resident mixture-of-experts exchange (GPU only): plan, dispatch, grouped expert GEMMs, combine.
 
-The reference has no MoE ops at all (see ``models/moe.py``).  ``ops/moe.py`` is the host-driven
+The reference has no MoE ops at all (it claims expert parallelism, README.md:8; the only trace in its code is the
+all-to-all entry of micro_benchmark/overlap.py:141-145; see ``models/moe.py``).  ``ops/moe.py`` is the host-driven
 restatement used on CPU ranks: sort / bincount, two ``.tolist()`` reads per layer, a variable-size
 ``all_to_all_single`` and a Python loop of per-expert GEMMs.  Here nothing about the routing ever
 reaches the host:
